@@ -1,0 +1,127 @@
+/*
+ * kdw.h - C ABI of the B200 (sm_100a) depthwise 3x3x3 channels-last fp16 convolution library.
+ *
+ * The library replaces the device side of two kerops operators:
+ *   kerops.ops.conv.DWConv       (kerops/ops/conv/dwconv.py:25-63,  kernel kerops/kernels/dw_conv.py:5-142)
+ *   kerops.ops.conv.DWConvWGRAD  (kerops/ops/conv/dwconv_wgrad.py:31-79, kernel kerops/kernels/dw_conv.py:147-287)
+ *
+ * Conventions
+ *   - Activations are channels_last_3d fp16 volumes.  kerops names the axes (N, C, H, W, D); the element
+ *     offset of (n, c, h, w, d) is n*strideN + h*strideH + w*strideW + d*C + c, i.e. the channel stride is 1
+ *     and the stride of the innermost spatial axis D is C.  Strides are in ELEMENTS.
+ *   - Weights / weight gradients are [3][3][3][C] contiguous (taps along h, w, d, then channel), the layout
+ *     asserted at kerops/ops/conv/dwconv.py:32.
+ *   - Cross-correlation, stride 1, zero padding 1, no bias:
+ *       y[n,h,w,d,c]  = sum_{a,b,t} x[n,h+a-1,w+b-1,d+t-1,c] * weight[a,b,t,c]
+ *       dw[a,b,t,c]   = sum_{n,h,w,d} grad[n,h,w,d,c] * x[n,h+a-1,w+b-1,d+t-1,c]
+ *   - Every function only ENQUEUES work on `stream` (a cudaStream_t passed as void*); none synchronises,
+ *     allocates or frees device memory, or keeps a pointer after it returns.  Outputs and workspaces are
+ *     allocated by the caller (the Python layer uses torch's allocator, like the reference's
+ *     torch.empty_like / torch.zeros at dwconv.py:40 and dwconv_wgrad.py:54).
+ *   - Return value: 0 on success, negative for an argument error, positive = cudaError_t / CUresult of a
+ *     failed runtime or driver call.  kdw_last_error() gives the message of the calling thread's last failure.
+ */
+#ifndef KDW_H_
+#define KDW_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* accumulate types, mirror the ACCTYPE keyword of the reference ('float32' | 'float16', dwconv.py:35) */
+#define KDW_ACC_F32 0
+#define KDW_ACC_F16 1
+
+/* argument errors */
+#define KDW_ERR_ARG (-1)         /* null pointer, non-positive size, bad enum            */
+#define KDW_ERR_ALIGN (-2)       /* pointer or stride not usable by the selected kernel  */
+#define KDW_ERR_WORKSPACE (-3)   /* workspace smaller than kdw_wgrad_workspace_bytes()   */
+#define KDW_ERR_TUNE (-4)        /* `tune` names no kernel variant valid for this C      */
+#define KDW_ERR_RANGE (-5)       /* plane range outside the tensor                       */
+
+/* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
+int kdw_version(void);
+
+/* Message of the last failure on the calling thread ("" if none). No reference counterpart. */
+const char* kdw_last_error(void);
+
+/*
+ * Reads and clears the device-side status word of the CURRENT device (synchronises the device):
+ * 0 = ok, 1 = a bounded wait on a TMA barrier ran out inside a kernel (the kernel stopped early and its
+ * output is invalid).  No reference counterpart (the reference has no device-side waits).
+ */
+int kdw_device_status(int* status);
+
+/*
+ * Forward pass.  Replaces the launch loop of kerops/ops/conv/dwconv.py:47-61 (one launch per sample of
+ * _DWConv_cl3d_impl) by one launch over the whole batch.
+ *   x, y      fp16 volumes (N, C, H, W, D), strides in elements; y may have different N/H/W strides
+ *   weight    fp16 [3][3][3][C]
+ *   acc_type  KDW_ACC_F32: per input plane the 9 taps are summed with packed fp16 FMAs and the three
+ *             plane partials are added in fp32;  KDW_ACC_F16: all 27 taps in one fp16 FMA chain
+ *   tune      0 = built-in choice for this C; >0 = explicit kernel variant (see kdw_fprop_variants());
+ *             takes the place of the num_warps / D_block keywords (dwconv.py:10-17)
+ * C must be a power of two.  C >= 8 uses the TMA kernel (x, y 16-byte aligned, strides multiples of 8);
+ * smaller C uses a plain kernel.
+ */
+int kdw_fprop_f16(const void* x, const void* weight, void* y, int64_t N, int64_t C, int64_t H, int64_t W,
+                  int64_t D, int64_t x_strideN, int64_t x_strideH, int64_t x_strideW, int64_t y_strideN,
+                  int64_t y_strideH, int64_t y_strideW, int acc_type, int tune, void* stream);
+
+/*
+ * Forward pass over a range of h-planes, for volumes sharded along H with halo planes (no reference
+ * counterpart: the reference is single-GPU).  Computes output planes h in [h_begin, h_end) in x's plane
+ * numbering, reading x planes h_begin-1 .. h_end (planes outside [0, Hx) read as zero), and writes them to
+ * y plane (h - y_h0); y has Hy planes and 0 <= h_begin - y_h0, h_end - y_h0 <= Hy.
+ */
+int kdw_fprop_f16_range(const void* x, const void* weight, void* y, int64_t N, int64_t C, int64_t Hx, int64_t W,
+                        int64_t D, int64_t x_strideN, int64_t x_strideH, int64_t x_strideW, int64_t Hy,
+                        int64_t y_strideN, int64_t y_strideH, int64_t y_strideW, int64_t h_begin, int64_t h_end,
+                        int64_t y_h0, int acc_type, int tune, void* stream);
+
+/* Number of fprop kernel variants; variant ids are 1..count.  kdw_fprop_variant_channels(id) gives the
+ * channel-slice width of a variant (usable when C is a multiple of it).  No reference counterpart. */
+int kdw_fprop_variants(void);
+int kdw_fprop_variant_channels(int id);
+
+/*
+ * Bytes of device workspace kdw_wgrad_f16 needs on the current device (upper bound for any tune).  Takes
+ * the place of the fp16 partial buffer [N, grid, 3,3,3,C] the reference allocates (dwconv_wgrad.py:54).
+ * The workspace needs no initialisation.
+ */
+int64_t kdw_wgrad_workspace_bytes(int64_t N, int64_t C, int64_t H, int64_t W, int64_t D);
+
+/*
+ * Weight gradient.  Replaces dwconv_wgrad.py:54-77: the zero-filled partial buffer, the per-sample launches
+ * of _DWConv_wgrad_cl3d_impl and the torch sum over partials.
+ *   x, grad    fp16 volumes (N, C, H, W, D)
+ *   workspace  >= kdw_wgrad_workspace_bytes() bytes, 16-byte aligned; holds one fp32 [27][C] row per CTA
+ *   dw_f32     optional fp32 [3][3][3][C] result (NULL to skip) - the quantity to all-reduce across GPUs
+ *   dw_f16     optional fp16 [3][3][3][C] result (NULL to skip) - what DWConvWGRAD returns (dwconv_wgrad.py:77)
+ * Pass 1 accumulates per-CTA fp32 rows (fp16 products summed over 8 voxels, then fp32); pass 2 adds the rows
+ * in CTA order.  No atomics: the result is bitwise reproducible for a given device and shape.
+ */
+int kdw_wgrad_f16(const void* x, const void* grad, void* workspace, int64_t workspace_bytes, float* dw_f32,
+                  void* dw_f16, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D, int64_t x_strideN,
+                  int64_t x_strideH, int64_t x_strideW, int64_t g_strideN, int64_t g_strideH, int64_t g_strideW,
+                  int tune, void* stream);
+
+/*
+ * Weight gradient over a range of h-planes (H-sharded volumes; no reference counterpart).  Sums over grad
+ * planes h in [h_begin, h_end) in x's plane numbering; grad plane index is (h - g_h0), grad has Hg planes.
+ * x planes h_begin-1 .. h_end are read (zero outside [0, Hx)).
+ */
+int kdw_wgrad_f16_range(const void* x, const void* grad, void* workspace, int64_t workspace_bytes, float* dw_f32,
+                        void* dw_f16, int64_t N, int64_t C, int64_t Hx, int64_t W, int64_t D, int64_t x_strideN,
+                        int64_t x_strideH, int64_t x_strideW, int64_t Hg, int64_t g_strideN, int64_t g_strideH,
+                        int64_t g_strideW, int64_t h_begin, int64_t h_end, int64_t g_h0, int tune, void* stream);
+
+int kdw_wgrad_variants(void);
+int kdw_wgrad_variant_channels(int id);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KDW_H_ */

@@ -1,0 +1,341 @@
+// Depthwise 3x3x3 channels-last fp16 forward pass for sm_100a.
+//
+// Replaces kerops/kernels/dw_conv.py:5-142 (_DWConv_cl3d_impl) and its launch loop
+// (kerops/ops/conv/dwconv.py:42-61).
+//
+// TMA kernel (C multiple of 8).  A CTA owns a column (w-tile x d-tile x channel-slice) and marches
+// along h.  Each step it receives ONE halo'd input plane [(WT+2) x (DT+2) x CS] by a tiled TMA load
+// (zero fill outside the volume = the padding on all three axes), and every thread - fixed
+// (channel pairs, d), M consecutive w positions - applies the plane to the three output planes
+// that use it:
+//     plane q+1 gets the a=0 taps, plane q the a=1 taps, plane q-1 the a=2 taps,
+// each as a 9-term packed-half (HFMA2) chain.  The three 9-tap partials of an output are added in
+// fp32 (mixed-precision add), so per output there are 27 HFMA2/2 + 3 fp32 adds and no index
+// arithmetic in the inner loop.  A finished plane is staged in shared memory and leaves through a
+// TMA store (which clips the w/d tails).  Every input plane is read from shared memory exactly
+// once per thread-patch; the weights (27 x channel pairs) live in registers.
+//
+// Plain kernel (any C): one thread per output element, fp32 FMAs, bounds checks.  Used for C < 8.
+#include "../../include/kdw.h"
+#include "fprop_core.cuh"
+#include "kdw_common.cuh"
+
+namespace kdw {
+
+// ------------------------------------------------------------------------------------------------
+// Plain kernel
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) fprop_plain_kernel(const __half* __restrict__ x, const __half* __restrict__ w,
+                                                         __half* __restrict__ y, long long total, int C, int Hx, int W,
+                                                         int D, long long xsN, long long xsH, long long xsW,
+                                                         long long ysN, long long ysH, long long ysW, int h_begin,
+                                                         int Hr, int y_h0, int acc16) {
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        long long r = idx;
+        const int c = (int)(r % C);
+        r /= C;
+        const int d = (int)(r % D);
+        r /= D;
+        const int wv = (int)(r % W);
+        r /= W;
+        const int h = h_begin + (int)(r % Hr);
+        const long long n = r / Hr;
+        float acc = 0.f;
+        __half acch = __float2half(0.f);
+#pragma unroll
+        for (int a = 0; a < 3; ++a) {
+            const int hh = h + a - 1;
+            if (hh < 0 || hh >= Hx) continue;
+#pragma unroll
+            for (int b = 0; b < 3; ++b) {
+                const int ww = wv + b - 1;
+                if (ww < 0 || ww >= W) continue;
+#pragma unroll
+                for (int t = 0; t < 3; ++t) {
+                    const int dd = d + t - 1;
+                    if (dd < 0 || dd >= D) continue;
+                    const __half xv = x[n * xsN + hh * xsH + ww * xsW + (long long)dd * C + c];
+                    const __half wt = w[((a * 3 + b) * 3 + t) * C + c];
+                    if (acc16)
+                        acch = __hfma(xv, wt, acch);
+                    else
+                        acc = fmaf(__half2float(xv), __half2float(wt), acc);
+                }
+            }
+        }
+        y[n * ysN + (long long)(h - y_h0) * ysH + wv * ysW + (long long)d * C + c] =
+            acc16 ? acch : __float2half_rn(acc);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// TMA kernel
+// ------------------------------------------------------------------------------------------------
+template <class Cfg, bool ACC16>
+__global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
+    fprop_tma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
+                     const __half* __restrict__ weight, const Sched s, const int C, const int y_h0, int* status) {
+    constexpr int M = Cfg::M, CP = Cfg::CP, ST = Cfg::ST;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
+    unsigned char* in_base = smem;
+    unsigned char* out_base = smem + ST * Cfg::IN_STRIDE;
+    const uint32_t bar0 = smem_u32(out_base + 2 * Cfg::OUT_BYTES);
+
+    const int tid = threadIdx.x;
+    const FThread<Cfg> th(tid);
+    const int cg = th.cg, in_off = th.in_off, out_off = th.out_off;
+
+    if (tid == 0) {
+        prefetch_tmap(&tmx);
+        prefetch_tmap(&tmy);
+        for (int k = 0; k < ST; ++k) mbar_init(bar0 + 8 * k, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const long long lo = (long long)blockIdx.x * s.total / gridDim.x;
+    const long long hi = (long long)(blockIdx.x + 1) * s.total / gridDim.x;
+
+    StepIter cons;
+    cons.init(s, lo, hi);
+    StepIter prod;
+    prod.active = false;
+    uint32_t pi = 0;  // loads issued (thread 0 only)
+    if (tid == 0) {
+        prod.init(s, lo, hi);
+        for (int k = 0; k < ST && prod.active; ++k) {
+            const uint32_t bar = bar0 + 8 * (pi % ST);
+            mbar_expect_tx(bar, Cfg::IN_BYTES);
+            tma_load_5d(smem_u32(in_base + (pi % ST) * Cfg::IN_STRIDE), &tmx, bar, prod.g.c0, prod.g.d0 - 1,
+                        prod.g.w0 - 1, prod.q, prod.g.n);
+            ++pi;
+            prod.next(s);
+        }
+    }
+
+    __half2 wgt[27][CP];
+    float2 A[M][CP];
+    __half2 A16[M][CP];
+    __half2 P0[M][CP];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int i = 0; i < CP; ++i) {
+            A[m][i] = make_float2(0.f, 0.f);
+            A16[m][i] = __float2half2_rn(0.f);
+            P0[m][i] = __float2half2_rn(0.f);
+        }
+
+    uint32_t ci = 0;  // steps consumed
+    uint32_t oc = 0;  // planes stored
+    bool failed = false;
+    while (cons.active) {
+        const int q = cons.q;
+        if (q == cons.g.hb - 1) {  // new segment: this thread's taps for the segment's channel slice
+            const __half* wp = weight + cons.g.c0 + cg * 2 * CP;
+#pragma unroll
+            for (int k = 0; k < 27; ++k)
+#pragma unroll
+                for (int i = 0; i < CP; ++i)
+                    wgt[k][i] = *reinterpret_cast<const __half2*>(wp + (size_t)k * C + 2 * i);
+        }
+        const uint32_t stage = ci % ST;
+        const bool ok = mbar_wait_bounded(bar0 + 8 * stage, (ci / ST) & 1u);
+        const int am = cons.amask();
+        const __half* in = reinterpret_cast<const __half*>(in_base + stage * Cfg::IN_STRIDE) + in_off;
+        __half* ob = reinterpret_cast<__half*>(out_base + (oc & 1u) * Cfg::OUT_BYTES) + out_off;
+        switch (am) {
+            case 1: fprop_step<Cfg, ACC16, 1>(in, ob, wgt, A, A16, P0); break;
+            case 2: fprop_step<Cfg, ACC16, 2>(in, ob, wgt, A, A16, P0); break;
+            case 3: fprop_step<Cfg, ACC16, 3>(in, ob, wgt, A, A16, P0); break;
+            case 4: fprop_step<Cfg, ACC16, 4>(in, ob, wgt, A, A16, P0); break;
+            case 6: fprop_step<Cfg, ACC16, 6>(in, ob, wgt, A, A16, P0); break;
+            default: fprop_step<Cfg, ACC16, 7>(in, ob, wgt, A, A16, P0); break;
+        }
+        if (am & 4) fence_proxy_async_smem();  // the out tile must be visible to the TMA store
+        if (tid == 0) tma_wait_read_all();     // the previous store has finished reading the other out tile
+        if (__syncthreads_or(ok ? 0 : 1)) {
+            failed = true;
+            break;
+        }
+        if (tid == 0) {
+            if (am & 4) {
+                tma_store_5d(&tmy, smem_u32(out_base + (oc & 1u) * Cfg::OUT_BYTES), cons.g.c0, cons.g.d0, cons.g.w0,
+                             q - 1 - y_h0, cons.g.n);
+                tma_commit();
+            }
+            if (prod.active) {  // the stage just consumed is free: refill it ST planes ahead
+                const uint32_t bar = bar0 + 8 * (pi % ST);
+                mbar_expect_tx(bar, Cfg::IN_BYTES);
+                tma_load_5d(smem_u32(in_base + (pi % ST) * Cfg::IN_STRIDE), &tmx, bar, prod.g.c0, prod.g.d0 - 1,
+                            prod.g.w0 - 1, prod.q, prod.g.n);
+                ++pi;
+                prod.next(s);
+            }
+        }
+        if (am & 4) ++oc;
+        cons.next(s);
+        ++ci;
+    }
+    if (tid == 0) {
+        if (failed) {
+            atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
+            // loads already issued still target this CTA's shared memory: give them a bounded chance to land
+            for (uint32_t k = ci; k < pi; ++k) (void)mbar_wait_bounded(bar0 + 8 * (k % ST), (k / ST) & 1u);
+        }
+        tma_wait_all();
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+struct FpropArgs {
+    const void* x;
+    const void* w;
+    void* y;
+    int64_t N, C, Hx, W, D, xsN, xsH, xsW, Hy, ysN, ysH, ysW;
+    int h_begin, h_end, y_h0;
+    cudaStream_t stream;
+};
+
+template <class Cfg, bool ACC16>
+static int launch_fprop_tma(const FpropArgs& a) {
+    CUtensorMap tmx, tmy;
+    int rc = encode_volume_map(&tmx, a.x, a.N, a.C, a.Hx, a.W, a.D, a.xsN, a.xsH, a.xsW, Cfg::CS, Cfg::DT + 2,
+                               Cfg::WT + 2);
+    if (rc) return rc;
+    rc = encode_volume_map(&tmy, a.y, a.N, a.C, a.Hy, a.W, a.D, a.ysN, a.ysH, a.ysW, Cfg::CS, Cfg::DT, Cfg::WT);
+    if (rc) return rc;
+    if (((uintptr_t)a.w & 3) != 0) {
+        set_error("weight pointer must be 4-byte aligned");
+        return KDW_ERR_ALIGN;
+    }
+    auto kern = fprop_tma_kernel<Cfg, ACC16>;
+    KDW_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+    int occ = 0, sms = 0;
+    KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::NT, Cfg::SMEM));
+    if (occ < 1) {
+        set_error("fprop kernel variant does not fit on this device");
+        return KDW_ERR_TUNE;
+    }
+    rc = device_sm_count(&sms);
+    if (rc) return rc;
+    int* status = nullptr;
+    rc = status_ptr(&status);
+    if (rc) return rc;
+    Sched s;
+    const int grid = make_sched(&s, a.N, a.C, a.W, a.D, a.h_begin, a.h_end, Cfg::WT, Cfg::DT, Cfg::CS, sms * occ);
+    kern<<<grid, Cfg::NT, Cfg::SMEM, a.stream>>>(tmx, tmy, (const __half*)a.w, s, (int)a.C, a.y_h0, status);
+    KDW_CUDA(cudaGetLastError());
+    return 0;
+}
+
+typedef int (*FpropLaunch)(const FpropArgs&);
+struct FpropVariant {
+    int cs;
+    FpropLaunch f32, f16;
+};
+#define KDW_VARIANT(ID, CS, DT, WT, M, CP, ST, MINB)                            \
+    {CS, &launch_fprop_tma<FCfg<CS, DT, WT, M, CP, ST, MINB>, false>,           \
+     &launch_fprop_tma<FCfg<CS, DT, WT, M, CP, ST, MINB>, true>},
+// index = id - 1
+static const FpropVariant g_fprop_variants[] = {
+#include "fprop_variants.inc"
+};
+#undef KDW_VARIANT
+static const int g_n_fprop_variants = (int)(sizeof(g_fprop_variants) / sizeof(g_fprop_variants[0]));
+
+static int auto_fprop_variant(int64_t C) {
+    if (C == 8) return 1;
+    if (C == 16) return 4;
+    if (C == 32) return 6;
+    return 9;
+}
+
+static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N, int64_t C, int64_t Hx, int64_t W,
+                          int64_t D, int64_t xsN, int64_t xsH, int64_t xsW, int64_t Hy, int64_t ysN, int64_t ysH,
+                          int64_t ysW, int64_t h_begin, int64_t h_end, int64_t y_h0, int acc_type, int tune,
+                          void* stream) {
+    if (!x || !weight || !y) {
+        set_error("fprop: null pointer");
+        return KDW_ERR_ARG;
+    }
+    if (N <= 0 || C <= 0 || Hx <= 0 || W <= 0 || D <= 0 || Hy <= 0 || (C & (C - 1)) != 0) {
+        set_error("fprop: sizes must be positive and C a power of two (N=%lld C=%lld H=%lld W=%lld D=%lld)",
+                  (long long)N, (long long)C, (long long)Hx, (long long)W, (long long)D);
+        return KDW_ERR_ARG;
+    }
+    if (acc_type != KDW_ACC_F32 && acc_type != KDW_ACC_F16) {
+        set_error("fprop: acc_type must be KDW_ACC_F32 or KDW_ACC_F16");
+        return KDW_ERR_ARG;
+    }
+    if (Hx > 0x7fffffff || W > 0x7fffffff || D > 0x7fffffff || N > 0x7fffffff || C > 0x7fffffff) {
+        set_error("fprop: extent does not fit in 32 bits");
+        return KDW_ERR_ARG;
+    }
+    if (h_begin < 0 || h_end > Hx || h_begin > h_end || h_begin - y_h0 < 0 || h_end - y_h0 > Hy) {
+        set_error("fprop: plane range [%lld,%lld) / y_h0=%lld outside x (%lld planes) or y (%lld planes)",
+                  (long long)h_begin, (long long)h_end, (long long)y_h0, (long long)Hx, (long long)Hy);
+        return KDW_ERR_RANGE;
+    }
+    if (h_begin == h_end) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (tune < 0 || tune > g_n_fprop_variants) {
+        set_error("fprop: tune=%d names no kernel variant (1..%d)", tune, g_n_fprop_variants);
+        return KDW_ERR_TUNE;
+    }
+    if (C < 8) {
+        if (tune != 0) {
+            set_error("fprop: C=%lld < 8 runs the plain kernel; tune must be 0", (long long)C);
+            return KDW_ERR_TUNE;
+        }
+        const long long total = (long long)N * (h_end - h_begin) * W * D * C;
+        long long blocks = (total + 255) / 256;
+        if (blocks > 148 * 32) blocks = 148 * 32;
+        fprop_plain_kernel<<<(unsigned)blocks, 256, 0, st>>>((const __half*)x, (const __half*)weight, (__half*)y,
+                                                             total, (int)C, (int)Hx, (int)W, (int)D, xsN, xsH, xsW,
+                                                             ysN, ysH, ysW, (int)h_begin, (int)(h_end - h_begin),
+                                                             (int)y_h0, acc_type == KDW_ACC_F16);
+        KDW_CUDA(cudaGetLastError());
+        return 0;
+    }
+    const int id = tune ? tune : auto_fprop_variant(C);
+    const FpropVariant& v = g_fprop_variants[id - 1];
+    if (C % v.cs != 0) {
+        set_error("fprop: variant %d works on %d-channel slices, C=%lld is not a multiple", id, v.cs, (long long)C);
+        return KDW_ERR_TUNE;
+    }
+    FpropArgs a{x, weight, y, N, C, Hx, W, D, xsN, xsH, xsW, Hy, ysN, ysH, ysW, (int)h_begin, (int)h_end, (int)y_h0, st};
+    return (acc_type == KDW_ACC_F16) ? v.f16(a) : v.f32(a);
+}
+
+}  // namespace kdw
+
+extern "C" {
+
+int kdw_fprop_variants(void) { return kdw::g_n_fprop_variants; }
+
+int kdw_fprop_variant_channels(int id) {
+    if (id < 1 || id > kdw::g_n_fprop_variants) return KDW_ERR_TUNE;
+    return kdw::g_fprop_variants[id - 1].cs;
+}
+
+int kdw_fprop_f16(const void* x, const void* weight, void* y, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
+                  int64_t x_strideN, int64_t x_strideH, int64_t x_strideW, int64_t y_strideN, int64_t y_strideH,
+                  int64_t y_strideW, int acc_type, int tune, void* stream) {
+    return kdw::fprop_dispatch(x, weight, y, N, C, H, W, D, x_strideN, x_strideH, x_strideW, H, y_strideN, y_strideH,
+                               y_strideW, 0, H, 0, acc_type, tune, stream);
+}
+
+int kdw_fprop_f16_range(const void* x, const void* weight, void* y, int64_t N, int64_t C, int64_t Hx, int64_t W,
+                        int64_t D, int64_t x_strideN, int64_t x_strideH, int64_t x_strideW, int64_t Hy,
+                        int64_t y_strideN, int64_t y_strideH, int64_t y_strideW, int64_t h_begin, int64_t h_end,
+                        int64_t y_h0, int acc_type, int tune, void* stream) {
+    return kdw::fprop_dispatch(x, weight, y, N, C, Hx, W, D, x_strideN, x_strideH, x_strideW, Hy, y_strideN,
+                               y_strideH, y_strideW, h_begin, h_end, y_h0, acc_type, tune, stream);
+}
+
+}  // extern "C"

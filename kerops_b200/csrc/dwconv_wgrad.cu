@@ -1,0 +1,406 @@
+// Depthwise 3x3x3 channels-last fp16 weight gradient for sm_100a.
+//
+// Replaces kerops/kernels/dw_conv.py:147-287 (_DWConv_wgrad_cl3d_impl), the zero-filled fp16 partial
+// buffer and the torch sum over it (kerops/ops/conv/dwconv_wgrad.py:54-77).
+//
+// Pass 1 (TMA kernel, C multiple of 8).  Same column march as the forward kernel: per step a CTA
+// receives the halo'd x plane q and the grad plane q+1 by TMA.  A thread - fixed (channel pairs, d),
+// M consecutive w positions - keeps the grad values of planes q-1, q, q+1 in registers and multiplies
+// every x value it reads with the (up to) nine grad values whose tap it is:
+//     dw[a][b][t] += grad[q+1-a][m] * x[q][m+b][d+t].
+// The 27 products of a step go into packed-half chains of M terms, which are then added to fp32
+// accumulators (mixed-precision add).  At the end of a segment the CTA reduces over its threads
+// (warp shuffles, then warps in fixed order through shared memory) and adds the [27][CS] result to
+// its own fp32 row of the workspace.
+// Pass 2 adds the rows in CTA order and writes the fp32 and fp16 [3][3][3][C] results.
+// There are no atomics anywhere, so results are bitwise reproducible.
+//
+// Plain pass 1 (any C, used for C < 8): one thread per (tap, channel), fp32 FMAs.
+#include "../../include/kdw.h"
+#include "kdw_common.cuh"
+#include "wgrad_core.cuh"
+
+namespace kdw {
+
+static constexpr int kMaxRowsFloor = 1184;  // workspace rows are max(8 * SMs, this)
+
+// ------------------------------------------------------------------------------------------------
+// Pass 2: fixed-order sum over the CTA rows
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) wgrad_reduce_kernel(const float* __restrict__ ws, int rows, int KC,
+                                                          float* __restrict__ dw32, __half* __restrict__ dw16) {
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= KC) return;
+    float acc = 0.f;
+    for (int r = 0; r < rows; ++r) acc += ws[(size_t)r * KC + k];
+    if (dw32) dw32[k] = acc;
+    if (dw16) dw16[k] = __float2half_rn(acc);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Plain pass 1
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) wgrad_plain_kernel(const __half* __restrict__ x, const __half* __restrict__ g,
+                                                         float* __restrict__ ws, long long voxels, int C, int Hx, int W,
+                                                         int D, long long xsN, long long xsH, long long xsW,
+                                                         long long gsN, long long gsH, long long gsW, int h_begin,
+                                                         int Hr, int g_h0) {
+    const int KC = 27 * C;
+    const long long lo = (long long)blockIdx.x * voxels / gridDim.x;
+    const long long hi = (long long)(blockIdx.x + 1) * voxels / gridDim.x;
+    for (int k = threadIdx.x; k < KC; k += blockDim.x) {
+        const int c = k % C;
+        const int tap = k / C;
+        const int a = tap / 9, b = (tap / 3) % 3, t = tap % 3;
+        float acc = 0.f;
+        for (long long v = lo; v < hi; ++v) {
+            long long r = v;
+            const int d = (int)(r % D);
+            r /= D;
+            const int wv = (int)(r % W);
+            r /= W;
+            const int h = h_begin + (int)(r % Hr);
+            const long long n = r / Hr;
+            const int hh = h + a - 1, ww = wv + b - 1, dd = d + t - 1;
+            if (hh < 0 || hh >= Hx || ww < 0 || ww >= W || dd < 0 || dd >= D) continue;
+            const float gv = __half2float(g[n * gsN + (long long)(h - g_h0) * gsH + wv * gsW + (long long)d * C + c]);
+            const float xv = __half2float(x[n * xsN + hh * xsH + ww * xsW + (long long)dd * C + c]);
+            acc = fmaf(gv, xv, acc);
+        }
+        ws[(size_t)blockIdx.x * KC + k] = acc;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// TMA pass 1
+// ------------------------------------------------------------------------------------------------
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
+    wgrad_tma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmg,
+                     float* __restrict__ ws, const Sched s, const int C, const int g_h0, int* status) {
+    constexpr int CS = Cfg::CS, M = Cfg::M, CP = Cfg::CP, ST = Cfg::ST, CPG = Cfg::CPG;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
+    unsigned char* stage_base = smem;
+    float* red = reinterpret_cast<float*>(smem + ST * Cfg::STAGE);
+    const uint32_t bar0 = smem_u32(smem + ST * Cfg::STAGE + Cfg::RED_BYTES);
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const WThread<Cfg> th(tid);
+    const int cg = th.cg, x_off = th.x_off, g_off = th.g_off;
+    const int KC = 27 * C;
+    float* row = ws + (size_t)blockIdx.x * KC;
+
+    if (tid == 0) {
+        prefetch_tmap(&tmx);
+        prefetch_tmap(&tmg);
+        for (int k = 0; k < ST; ++k) mbar_init(bar0 + 8 * k, 1);
+        mbar_fence_init();
+    }
+    for (int k = tid; k < KC; k += Cfg::NT) row[k] = 0.f;  // this CTA's workspace row
+    __syncthreads();
+
+    const long long lo = (long long)blockIdx.x * s.total / gridDim.x;
+    const long long hi = (long long)(blockIdx.x + 1) * s.total / gridDim.x;
+
+    StepIter cons;
+    cons.init(s, lo, hi);
+    StepIter prod;
+    prod.active = false;
+    uint32_t pi = 0;
+    auto issue = [&]() {
+        const uint32_t st = pi % ST;
+        const uint32_t bar = bar0 + 8 * st;
+        const bool with_g = prod.q + 1 < prod.g.he;  // grad plane q+1 is owned by the segment
+        mbar_expect_tx(bar, Cfg::X_BYTES + (with_g ? Cfg::G_BYTES : 0));
+        tma_load_5d(smem_u32(stage_base + st * Cfg::STAGE), &tmx, bar, prod.g.c0, prod.g.d0 - 1, prod.g.w0 - 1, prod.q,
+                    prod.g.n);
+        if (with_g)
+            tma_load_5d(smem_u32(stage_base + st * Cfg::STAGE + Cfg::X_STRIDE), &tmg, bar, prod.g.c0, prod.g.d0,
+                        prod.g.w0, prod.q + 1 - g_h0, prod.g.n);
+        ++pi;
+        prod.next(s);
+    };
+    if (tid == 0) {
+        prod.init(s, lo, hi);
+        for (int k = 0; k < ST && prod.active; ++k) issue();
+    }
+
+    __half2 G[3][M][CP];
+    float2 acc[27][CP];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int i = 0; i < CP; ++i) G[0][m][i] = G[1][m][i] = G[2][m][i] = __float2half2_rn(0.f);
+#pragma unroll
+    for (int k = 0; k < 27; ++k)
+#pragma unroll
+        for (int i = 0; i < CP; ++i) acc[k][i] = make_float2(0.f, 0.f);
+
+    uint32_t ci = 0;
+    bool failed = false;
+    while (cons.active) {
+        const uint32_t stage = ci % ST;
+        const bool ok = mbar_wait_bounded(bar0 + 8 * stage, (ci / ST) & 1u);
+        const int am = cons.amask();
+        const __half* xin = reinterpret_cast<const __half*>(stage_base + stage * Cfg::STAGE) + x_off;
+        const __half* gin = reinterpret_cast<const __half*>(stage_base + stage * Cfg::STAGE + Cfg::X_STRIDE) + g_off;
+        switch (am) {
+            case 1: wgrad_step<Cfg, 1>(xin, gin, G, acc); break;
+            case 2: wgrad_step<Cfg, 2>(xin, gin, G, acc); break;
+            case 3: wgrad_step<Cfg, 3>(xin, gin, G, acc); break;
+            case 4: wgrad_step<Cfg, 4>(xin, gin, G, acc); break;
+            case 6: wgrad_step<Cfg, 6>(xin, gin, G, acc); break;
+            default: wgrad_step<Cfg, 7>(xin, gin, G, acc); break;
+        }
+        if (__syncthreads_or(ok ? 0 : 1)) {
+            failed = true;
+            break;
+        }
+        if (tid == 0 && prod.active) issue();  // the stage just consumed is free
+        if (cons.q == cons.g.he) {
+            // Segment finished: reduce over the threads of the CTA that share channels.
+            const int c0 = cons.g.c0;
+#pragma unroll
+            for (int k = 0; k < 27; ++k)
+#pragma unroll
+                for (int i = 0; i < CP; ++i) {
+                    float2 v = acc[k][i];
+#pragma unroll
+                    for (int off = CPG; off < 32; off <<= 1) {
+                        v.x += __shfl_xor_sync(0xffffffffu, v.x, off);
+                        v.y += __shfl_xor_sync(0xffffffffu, v.y, off);
+                    }
+                    acc[k][i] = v;
+                }
+            for (int wi = 0; wi < Cfg::NW; ++wi) {  // warps in fixed order
+                if (warp == wi && lane < CPG) {
+#pragma unroll
+                    for (int k = 0; k < 27; ++k)
+#pragma unroll
+                        for (int i = 0; i < CP; ++i) {
+                            float2* dst = reinterpret_cast<float2*>(red + k * CS + cg * 2 * CP + 2 * i);
+                            if (wi == 0) {
+                                *dst = acc[k][i];
+                            } else {
+                                float2 o = *dst;
+                                o.x += acc[k][i].x;
+                                o.y += acc[k][i].y;
+                                *dst = o;
+                            }
+                        }
+                }
+                __syncthreads();
+            }
+            for (int e = tid; e < 27 * CS; e += Cfg::NT) {
+                const int k = e / CS, c = e % CS;
+                row[k * C + c0 + c] += red[e];
+            }
+            __syncthreads();
+#pragma unroll
+            for (int k = 0; k < 27; ++k)
+#pragma unroll
+                for (int i = 0; i < CP; ++i) acc[k][i] = make_float2(0.f, 0.f);
+        }
+        cons.next(s);
+        ++ci;
+    }
+    if (tid == 0 && failed) {
+        atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
+        for (uint32_t k = ci; k < pi; ++k) (void)mbar_wait_bounded(bar0 + 8 * (k % ST), (k / ST) & 1u);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+struct WgradArgs {
+    const void* x;
+    const void* g;
+    float* ws;
+    int64_t ws_rows;
+    int64_t N, C, Hx, W, D, xsN, xsH, xsW, Hg, gsN, gsH, gsW;
+    int h_begin, h_end, g_h0;
+    cudaStream_t stream;
+};
+
+template <class Cfg>
+static int launch_wgrad_tma(const WgradArgs& a, int* rows_used) {
+    CUtensorMap tmx, tmg;
+    int rc = encode_volume_map(&tmx, a.x, a.N, a.C, a.Hx, a.W, a.D, a.xsN, a.xsH, a.xsW, Cfg::CS, Cfg::DT + 2,
+                               Cfg::WT + 2);
+    if (rc) return rc;
+    rc = encode_volume_map(&tmg, a.g, a.N, a.C, a.Hg, a.W, a.D, a.gsN, a.gsH, a.gsW, Cfg::CS, Cfg::DT, Cfg::WT);
+    if (rc) return rc;
+    auto kern = wgrad_tma_kernel<Cfg>;
+    KDW_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+    int occ = 0, sms = 0;
+    KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::NT, Cfg::SMEM));
+    if (occ < 1) {
+        set_error("wgrad kernel variant does not fit on this device");
+        return KDW_ERR_TUNE;
+    }
+    rc = device_sm_count(&sms);
+    if (rc) return rc;
+    int* status = nullptr;
+    rc = status_ptr(&status);
+    if (rc) return rc;
+    long long target = (long long)sms * occ;
+    if (target > a.ws_rows) target = a.ws_rows;
+    Sched s;
+    const int grid = make_sched(&s, a.N, a.C, a.W, a.D, a.h_begin, a.h_end, Cfg::WT, Cfg::DT, Cfg::CS, (int)target);
+    kern<<<grid, Cfg::NT, Cfg::SMEM, a.stream>>>(tmx, tmg, a.ws, s, (int)a.C, a.g_h0, status);
+    KDW_CUDA(cudaGetLastError());
+    *rows_used = grid;
+    return 0;
+}
+
+typedef int (*WgradLaunch)(const WgradArgs&, int*);
+struct WgradVariant {
+    int cs;
+    WgradLaunch f;
+};
+#define KDW_VARIANT(ID, CS, DT, WT, M, CP, ST, MINB) {CS, &launch_wgrad_tma<WCfg<CS, DT, WT, M, CP, ST, MINB>>},
+// index = id - 1
+static const WgradVariant g_wgrad_variants[] = {
+#include "wgrad_variants.inc"
+};
+#undef KDW_VARIANT
+static const int g_n_wgrad_variants = (int)(sizeof(g_wgrad_variants) / sizeof(g_wgrad_variants[0]));
+
+static int auto_wgrad_variant(int64_t C) {
+    if (C == 8) return 1;
+    if (C == 16) return 3;
+    if (C == 32) return 5;
+    return 7;
+}
+
+static int64_t ws_rows_for_device(int* rc_out) {
+    int sms = 0;
+    *rc_out = device_sm_count(&sms);
+    if (*rc_out) return 0;
+    int64_t rows = (int64_t)sms * 8;
+    if (rows < kMaxRowsFloor) rows = kMaxRowsFloor;
+    return rows;
+}
+
+static int wgrad_dispatch(const void* x, const void* grad, void* workspace, int64_t workspace_bytes, float* dw_f32,
+                          void* dw_f16, int64_t N, int64_t C, int64_t Hx, int64_t W, int64_t D, int64_t xsN, int64_t xsH,
+                          int64_t xsW, int64_t Hg, int64_t gsN, int64_t gsH, int64_t gsW, int64_t h_begin,
+                          int64_t h_end, int64_t g_h0, int tune, void* stream) {
+    if (!x || !grad || !workspace || (!dw_f32 && !dw_f16)) {
+        set_error("wgrad: null pointer (x, grad, workspace and at least one output are required)");
+        return KDW_ERR_ARG;
+    }
+    if (N <= 0 || C <= 0 || Hx <= 0 || W <= 0 || D <= 0 || Hg <= 0 || (C & (C - 1)) != 0) {
+        set_error("wgrad: sizes must be positive and C a power of two (N=%lld C=%lld H=%lld W=%lld D=%lld)",
+                  (long long)N, (long long)C, (long long)Hx, (long long)W, (long long)D);
+        return KDW_ERR_ARG;
+    }
+    if (Hx > 0x7fffffff || W > 0x7fffffff || D > 0x7fffffff || N > 0x7fffffff || C > (1 << 20)) {
+        set_error("wgrad: extent does not fit in 32 bits");
+        return KDW_ERR_ARG;
+    }
+    if (h_begin < 0 || h_end > Hx || h_begin > h_end || h_begin - g_h0 < 0 || h_end - g_h0 > Hg) {
+        set_error("wgrad: plane range [%lld,%lld) / g_h0=%lld outside x (%lld planes) or grad (%lld planes)",
+                  (long long)h_begin, (long long)h_end, (long long)g_h0, (long long)Hx, (long long)Hg);
+        return KDW_ERR_RANGE;
+    }
+    if (((uintptr_t)workspace & 15) != 0) {
+        set_error("wgrad: workspace must be 16-byte aligned");
+        return KDW_ERR_ALIGN;
+    }
+    if (tune < 0 || tune > g_n_wgrad_variants) {
+        set_error("wgrad: tune=%d names no kernel variant (1..%d)", tune, g_n_wgrad_variants);
+        return KDW_ERR_TUNE;
+    }
+    int rc = 0;
+    const int64_t rows_cap = ws_rows_for_device(&rc);
+    if (rc) return rc;
+    const int KC = (int)(27 * C);
+    if (workspace_bytes < rows_cap * KC * 4) {
+        set_error("wgrad: workspace has %lld bytes, needs %lld", (long long)workspace_bytes,
+                  (long long)(rows_cap * KC * 4));
+        return KDW_ERR_WORKSPACE;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    float* ws = (float*)workspace;
+    int rows = 0;
+    if (h_begin == h_end) {
+        // empty range: the gradient is zero
+        if (dw_f32) KDW_CUDA(cudaMemsetAsync(dw_f32, 0, (size_t)KC * 4, st));
+        if (dw_f16) KDW_CUDA(cudaMemsetAsync(dw_f16, 0, (size_t)KC * 2, st));
+        return 0;
+    }
+    if (C < 8) {
+        if (tune != 0) {
+            set_error("wgrad: C=%lld < 8 runs the plain kernel; tune must be 0", (long long)C);
+            return KDW_ERR_TUNE;
+        }
+        const long long voxels = (long long)N * (h_end - h_begin) * W * D;
+        long long blocks = voxels < rows_cap ? voxels : rows_cap;
+        wgrad_plain_kernel<<<(unsigned)blocks, 128, 0, st>>>((const __half*)x, (const __half*)grad, ws, voxels, (int)C,
+                                                             (int)Hx, (int)W, (int)D, xsN, xsH, xsW, gsN, gsH, gsW,
+                                                             (int)h_begin, (int)(h_end - h_begin), (int)g_h0);
+        KDW_CUDA(cudaGetLastError());
+        rows = (int)blocks;
+    } else {
+        const int id = tune ? tune : auto_wgrad_variant(C);
+        const WgradVariant& v = g_wgrad_variants[id - 1];
+        if (C % v.cs != 0) {
+            set_error("wgrad: variant %d works on %d-channel slices, C=%lld is not a multiple", id, v.cs,
+                      (long long)C);
+            return KDW_ERR_TUNE;
+        }
+        WgradArgs a{x,   grad, ws,  rows_cap, N,   C,          Hx,         W,          D,  xsN, xsH,
+                    xsW, Hg,   gsN, gsH,      gsW, (int)h_begin, (int)h_end, (int)g_h0, st};
+        rc = v.f(a, &rows);
+        if (rc) return rc;
+    }
+    wgrad_reduce_kernel<<<(KC + 127) / 128, 128, 0, st>>>(ws, rows, KC, dw_f32, (__half*)dw_f16);
+    KDW_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace kdw
+
+extern "C" {
+
+int kdw_wgrad_variants(void) { return kdw::g_n_wgrad_variants; }
+
+int kdw_wgrad_variant_channels(int id) {
+    if (id < 1 || id > kdw::g_n_wgrad_variants) return KDW_ERR_TUNE;
+    return kdw::g_wgrad_variants[id - 1].cs;
+}
+
+int64_t kdw_wgrad_workspace_bytes(int64_t N, int64_t C, int64_t H, int64_t W, int64_t D) {
+    (void)N;
+    (void)H;
+    (void)W;
+    (void)D;
+    if (C <= 0) return KDW_ERR_ARG;
+    int rc = 0;
+    const int64_t rows = kdw::ws_rows_for_device(&rc);
+    if (rc) return -(int64_t)rc;
+    return rows * 27 * C * 4;
+}
+
+int kdw_wgrad_f16(const void* x, const void* grad, void* workspace, int64_t workspace_bytes, float* dw_f32,
+                  void* dw_f16, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D, int64_t x_strideN,
+                  int64_t x_strideH, int64_t x_strideW, int64_t g_strideN, int64_t g_strideH, int64_t g_strideW,
+                  int tune, void* stream) {
+    return kdw::wgrad_dispatch(x, grad, workspace, workspace_bytes, dw_f32, dw_f16, N, C, H, W, D, x_strideN,
+                               x_strideH, x_strideW, H, g_strideN, g_strideH, g_strideW, 0, H, 0, tune, stream);
+}
+
+int kdw_wgrad_f16_range(const void* x, const void* grad, void* workspace, int64_t workspace_bytes, float* dw_f32,
+                        void* dw_f16, int64_t N, int64_t C, int64_t Hx, int64_t W, int64_t D, int64_t x_strideN,
+                        int64_t x_strideH, int64_t x_strideW, int64_t Hg, int64_t g_strideN, int64_t g_strideH,
+                        int64_t g_strideW, int64_t h_begin, int64_t h_end, int64_t g_h0, int tune, void* stream) {
+    return kdw::wgrad_dispatch(x, grad, workspace, workspace_bytes, dw_f32, dw_f16, N, C, Hx, W, D, x_strideN,
+                               x_strideH, x_strideW, Hg, g_strideN, g_strideH, g_strideW, h_begin, h_end, g_h0, tune,
+                               stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,278 @@
+// Shared device/host helpers for the depthwise 3x3x3 channels-last kernels (sm_100a).
+//
+//  * PTX wrappers: mbarrier, tiled TMA load/store (cp.async.bulk.tensor, no cluster
+//    multicast anywhere), proxy fences, the sm_100 mixed-precision add (f32 += f16).
+//  * Balanced plane scheduler: the (sample, h-chunk, w-tile, d-tile, channel-slice, plane)
+//    space is linearised and cut into gridDim.x equal ranges, so every CTA marches the same
+//    number of h-planes (+-1) while CTAs that run at the same time work on neighbouring
+//    columns of the same h-chunk (their halos then hit in L2).
+//  * Host helpers: error string, tensor-map encoding through the driver entry point.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace kdw {
+
+// ------------------------------------------------------------------------------------------
+// Status codes written by kernels into the per-library device status word.
+// ------------------------------------------------------------------------------------------
+enum : int {
+    KDW_STATUS_OK = 0,
+    KDW_STATUS_TMA_TIMEOUT = 1,  // a bounded mbarrier wait ran out
+};
+
+// ------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);  // records the message, returns (int)e
+
+#define KDW_CUDA(expr)                                            \
+    do {                                                          \
+        cudaError_t _e = (expr);                                  \
+        if (_e != cudaSuccess) return ::kdw::cuda_fail(_e, #expr); \
+    } while (0)
+
+// Encodes a 5-D fp16 tensor map over a channels-last volume: dims (C, D, W, H, N), element
+// strides (1, C, strideW, strideH, strideN), box (boxC, boxD, boxW, 1, 1), zero fill for
+// out-of-bounds elements.  Returns 0 or a negative argument error / positive driver error.
+int encode_volume_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
+                      int64_t strideN, int64_t strideH, int64_t strideW, int boxC, int boxD, int boxW);
+
+int device_sm_count(int* sms);
+
+// Device address (on the current device) of the library's status word.
+int status_ptr(int** p);
+
+// Work decomposition shared by fprop and wgrad (see decode_segment).
+struct Sched {
+    long long total;  // N * Kc * Hr plane units
+    int Kc;           // columns per sample = nWT * nDT * nCS
+    int Hr;           // planes in [h_begin, h_end)
+    int PH;           // planes per h-chunk
+    int nh;           // h-chunks
+    int nWT, nDT, nCS;
+    int h_begin;
+    int WT, DT, CS;   // tile extents (w, d, channels)
+};
+
+// Fills the schedule for `grid_target` CTAs; returns the grid size to launch.
+int make_sched(Sched* s, int64_t N, int64_t C, int64_t W, int64_t D, int h_begin, int h_end, int WT, int DT, int CS,
+               int grid_target);
+
+// ------------------------------------------------------------------------------------------
+// Device side
+// ------------------------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+#define KDW_HD __host__ __device__ __forceinline__
+
+struct Seg {
+    int n, w0, d0, c0;  // sample and tile origin
+    int hb, he;         // owned planes [hb, he)
+};
+
+// Decodes the segment that starts at linear position `pos` (< end); returns the number of plane
+// units it covers.  Linear order: sample, h-chunk, w-tile, d-tile, channel-slice, plane-in-chunk.
+KDW_HD int decode_segment(const Sched& s, long long pos, long long end, Seg& g) {
+    const long long per_n = (long long)s.Kc * s.Hr;
+    const int n = (int)(pos / per_n);
+    const long long r = pos - (long long)n * per_n;
+    const long long chunk_units = (long long)s.Kc * s.PH;
+    int j = (int)(r / chunk_units);
+    if (j > s.nh - 1) j = s.nh - 1;
+    const int len = (j < s.nh - 1) ? s.PH : s.Hr - (s.nh - 1) * s.PH;
+    const long long r2 = r - (long long)j * chunk_units;
+    int col = (int)(r2 / len);
+    const int p = (int)(r2 - (long long)col * len);
+    long long take = len - p;
+    if (take > end - pos) take = end - pos;
+    const int ics = col % s.nCS;
+    col /= s.nCS;
+    const int idt = col % s.nDT;
+    const int iwt = col / s.nDT;
+    g.n = n;
+    g.w0 = iwt * s.WT;
+    g.d0 = idt * s.DT;
+    g.c0 = ics * s.CS;
+    g.hb = s.h_begin + j * s.PH + p;
+    g.he = g.hb + (int)take;
+    return (int)take;
+}
+
+// Walks the input planes hb-1 .. he of every segment of a CTA's range.
+struct StepIter {
+    long long pos, end;
+    Seg g;
+    int q;
+    bool active;
+    KDW_HD void next_segment(const Sched& s) {
+        if (pos < end) {
+            pos += decode_segment(s, pos, end, g);
+            q = g.hb - 1;
+            active = true;
+        } else {
+            active = false;
+        }
+    }
+    KDW_HD void init(const Sched& s, long long p, long long e) {
+        pos = p;
+        end = e;
+        next_segment(s);
+    }
+    KDW_HD void next(const Sched& s) {
+        if (++q > g.he) next_segment(s);
+    }
+    // bit a set <=> the owned-plane test holds for plane q + 1 - a
+    KDW_HD int amask() const {
+        return ((q + 1 < g.he) ? 1 : 0) | ((q >= g.hb && q < g.he) ? 2 : 0) | ((q - 1 >= g.hb) ? 4 : 0);
+    }
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: gives up after ~2 s of wall time and returns false (the caller then raises the
+// status word and leaves the kernel instead of spinning for ever).
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63u) == 63u && global_ns() - t0 > 2000000000ull) return false;
+    }
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1, int c2,
+                                            int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+        ::"r"(dst), "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_5d(const CUtensorMap* tm, uint32_t src, int c0, int c1, int c2, int c3,
+                                             int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%1, %2, %3, %4, %5}], [%6];"
+        ::"l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(src)
+        : "memory");
+}
+__device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* tm) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tm) : "memory");
+}
+
+// Raw view of CP packed half2 values (type punning through a union).
+template <int CP>
+union H2Pack {
+    static_assert(CP == 1 || CP == 2 || CP == 4, "CP must be 1, 2 or 4");
+    __half2 h[CP];
+    uint32_t u1;
+    uint2 u2;
+    uint4 u4;
+    KDW_HD H2Pack() {}
+};
+// Packed-half multiply / fused multiply-add.  The host branches exist so that the per-thread step
+// functions can also be executed on the CPU by the test-suite's kernel emulation.
+KDW_HD __half2 h2_mul(__half2 a, __half2 b) {
+#ifdef __CUDA_ARCH__
+    return __hmul2(a, b);
+#else
+    const float2 fa = __half22float2(a), fb = __half22float2(b);
+    return __floats2half2_rn(fa.x * fb.x, fa.y * fb.y);  // an fp16 x fp16 product is exact in fp32
+#endif
+}
+KDW_HD __half2 h2_fma(__half2 a, __half2 b, __half2 c) {
+#ifdef __CUDA_ARCH__
+    return __hfma2(a, b, c);
+#else
+    const float2 fa = __half22float2(a), fb = __half22float2(b), fc = __half22float2(c);
+    const double lo = (double)fa.x * (double)fb.x + (double)fc.x;
+    const double hi = (double)fa.y * (double)fb.y + (double)fc.y;
+    return __halves2half2(__double2half(lo), __double2half(hi));
+#endif
+}
+
+// c + float(h), element-wise; on the device one sm_100 mixed-precision add per lane (no separate convert).
+KDW_HD float2 add_h2_f2(__half2 h, float2 c) {
+#ifdef __CUDA_ARCH__
+    float2 r;
+    H2Pack<1> k;
+    k.h[0] = h;
+    const uint32_t hu = k.u1;
+    asm("{\n\t.reg .b16 lo, hi;\n\t"
+        "mov.b32 {lo, hi}, %2;\n\t"
+        "add.rn.f32.f16 %0, lo, %3;\n\t"
+        "add.rn.f32.f16 %1, hi, %4;\n\t}"
+        : "=f"(r.x), "=f"(r.y)
+        : "r"(hu), "f"(c.x), "f"(c.y));
+    return r;
+#else
+    const float2 f = __half22float2(h);
+    return make_float2(f.x + c.x, f.y + c.y);
+#endif
+}
+
+// CP consecutive half2 (4*CP bytes) from / to shared memory in one access.
+template <int CP>
+KDW_HD void lds_h2(__half2 (&v)[CP], const __half* p) {
+    H2Pack<CP> k;
+    if constexpr (CP == 1)
+        k.u1 = *reinterpret_cast<const uint32_t*>(p);
+    else if constexpr (CP == 2)
+        k.u2 = *reinterpret_cast<const uint2*>(p);
+    else
+        k.u4 = *reinterpret_cast<const uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < CP; ++i) v[i] = k.h[i];
+}
+template <int CP>
+KDW_HD void sts_h2(__half* p, const __half2 (&v)[CP]) {
+    H2Pack<CP> k;
+#pragma unroll
+    for (int i = 0; i < CP; ++i) k.h[i] = v[i];
+    if constexpr (CP == 1)
+        *reinterpret_cast<uint32_t*>(p) = k.u1;
+    else if constexpr (CP == 2)
+        *reinterpret_cast<uint2*>(p) = k.u2;
+    else
+        *reinterpret_cast<uint4*>(p) = k.u4;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace kdw

@@ -1,0 +1,145 @@
+// Host-side helpers of the library: error string, device status word, tensor-map encoding,
+// schedule construction.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/kdw.h"
+#include "kdw_common.cuh"
+
+namespace kdw {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+    return (int)e;
+}
+
+// One status word per device that loads the library.
+static __device__ int g_status_word;
+
+int status_ptr(int** p) {
+    void* addr = nullptr;
+    KDW_CUDA(cudaGetSymbolAddress(&addr, g_status_word));
+    *p = (int*)addr;
+    return 0;
+}
+
+int device_sm_count(int* sms) {
+    int dev = 0;
+    KDW_CUDA(cudaGetDevice(&dev));
+    KDW_CUDA(cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev));
+    return 0;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int get_encode_fn(EncodeTiledFn* out) {
+    static EncodeTiledFn fn = nullptr;  // immutable once set; a race only repeats the lookup
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        KDW_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres));
+        if (qres != cudaDriverEntryPointSuccess || !p) {
+            set_error("cuTensorMapEncodeTiled is not available from this driver");
+            return (int)cudaErrorNotSupported;
+        }
+        fn = (EncodeTiledFn)p;
+    }
+    *out = fn;
+    return 0;
+}
+
+int encode_volume_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
+                      int64_t strideN, int64_t strideH, int64_t strideW, int boxC, int boxD, int boxW) {
+    EncodeTiledFn fn;
+    int rc = get_encode_fn(&fn);
+    if (rc) return rc;
+    if (((uintptr_t)base & 15) != 0 || (C % 8) != 0 || (strideW % 8) != 0 || (strideH % 8) != 0 ||
+        (strideN % 8) != 0) {
+        set_error("TMA path needs 16-byte aligned base and strides (C, strideW, strideH, strideN multiples of 8)");
+        return KDW_ERR_ALIGN;
+    }
+    if (boxC < 8 || boxC > 256 || boxD < 1 || boxD > 256 || boxW < 1 || boxW > 256) {
+        set_error("tensor-map box out of range");
+        return KDW_ERR_ARG;
+    }
+    const cuuint64_t dims[5] = {(cuuint64_t)C, (cuuint64_t)D, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+    // byte strides of dims 1..4; a dimension of extent 1 still needs a legal (multiple of 16) stride
+    cuuint64_t strides[4] = {(cuuint64_t)C * 2, (cuuint64_t)strideW * 2, (cuuint64_t)strideH * 2,
+                             (cuuint64_t)strideN * 2};
+    for (int i = 0; i < 4; ++i)
+        if (strides[i] == 0) strides[i] = 16;
+    const cuuint32_t box[5] = {(cuuint32_t)boxC, (cuuint32_t)boxD, (cuuint32_t)boxW, 1, 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with CUresult %d (dims C=%lld D=%lld W=%lld H=%lld N=%lld)", (int)r,
+                  (long long)C, (long long)D, (long long)W, (long long)H, (long long)N);
+        return (int)r;
+    }
+    return 0;
+}
+
+int make_sched(Sched* s, int64_t N, int64_t C, int64_t W, int64_t D, int h_begin, int h_end, int WT, int DT, int CS,
+               int grid_target) {
+    s->WT = WT;
+    s->DT = DT;
+    s->CS = CS;
+    s->nWT = (int)((W + WT - 1) / WT);
+    s->nDT = (int)((D + DT - 1) / DT);
+    s->nCS = (int)(C / CS);
+    s->Kc = s->nWT * s->nDT * s->nCS;
+    s->Hr = h_end - h_begin;
+    s->h_begin = h_begin;
+    s->total = (long long)N * s->Kc * s->Hr;
+    long long grid = grid_target;
+    if (grid > s->total) grid = s->total;
+    if (grid < 1) grid = 1;
+    // planes per CTA; chunk the h range so that one chunk of all columns ~ a whole number of CTA shares
+    const double ppc = (double)s->total / (double)grid;
+    long long nh = (long long)((double)s->Hr / ppc + 0.5);
+    if (nh < 1) nh = 1;
+    if (nh > s->Hr) nh = s->Hr;
+    s->PH = (int)((s->Hr + nh - 1) / nh);
+    s->nh = (s->Hr + s->PH - 1) / s->PH;
+    return (int)grid;
+}
+
+}  // namespace kdw
+
+extern "C" {
+
+int kdw_version(void) { return 100; }
+
+const char* kdw_last_error(void) { return kdw::g_err; }
+
+int kdw_device_status(int* status) {
+    if (!status) {
+        kdw::set_error("kdw_device_status: status is NULL");
+        return KDW_ERR_ARG;
+    }
+    KDW_CUDA(cudaDeviceSynchronize());
+    int v = 0;
+    KDW_CUDA(cudaMemcpyFromSymbol(&v, kdw::g_status_word, sizeof(int)));
+    if (v != 0) {
+        const int zero = 0;
+        KDW_CUDA(cudaMemcpyToSymbol(kdw::g_status_word, &zero, sizeof(int)));
+    }
+    *status = v;
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,4 @@
+from .dwconv import DWConv
+from .dwconv_wgrad import DWConvWGRAD
+
+__all__ = ['DWConv', 'DWConvWGRAD']

@@ -1,0 +1,83 @@
+"""Argument marshalling between torch tensors and the C-ABI (include/kdw.h)."""
+import ctypes
+import os
+
+import torch
+
+from ... import _lib
+
+ACC_TYPES = {'float32': 0, 'float16': 1}
+
+
+def _stream_ptr(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _env_tune(name):
+    v = os.environ.get(name)
+    return int(v) if v else 0
+
+
+def volume_strides(t):
+    """(strideN, strideH, strideW) in elements of a channels_last_3d (N, C, H, W, D) tensor."""
+    sN, sC, sH, sW, sD = t.stride()
+    C = t.shape[1]
+    # channels innermost, D next: the only layout the kernels address
+    assert sC == 1 or C == 1, 'channel stride must be 1 (channels_last_3d)'
+    assert sD == C or t.shape[4] == 1, 'stride of the innermost spatial axis must equal C (channels_last_3d)'
+    return sN, sH, sW
+
+
+def fprop(x, weight, y, h_begin=None, h_end=None, y_h0=0, acc='float32', tune=0):
+    """Enqueues y[:, :, h - y_h0] = conv(x)[h] for h in [h_begin, h_end) on x's device / current stream."""
+    lib = _lib.load()
+    N, C, Hx, W, D = x.shape
+    Hy = y.shape[2]
+    if h_begin is None:
+        h_begin, h_end = 0, Hx
+    xs = volume_strides(x)
+    ys = volume_strides(y)
+    tune = tune or _env_tune('KDW_FPROP_TUNE')
+    with torch.cuda.device(x.device):
+        rc = lib.kdw_fprop_f16_range(
+            x.data_ptr(), weight.data_ptr(), y.data_ptr(), N, C, Hx, W, D, xs[0], xs[1], xs[2], Hy, ys[0], ys[1],
+            ys[2], h_begin, h_end, y_h0, ACC_TYPES[acc], tune, _stream_ptr(x.device),
+        )
+    _lib.check(rc)
+    return y
+
+
+def wgrad_workspace(x):
+    lib = _lib.load()
+    N, C, H, W, D = x.shape
+    with torch.cuda.device(x.device):
+        nbytes = lib.kdw_wgrad_workspace_bytes(N, C, H, W, D)
+    if nbytes < 0:
+        _lib.check(int(nbytes))
+    return torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+
+
+def wgrad(x, grad, h_begin=None, h_end=None, g_h0=0, want_f32=False, want_f16=True, tune=0, workspace=None):
+    """Enqueues the weight gradient over grad planes [h_begin, h_end) (x plane numbering).
+
+    Returns (dw_f32 or None, dw_f16 or None), each [3, 3, 3, C]."""
+    lib = _lib.load()
+    N, C, Hx, W, D = x.shape
+    Hg = grad.shape[2]
+    if h_begin is None:
+        h_begin, h_end = 0, Hx
+    xs = volume_strides(x)
+    gs = volume_strides(grad)
+    ws = workspace if workspace is not None else wgrad_workspace(x)
+    dw32 = torch.empty([3, 3, 3, C], dtype=torch.float32, device=x.device) if want_f32 else None
+    dw16 = torch.empty([3, 3, 3, C], dtype=torch.float16, device=x.device) if want_f16 else None
+    tune = tune or _env_tune('KDW_WGRAD_TUNE')
+    with torch.cuda.device(x.device):
+        rc = lib.kdw_wgrad_f16_range(
+            x.data_ptr(), grad.data_ptr(), ws.data_ptr(), ws.numel(),
+            dw32.data_ptr() if want_f32 else None, dw16.data_ptr() if want_f16 else None,
+            N, C, Hx, W, D, xs[0], xs[1], xs[2], Hg, gs[0], gs[1], gs[2], h_begin, h_end, g_h0, tune,
+            _stream_ptr(x.device),
+        )
+    _lib.check(rc)
+    return dw32, dw16

@@ -1,0 +1,205 @@
+// CPU emulation of the TMA kernels, used only by the CPU test-suite.
+//
+// It runs the SAME host scheduler (make_sched), segment decoding (decode_segment / StepIter), thread
+// mapping (FThread / WThread) and per-thread step functions (fprop_step / wgrad_step) as the CUDA
+// kernels, one emulated thread after the other, and replaces only the hardware plumbing: a tiled TMA
+// load becomes a box copy with zero fill, a TMA store a clipped box copy, the block reduction of the
+// weight-gradient kernel a plain loop.  It lets the index arithmetic of every kernel variant be
+// checked against the oracle on a machine without a GPU.
+#include <string.h>
+
+#include <vector>
+
+#include "../../kerops_b200/csrc/fprop_core.cuh"
+#include "../../kerops_b200/csrc/kdw_common.cuh"
+#include "../../kerops_b200/csrc/wgrad_core.cuh"
+
+using namespace kdw;
+
+struct Vol {
+    int64_t N, C, H, W, D, sN, sH, sW;
+};
+
+// box (CS, BD, BW) at (c0, d0, w0) of plane h of sample n; zero outside the volume
+static void emu_tma_load(__half* dst, const __half* src, const Vol& v, int CS, int BD, int BW, int c0, int d0, int w0,
+                         int h, int n) {
+    for (int wj = 0; wj < BW; ++wj)
+        for (int dd = 0; dd < BD; ++dd)
+            for (int c = 0; c < CS; ++c) {
+                const int w = w0 + wj, d = d0 + dd, ch = c0 + c;
+                const bool in = h >= 0 && h < v.H && w >= 0 && w < v.W && d >= 0 && d < v.D && ch < v.C && n < v.N;
+                dst[(wj * BD + dd) * CS + c] =
+                    in ? src[n * v.sN + (int64_t)h * v.sH + (int64_t)w * v.sW + (int64_t)d * v.C + ch]
+                       : __float2half(0.f);
+            }
+}
+static void emu_tma_store(__half* dst, const __half* tile, const Vol& v, int CS, int BD, int BW, int c0, int d0, int w0,
+                          int h, int n) {
+    for (int wj = 0; wj < BW; ++wj)
+        for (int dd = 0; dd < BD; ++dd)
+            for (int c = 0; c < CS; ++c) {
+                const int w = w0 + wj, d = d0 + dd, ch = c0 + c;
+                const bool in = h >= 0 && h < v.H && w >= 0 && w < v.W && d >= 0 && d < v.D && ch < v.C && n < v.N;
+                if (in) dst[n * v.sN + (int64_t)h * v.sH + (int64_t)w * v.sW + (int64_t)d * v.C + ch] = tile[(wj * BD + dd) * CS + c];
+            }
+}
+
+template <class Cfg, bool ACC16>
+static int emu_fprop_cfg(const __half* x, const __half* w, __half* y, Vol vx, Vol vy, int h_begin, int h_end, int y_h0,
+                         int grid_target) {
+    constexpr int M = Cfg::M, CP = Cfg::CP;
+    struct TState {
+        __half2 wgt[27][CP];
+        float2 A[M][CP];
+        __half2 A16[M][CP];
+        __half2 P0[M][CP];
+    };
+    Sched s;
+    const int grid = make_sched(&s, vx.N, vx.C, vx.W, vx.D, h_begin, h_end, Cfg::WT, Cfg::DT, Cfg::CS, grid_target);
+    std::vector<__half> stage(Cfg::IN_BYTES / 2), out(Cfg::OUT_BYTES / 2);
+    std::vector<TState> ts(Cfg::NT);
+    for (int blk = 0; blk < grid; ++blk) {
+        const long long lo = (long long)blk * s.total / grid, hi = (long long)(blk + 1) * s.total / grid;
+        memset(ts.data(), 0, sizeof(TState) * ts.size());
+        StepIter cons;
+        cons.init(s, lo, hi);
+        while (cons.active) {
+            const int q = cons.q;
+            const Seg& g = cons.g;
+            emu_tma_load(stage.data(), x, vx, Cfg::CS, Cfg::DT + 2, Cfg::WT + 2, g.c0, g.d0 - 1, g.w0 - 1, q, g.n);
+            const int am = cons.amask();
+            for (int tid = 0; tid < Cfg::NT; ++tid) {
+                TState& t = ts[tid];
+                const FThread<Cfg> th(tid);
+                if (q == g.hb - 1) {
+                    const __half* wp = w + g.c0 + th.cg * 2 * CP;
+                    for (int k = 0; k < 27; ++k)
+                        for (int i = 0; i < CP; ++i) t.wgt[k][i] = *reinterpret_cast<const __half2*>(wp + (size_t)k * vx.C + 2 * i);
+                }
+                const __half* in = stage.data() + th.in_off;
+                __half* ob = out.data() + th.out_off;
+                switch (am) {
+                    case 1: fprop_step<Cfg, ACC16, 1>(in, ob, t.wgt, t.A, t.A16, t.P0); break;
+                    case 2: fprop_step<Cfg, ACC16, 2>(in, ob, t.wgt, t.A, t.A16, t.P0); break;
+                    case 3: fprop_step<Cfg, ACC16, 3>(in, ob, t.wgt, t.A, t.A16, t.P0); break;
+                    case 4: fprop_step<Cfg, ACC16, 4>(in, ob, t.wgt, t.A, t.A16, t.P0); break;
+                    case 6: fprop_step<Cfg, ACC16, 6>(in, ob, t.wgt, t.A, t.A16, t.P0); break;
+                    case 7: fprop_step<Cfg, ACC16, 7>(in, ob, t.wgt, t.A, t.A16, t.P0); break;
+                    default: return -100 - am;
+                }
+            }
+            if (am & 4) emu_tma_store(y, out.data(), vy, Cfg::CS, Cfg::DT, Cfg::WT, g.c0, g.d0, g.w0, q - 1 - y_h0, g.n);
+            cons.next(s);
+        }
+    }
+    return grid;
+}
+
+template <class Cfg>
+static int emu_wgrad_cfg(const __half* x, const __half* gr, float* dw, Vol vx, Vol vg, int h_begin, int h_end, int g_h0,
+                         int grid_target) {
+    constexpr int M = Cfg::M, CP = Cfg::CP, CS = Cfg::CS;
+    struct TState {
+        __half2 G[3][M][CP];
+        float2 acc[27][CP];
+    };
+    Sched s;
+    const int grid = make_sched(&s, vx.N, vx.C, vx.W, vx.D, h_begin, h_end, Cfg::WT, Cfg::DT, Cfg::CS, grid_target);
+    const int KC = 27 * (int)vx.C;
+    std::vector<float> rows((size_t)grid * KC, 0.f);
+    std::vector<__half> xs(Cfg::X_BYTES / 2), gs(Cfg::G_BYTES / 2);
+    std::vector<TState> ts(Cfg::NT);
+    for (int blk = 0; blk < grid; ++blk) {
+        const long long lo = (long long)blk * s.total / grid, hi = (long long)(blk + 1) * s.total / grid;
+        memset(ts.data(), 0, sizeof(TState) * ts.size());
+        float* row = rows.data() + (size_t)blk * KC;
+        StepIter cons;
+        cons.init(s, lo, hi);
+        while (cons.active) {
+            const int q = cons.q;
+            const Seg& g = cons.g;
+            emu_tma_load(xs.data(), x, vx, CS, Cfg::DT + 2, Cfg::WT + 2, g.c0, g.d0 - 1, g.w0 - 1, q, g.n);
+            const bool with_g = q + 1 < g.he;
+            if (with_g)
+                emu_tma_load(gs.data(), gr, vg, CS, Cfg::DT, Cfg::WT, g.c0, g.d0, g.w0, q + 1 - g_h0, g.n);
+            else
+                for (auto& e : gs) e = __float2half(12345.f);  // stale data must never be used
+            const int am = cons.amask();
+            for (int tid = 0; tid < Cfg::NT; ++tid) {
+                TState& t = ts[tid];
+                const WThread<Cfg> th(tid);
+                const __half* xin = xs.data() + th.x_off;
+                const __half* gin = gs.data() + th.g_off;
+                switch (am) {
+                    case 1: wgrad_step<Cfg, 1>(xin, gin, t.G, t.acc); break;
+                    case 2: wgrad_step<Cfg, 2>(xin, gin, t.G, t.acc); break;
+                    case 3: wgrad_step<Cfg, 3>(xin, gin, t.G, t.acc); break;
+                    case 4: wgrad_step<Cfg, 4>(xin, gin, t.G, t.acc); break;
+                    case 6: wgrad_step<Cfg, 6>(xin, gin, t.G, t.acc); break;
+                    case 7: wgrad_step<Cfg, 7>(xin, gin, t.G, t.acc); break;
+                    default: return -100 - am;
+                }
+            }
+            if (q == g.he) {
+                for (int tid = 0; tid < Cfg::NT; ++tid) {
+                    const WThread<Cfg> th(tid);
+                    for (int k = 0; k < 27; ++k)
+                        for (int i = 0; i < CP; ++i) {
+                            row[k * vx.C + g.c0 + th.cg * 2 * CP + 2 * i] += ts[tid].acc[k][i].x;
+                            row[k * vx.C + g.c0 + th.cg * 2 * CP + 2 * i + 1] += ts[tid].acc[k][i].y;
+                            ts[tid].acc[k][i] = make_float2(0.f, 0.f);
+                        }
+                }
+            }
+            cons.next(s);
+        }
+    }
+    for (int k = 0; k < KC; ++k) {
+        float a = 0.f;
+        for (int r = 0; r < grid; ++r) a += rows[(size_t)r * KC + k];
+        dw[k] = a;
+    }
+    return grid;
+}
+
+#define EMU_FV(ID, CS, DT, WT, M, CP, ST, MINB)                                                                       \
+    case ID:                                                                                                          \
+        return acc16 ? emu_fprop_cfg<FCfg<CS, DT, WT, M, CP, ST, MINB>, true>((const __half*)x, (const __half*)w,      \
+                                                                             (__half*)y, vx, vy, h_begin, h_end, y_h0, \
+                                                                             grid)                                    \
+                     : emu_fprop_cfg<FCfg<CS, DT, WT, M, CP, ST, MINB>, false>((const __half*)x, (const __half*)w,     \
+                                                                              (__half*)y, vx, vy, h_begin, h_end,     \
+                                                                              y_h0, grid);
+#define EMU_WV(ID, CS, DT, WT, M, CP, ST, MINB)                                                                  \
+    case ID:                                                                                                     \
+        return emu_wgrad_cfg<WCfg<CS, DT, WT, M, CP, ST, MINB>>((const __half*)x, (const __half*)g, dw, vx, vg,  \
+                                                                h_begin, h_end, g_h0, grid);
+
+extern "C" {
+
+// Returns the emulated grid size (> 0) or a negative error.  Volumes are dense channels-last.
+int emu_fprop(int variant, const void* x, const void* w, void* y, int64_t N, int64_t C, int64_t Hx, int64_t W,
+              int64_t D, int64_t Hy, int h_begin, int h_end, int y_h0, int acc16, int grid) {
+    const Vol vx{N, C, Hx, W, D, Hx * W * D * C, W * D * C, D * C};
+    const Vol vy{N, C, Hy, W, D, Hy * W * D * C, W * D * C, D * C};
+    switch (variant) {
+#define KDW_VARIANT EMU_FV
+#include "../../kerops_b200/csrc/fprop_variants.inc"
+#undef KDW_VARIANT
+    }
+    return -1;
+}
+
+int emu_wgrad(int variant, const void* x, const void* g, float* dw, int64_t N, int64_t C, int64_t Hx, int64_t W,
+              int64_t D, int64_t Hg, int h_begin, int h_end, int g_h0, int grid) {
+    const Vol vx{N, C, Hx, W, D, Hx * W * D * C, W * D * C, D * C};
+    const Vol vg{N, C, Hg, W, D, Hg * W * D * C, W * D * C, D * C};
+    switch (variant) {
+#define KDW_VARIANT EMU_WV
+#include "../../kerops_b200/csrc/wgrad_variants.inc"
+#undef KDW_VARIANT
+    }
+    return -1;
+}
+
+}  // extern "C"
