@@ -1,0 +1,471 @@
+#!/usr/bin/env python
+"""Benchmark of the depthwise 3x3x3 channels-last fp16 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--channels 8,16,...]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A STEP is one pass over the headline sweep: for every C in {8, 16, 32, 64, 128}, DWConv of a
+(1, C, 350, 350, 128) fp16 channels_last_3d volume followed by DWConvWGRAD of the same volume against
+an independent gradient (seeded synthetic N(0,1) data, weights U(+-1/sqrt(27))).  With N GPUs every rank
+runs the sweep on its own sample (weak scaling) and the fp32 [27][C] weight gradients are summed with
+one NCCL all-reduce per C - the only exchange the sample-sharded path has.
+
+`value` = algorithmic bytes of all ranks / max-over-ranks device time; algorithmic bytes are 4*V*C per
+operator call (read x + write y, or read x + read grad; V = 350*350*128 voxels).
+The JSON line also carries: `roofline` (the kernel with the largest share of the timed region, bytes /
+CUDA-event time against the measured HBM peak), `detail` (per operator and C: ms, GB/s, fraction),
+`e2e` (the same sweep through the host-buffer operators, host<->device copies inside the timed region),
+`cpu_baseline` (torch CPU depthwise conv3d, the check the reference's tests use, on a bounded sample),
+`clocks` (SM clock and throttle reasons sampled through NVML during the timed region).
+
+`--impl reference` times the CPU arm alone (rank 0 only): torch conv3d(groups=C) forward + weight
+gradient on the host cores, one (1, 8, 350, 350, 128) volume per step.
+"""
+import argparse
+import json
+import math
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SHAPE = (350, 350, 128)  # kerops H, W, D = torch dims 2, 3, 4
+VOX = SHAPE[0] * SHAPE[1] * SHAPE[2]
+ALL_CHANNELS = [8, 16, 32, 64, 128]
+FALLBACK_HBM_GBS = 6650.0
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
+# profiles/ (bytes; None where no capture has been taken).
+NCU_TRAFFIC = {'fprop': None, 'wgrad': None}
+
+
+def set_planes(h):
+    global SHAPE, VOX
+    SHAPE = (h, SHAPE[1], SHAPE[2])
+    VOX = SHAPE[0] * SHAPE[1] * SHAPE[2]
+
+
+def algorithmic_bytes(C, n_samples=1):
+    return 4 * VOX * C * n_samples
+
+
+def measured_peak():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    try:
+        with open(path) as f:
+            return float(json.load(f)['hbm_gbs']), 'measured'
+    except Exception:
+        return FALLBACK_HBM_GBS, 'fallback'
+
+
+# ----------------------------------------------------------------------------------------------------
+# clocks through NVML (read-only)
+# ----------------------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x4: 'sw_power_cap', 0x8: 'hw_slowdown', 0x20: 'sw_thermal_slowdown', 0x40: 'hw_thermal_slowdown',
+               0x80: 'hw_power_brake_slowdown', 0x2: 'applications_clocks_setting', 0x10: 'sync_boost'}
+
+    def __init__(self, torch_device):
+        self.samples, self.reasons, self.err = [], set(), None
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            import torch
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            props = torch.cuda.get_device_properties(torch_device)
+            handle = None
+            uuid = getattr(props, 'uuid', None)
+            if uuid is not None:
+                try:
+                    handle = pynvml.nvmlDeviceGetHandleByUUID(('GPU-' + str(uuid)).encode())
+                except Exception:
+                    handle = None
+            if handle is None:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(torch_device.index or 0)
+            self.h = handle
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # no NVML: report it instead of failing the benchmark
+            self.err = f'{type(e).__name__}: {e}'
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception as e:
+                self.err = f'{type(e).__name__}: {e}'
+                return
+            time.sleep(0.004)
+
+    def start(self):
+        if self.err is None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        out = {'sm_mhz': statistics.median(self.samples) if self.samples else None, 'sm_max_mhz': self.max_mhz,
+               'reasons': sorted(self.reasons), 'samples': len(self.samples)}
+        if self.err:
+            out['error'] = self.err
+        return out
+
+
+# ----------------------------------------------------------------------------------------------------
+# CPU arm: torch depthwise conv3d on the host cores (the reference tests' own check, test_conv.py:25,60-72)
+# ----------------------------------------------------------------------------------------------------
+def make_cpu_inputs(C, seed=0):
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    H, W, D = SHAPE
+    x = torch.randn(1, H, W, D, C, generator=g, dtype=torch.float32).to(torch.float16).permute(0, 4, 1, 2, 3)
+    grad = torch.randn(1, H, W, D, C, generator=g, dtype=torch.float32).to(torch.float16).permute(0, 4, 1, 2, 3)
+    w = ((torch.rand(3, 3, 3, C, generator=g) * 2 - 1) / math.sqrt(27)).to(torch.float16)
+    return x, grad, w
+
+
+def cpu_step(x, grad, w, dtype):
+    """fprop + weight gradient of one volume with torch on the CPU; returns (y, dw)."""
+    import torch
+    import torch.nn.functional as F
+    from oracle import torch_oracle
+
+    C = x.shape[1]
+    wt = torch_oracle.to_torch_weight(w).to(dtype).requires_grad_(True)
+    y = F.conv3d(x.to(dtype), wt, None, stride=1, padding=1, groups=C)
+    y.backward(grad.to(dtype))
+    return y.detach().to(torch.float16), wt.grad
+
+
+def time_cpu_arm(C, steps, warmup):
+    """Seconds per step (median) of the faster of the fp32 / fp16 torch CPU paths, and its name."""
+    import torch
+
+    x, grad, w = make_cpu_inputs(C)
+    best = None
+    for dtype in (torch.float32, torch.float16):
+        try:
+            for _ in range(warmup):
+                cpu_step(x, grad, w, dtype)
+            ts = []
+            for _ in range(steps):
+                t0 = time.perf_counter()
+                cpu_step(x, grad, w, dtype)
+                ts.append(time.perf_counter() - t0)
+            med = statistics.median(ts)
+            if best is None or med < best[0]:
+                best = (med, str(dtype).replace('torch.', ''), sum(ts))
+        except Exception:
+            continue
+    if best is None:
+        raise RuntimeError('torch CPU conv3d failed in both fp32 and fp16')
+    return best
+
+
+def run_reference(args):
+    import torch
+
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    C = 8
+    cores = torch.get_num_threads()
+    med, dtype, _ = time_cpu_arm(C, args.steps, max(1, args.warmup))
+    nbytes = 2 * algorithmic_bytes(C)
+    value = nbytes / med / 1e9
+    sample = f'one (1,{C},350,350,128) volume per step: conv3d(groups=C) forward + weight gradient, torch CPU {dtype}'
+    line = {
+        'impl': 'reference', 'metric': METRIC, 'value': value, 'unit': 'GB/s', 'n_gpus': args.gpus,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': med * 1e3, 'higher_is_better': True,
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': dtype, 'data': 'synthetic',
+        'config': {'workload': f'DWConv + DWConvWGRAD on (1,{C},350,350,128) fp16 channels_last_3d, host cores'},
+        'cpu_baseline': {'value': value, 'unit': 'GB/s', 'cores': cores, 'kind': 'port', 'sample': sample},
+        'e2e': {'value': value, 'unit': 'GB/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+METRIC = 'DWConv + DWConvWGRAD algorithmic HBM GB/s at (1,C,350,350,128) fp16 channels_last_3d'
+
+
+# ----------------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------------
+def make_gpu_inputs(C, device, seed):
+    import torch
+
+    g = torch.Generator(device=device).manual_seed(seed)
+    H, W, D = SHAPE
+    x = torch.randn(1, H, W, D, C, generator=g, device=device, dtype=torch.float16).permute(0, 4, 1, 2, 3)
+    grad = torch.randn(1, H, W, D, C, generator=g, device=device, dtype=torch.float16).permute(0, 4, 1, 2, 3)
+    w = ((torch.rand(3, 3, 3, C, generator=g, device=device) * 2 - 1) / math.sqrt(27)).to(torch.float16)
+    return x, grad, w
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from kerops_b200 import _lib
+    from kerops_b200.ops.conv import DWConv, _launch
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f'--gpus {args.gpus} but WORLD_SIZE={world}')
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a CUDA device: kerops_b200 has no CPU path')
+    dev = torch.device('cuda', local)
+    torch.cuda.set_device(dev)
+    _lib.load()
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+
+    channels = args.channels
+    data = {C: make_gpu_inputs(C, dev, seed=1000 * rank + C) for C in channels}
+    ws = {C: _launch.wgrad_workspace(data[C][0]) for C in channels}
+
+    def step(events=None):
+        for C in channels:
+            x, grad, w = data[C]
+            if events is not None:
+                e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+                e0.record()
+            y = DWConv(x, w)
+            if events is not None:
+                e1.record()
+            dw32, dw16 = _launch.wgrad(x, grad, want_f32=True, want_f16=(world == 1), workspace=ws[C])
+            if events is not None:
+                e2.record()
+                events.append((C, e0, e1, e2))
+            if world > 1:
+                dist.all_reduce(dw32)
+            del y
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(dev)
+    sampler.start()
+    events = []
+    t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for _ in range(args.steps):
+        step(events)
+    t_end.record()
+    barrier()
+    clocks = sampler.stop()
+    total_ms = t_start.elapsed_time(t_end)
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    status = _lib.device_status()
+
+    peak, peak_kind = measured_peak()
+    detail = {'fprop': {}, 'wgrad': {}}
+    tot = {'fprop': [0.0, 0.0], 'wgrad': [0.0, 0.0]}  # ms, bytes
+    for C in channels:
+        f_ms = statistics.mean(e0.elapsed_time(e1) for (c, e0, e1, e2) in events if c == C)
+        w_ms = statistics.mean(e1.elapsed_time(e2) for (c, e0, e1, e2) in events if c == C)
+        for kind, ms in (('fprop', f_ms), ('wgrad', w_ms)):
+            gbs = algorithmic_bytes(C) / (ms * 1e-3) / 1e9
+            detail[kind][str(C)] = {'ms': round(ms, 4), 'gbs': round(gbs, 1), 'frac': round(gbs / peak, 4)}
+            tot[kind][0] += ms
+            tot[kind][1] += algorithmic_bytes(C)
+    # torch.clone of the same tensors, the comparator the reference's README uses
+    clone = {}
+    for C in channels:
+        x = data[C][0]
+        for _ in range(2):
+            x.clone()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            x.clone()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 5
+        clone[str(C)] = {'ms': round(ms, 4), 'gbs': round(algorithmic_bytes(C) / (ms * 1e-3) / 1e9, 1)}
+    detail['clone'] = clone
+
+    def roof(kind):
+        ms, nbytes = tot[kind]
+        ach = nbytes / (ms * 1e-3) / 1e9
+        traffic = NCU_TRAFFIC.get(kind)
+        return {'bound': 'hbm', 'kernel': kind, 'achieved': round(ach, 1), 'peak': peak, 'peak_kind': peak_kind,
+                'unit': 'GB/s', 'frac': round(ach / peak, 4), 'traffic': traffic,
+                'avg_launch_ms': round(ms / len(channels), 4)}
+
+    dominant = 'wgrad' if tot['wgrad'][0] >= tot['fprop'][0] else 'fprop'
+    step_bytes = sum(2 * algorithmic_bytes(C) for C in channels) * world
+    value = step_bytes * args.steps / (total_ms * 1e-3) / 1e9
+
+    e2e = measure_e2e(args, channels, dev, world, rank)
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cores = torch.get_num_threads()
+        med, dtype, spent = time_cpu_arm(8, steps=2, warmup=1)
+        cpu_baseline = {
+            'value': round(2 * algorithmic_bytes(8) / med / 1e9, 3), 'unit': 'GB/s', 'cores': cores, 'kind': 'port',
+            'sample': f'(1,8,350,350,128) only: torch CPU conv3d(groups=8) forward + weight gradient in {dtype}, '
+                      f'median of 2 steps after 1 warm-up ({spent:.1f} s of CPU work)',
+        }
+    triton_ref = measure_triton_reference(channels, data, dev) if (args.compare_triton and rank == 0) else None
+
+    if rank == 0:
+        line = {
+            'metric': METRIC, 'value': round(value, 1), 'unit': 'GB/s', 'n_gpus': world, 'steps': args.steps,
+            'warmup': args.warmup, 'ms_per_step': round(total_ms / args.steps, 4), 'higher_is_better': True,
+            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f16 products, f32 accumulation', 'data': 'synthetic',
+            'config': {
+                'workload': f'configs[1]+[2]: DWConv then DWConvWGRAD on (1,C,{SHAPE[0]},350,128) fp16 channels_last_3d for C in '
+                            + ','.join(map(str, channels)) + '; one sample per GPU',
+                'l2': 'inputs larger than L2 (smallest tensor 251 MB; 31 GB touched per step)',
+                'parallelism': f'dp{world}' if world > 1 else 'single',
+            },
+            'roofline': roof(dominant), 'roofline_fprop': roof('fprop'), 'roofline_wgrad': roof('wgrad'),
+            'cpu_baseline': cpu_baseline, 'e2e': e2e, 'clocks': clocks,
+            'gpu_launches': 3 * len(channels) * args.steps, 'detail': detail, 'device_status': status,
+        }
+        if triton_ref is not None:
+            line['reference_triton_on_this_gpu'] = triton_ref
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def measure_e2e(args, channels, dev, world, rank):
+    """The same sweep through the host-buffer operators: pinned host inputs, host outputs."""
+    import torch
+    import torch.distributed as dist
+
+    from kerops_b200.host import DWConvHost, DWConvWGRADHost
+
+    if args.no_e2e:
+        return None
+    Cmax = max(channels)
+    H, W, D = SHAPE
+    # one pinned pool, sliced per C (contents: N(0,1) generated on the device once)
+    pool = [torch.empty(VOX * Cmax, dtype=torch.float16, pin_memory=True) for _ in range(3)]
+    g = torch.Generator(device=dev).manual_seed(7 + rank)
+    for p in pool[:2]:
+        p.copy_(torch.randn(VOX * Cmax, generator=g, device=dev, dtype=torch.float16))
+    torch.cuda.synchronize()
+
+    def view(p, C):
+        return p[:VOX * C].view(1, H, W, D, C).permute(0, 4, 1, 2, 3)
+
+    wts = {C: ((torch.rand(3, 3, 3, C) * 2 - 1) / math.sqrt(27)).to(torch.float16).pin_memory() for C in channels}
+
+    def step():
+        for C in channels:
+            DWConvHost(view(pool[0], C), wts[C], out=view(pool[2], C), device=dev)
+            DWConvWGRADHost(view(pool[0], C), view(pool[1], C), device=dev)
+
+    n = max(1, min(args.steps, 3))
+    step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(n):
+        step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([dt], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+    h2d = sum(3 * 2 * VOX * C + 54 * C for C in channels)  # x for fprop; x and grad for wgrad; weights
+    d2h = sum(2 * VOX * C + 54 * C for C in channels)      # y; dw
+    nbytes = sum(2 * algorithmic_bytes(C) for C in channels) * world
+    return {'value': round(nbytes * n / dt / 1e9, 2), 'unit': 'GB/s', 'h2d_bytes_per_step': h2d,
+            'd2h_bytes_per_step': d2h, 'steps': n, 'ms_per_step': round(dt / n * 1e3, 2),
+            'api': 'kerops_b200.host.DWConvHost / DWConvWGRADHost (pinned host buffers, slab pipeline)'}
+
+
+def measure_triton_reference(channels, data, dev):
+    """Optional comparator: the unmodified reference Triton kernels (installed under baseline/_ref) on this GPU."""
+    import torch
+
+    ref_root = os.path.join(ROOT, 'baseline', '_ref')
+    if not os.path.isdir(os.path.join(ref_root, 'kerops')):
+        return {'unavailable': 'baseline/_ref/kerops not present'}
+    sys.path.insert(0, ref_root)
+    try:
+        from kerops.ops.conv import DWConv as RefDWConv, DWConvWGRAD as RefDWConvWGRAD
+    except Exception as e:
+        return {'unavailable': f'{type(e).__name__}: {e}'}
+    out = {'fprop': {}, 'wgrad': {}}
+    for C in channels:
+        x, grad, w = data[C]
+        for name, fn in (('fprop', lambda: RefDWConv(x, w)), ('wgrad', lambda: RefDWConvWGRAD(x, grad))):
+            try:
+                for _ in range(3):
+                    fn()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(5):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                ms = e0.elapsed_time(e1) / 5
+                out[name][str(C)] = {'ms': round(ms, 4), 'gbs': round(algorithmic_bytes(C) / (ms * 1e-3) / 1e9, 1)}
+            except Exception as e:
+                out[name][str(C)] = {'error': f'{type(e).__name__}: {e}'[:200]}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=10)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--channels', default=','.join(map(str, ALL_CHANNELS)))
+    ap.add_argument('--planes', type=int, default=SHAPE[0],
+                    help='h extent of the volume (default 350); smaller values are for profiler captures only')
+    ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--compare-triton', action='store_true',
+                    help='also time the reference Triton kernels from baseline/_ref on this GPU')
+    args = ap.parse_args()
+    args.channels = [int(c) for c in args.channels.split(',')]
+    set_planes(args.planes)
+    args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
+    if args.impl == 'reference':
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == '__main__':
+    main()
