@@ -33,6 +33,9 @@ extern "C" {
 /* accumulate types, mirror the ACCTYPE keyword of the reference ('float32' | 'float16', dwconv.py:35) */
 #define KDW_ACC_F32 0
 #define KDW_ACC_F16 1
+/* no reference counterpart: fp32 accumulation of per-plane (9-tap) fp16 partial sums; cheaper than
+ * KDW_ACC_F32, less accurate (outside the reference test's two-stage tolerance) */
+#define KDW_ACC_F32_PLANE 2
 
 /* argument errors */
 #define KDW_ERR_ARG (-1)         /* null pointer, non-positive size, bad enum            */
@@ -50,7 +53,7 @@ const char* kdw_last_error(void);
 /*
  * Reads and clears the device-side status word of the CURRENT device (synchronises the device):
  * 0 = ok, 1 = a bounded wait on a TMA barrier ran out inside a kernel (the kernel stopped early and its
- * output is invalid).  No reference counterpart (the reference has no device-side waits).
+ * output is invalid), 2 = a TMA copy with a misaligned shared address or channel coordinate was skipped.  No reference counterpart (the reference has no device-side waits).
  */
 int kdw_device_status(int* status);
 
@@ -59,8 +62,9 @@ int kdw_device_status(int* status);
  * _DWConv_cl3d_impl) by one launch over the whole batch.
  *   x, y      fp16 volumes (N, C, H, W, D), strides in elements; y may have different N/H/W strides
  *   weight    fp16 [3][3][3][C]
- *   acc_type  KDW_ACC_F32: per input plane the 9 taps are summed with packed fp16 FMAs and the three
- *             plane partials are added in fp32;  KDW_ACC_F16: all 27 taps in one fp16 FMA chain
+ *   acc_type  KDW_ACC_F32: the reference's arithmetic - the three d-taps of a row in a packed fp16 FMA chain,
+ *             the nine row sums added in fp32;  KDW_ACC_F16: all 27 taps in one fp16 FMA chain;
+ *             KDW_ACC_F32_PLANE: nine taps per fp16 chain, three plane sums added in fp32
  *   tune      0 = built-in choice for this C; >0 = explicit kernel variant (see kdw_fprop_variants());
  *             takes the place of the num_warps / D_block keywords (dwconv.py:10-17)
  * C must be a power of two.  C >= 8 uses the TMA kernel (x, y 16-byte aligned, strides multiples of 8);

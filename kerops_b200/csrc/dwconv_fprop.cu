@@ -9,9 +9,8 @@
 // (channel pairs, d), M consecutive w positions - applies the plane to the three output planes
 // that use it:
 //     plane q+1 gets the a=0 taps, plane q the a=1 taps, plane q-1 the a=2 taps,
-// each as a 9-term packed-half (HFMA2) chain.  The three 9-tap partials of an output are added in
-// fp32 (mixed-precision add), so per output there are 27 HFMA2/2 + 3 fp32 adds and no index
-// arithmetic in the inner loop.  A finished plane is staged in shared memory and leaves through a
+// with packed-half FMAs (HFMA2) whose partial sums are added in fp32 by the sm_100 mixed-precision add
+// (three accumulate modes, see fprop_step); there is no index arithmetic in the inner loop.  A finished plane is staged in shared memory and leaves through a
 // TMA store (which clips the w/d tails).  Every input plane is read from shared memory exactly
 // once per thread-patch; the weights (27 x channel pairs) live in registers.
 //
@@ -72,7 +71,7 @@ __global__ void __launch_bounds__(256) fprop_plain_kernel(const __half* __restri
 // ------------------------------------------------------------------------------------------------
 // TMA kernel
 // ------------------------------------------------------------------------------------------------
-template <class Cfg, bool ACC16>
+template <class Cfg, int MODE>
 __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
     fprop_tma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
                      const __half* __restrict__ weight, const Sched s, const int C, const int y_h0, int* status) {
@@ -108,7 +107,7 @@ __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
         for (int k = 0; k < ST && prod.active; ++k) {
             const uint32_t bar = bar0 + 8 * (pi % ST);
             mbar_expect_tx(bar, Cfg::IN_BYTES);
-            tma_load_5d(smem_u32(in_base + (pi % ST) * Cfg::IN_STRIDE), &tmx, bar, prod.g.c0, prod.g.d0 - 1,
+            tma_load_5d(status, smem_u32(in_base + (pi % ST) * Cfg::IN_STRIDE), &tmx, bar, prod.g.c0, prod.g.d0 - 1,
                         prod.g.w0 - 1, prod.q, prod.g.n);
             ++pi;
             prod.next(s);
@@ -116,16 +115,14 @@ __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
     }
 
     __half2 wgt[27][CP];
-    float2 A[M][CP];
-    __half2 A16[M][CP];
-    __half2 P0[M][CP];
+    float2 P1[M][CP], P2[M][CP];  // carried fp32 partials (see fprop_step)
+    __half2 H1[M][CP], H2[M][CP];  // carried packed-half partials
 #pragma unroll
     for (int m = 0; m < M; ++m)
 #pragma unroll
         for (int i = 0; i < CP; ++i) {
-            A[m][i] = make_float2(0.f, 0.f);
-            A16[m][i] = __float2half2_rn(0.f);
-            P0[m][i] = __float2half2_rn(0.f);
+            P1[m][i] = P2[m][i] = make_float2(0.f, 0.f);
+            H1[m][i] = H2[m][i] = __float2half2_rn(0.f);
         }
 
     uint32_t ci = 0;  // steps consumed
@@ -147,12 +144,12 @@ __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
         const __half* in = reinterpret_cast<const __half*>(in_base + stage * Cfg::IN_STRIDE) + in_off;
         __half* ob = reinterpret_cast<__half*>(out_base + (oc & 1u) * Cfg::OUT_BYTES) + out_off;
         switch (am) {
-            case 1: fprop_step<Cfg, ACC16, 1>(in, ob, wgt, A, A16, P0); break;
-            case 2: fprop_step<Cfg, ACC16, 2>(in, ob, wgt, A, A16, P0); break;
-            case 3: fprop_step<Cfg, ACC16, 3>(in, ob, wgt, A, A16, P0); break;
-            case 4: fprop_step<Cfg, ACC16, 4>(in, ob, wgt, A, A16, P0); break;
-            case 6: fprop_step<Cfg, ACC16, 6>(in, ob, wgt, A, A16, P0); break;
-            default: fprop_step<Cfg, ACC16, 7>(in, ob, wgt, A, A16, P0); break;
+            case 1: fprop_step<Cfg, MODE, 1>(in, ob, wgt, P1, P2, H1, H2); break;
+            case 2: fprop_step<Cfg, MODE, 2>(in, ob, wgt, P1, P2, H1, H2); break;
+            case 3: fprop_step<Cfg, MODE, 3>(in, ob, wgt, P1, P2, H1, H2); break;
+            case 4: fprop_step<Cfg, MODE, 4>(in, ob, wgt, P1, P2, H1, H2); break;
+            case 6: fprop_step<Cfg, MODE, 6>(in, ob, wgt, P1, P2, H1, H2); break;
+            default: fprop_step<Cfg, MODE, 7>(in, ob, wgt, P1, P2, H1, H2); break;
         }
         if (am & 4) fence_proxy_async_smem();  // the out tile must be visible to the TMA store
         if (tid == 0) tma_wait_read_all();     // the previous store has finished reading the other out tile
@@ -162,14 +159,14 @@ __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
         }
         if (tid == 0) {
             if (am & 4) {
-                tma_store_5d(&tmy, smem_u32(out_base + (oc & 1u) * Cfg::OUT_BYTES), cons.g.c0, cons.g.d0, cons.g.w0,
+                tma_store_5d(status, &tmy, smem_u32(out_base + (oc & 1u) * Cfg::OUT_BYTES), cons.g.c0, cons.g.d0, cons.g.w0,
                              q - 1 - y_h0, cons.g.n);
                 tma_commit();
             }
             if (prod.active) {  // the stage just consumed is free: refill it ST planes ahead
                 const uint32_t bar = bar0 + 8 * (pi % ST);
                 mbar_expect_tx(bar, Cfg::IN_BYTES);
-                tma_load_5d(smem_u32(in_base + (pi % ST) * Cfg::IN_STRIDE), &tmx, bar, prod.g.c0, prod.g.d0 - 1,
+                tma_load_5d(status, smem_u32(in_base + (pi % ST) * Cfg::IN_STRIDE), &tmx, bar, prod.g.c0, prod.g.d0 - 1,
                             prod.g.w0 - 1, prod.q, prod.g.n);
                 ++pi;
                 prod.next(s);
@@ -201,7 +198,7 @@ struct FpropArgs {
     cudaStream_t stream;
 };
 
-template <class Cfg, bool ACC16>
+template <class Cfg, int MODE>
 static int launch_fprop_tma(const FpropArgs& a) {
     CUtensorMap tmx, tmy;
     int rc = encode_volume_map(&tmx, a.x, a.N, a.C, a.Hx, a.W, a.D, a.xsN, a.xsH, a.xsW, Cfg::CS, Cfg::DT + 2,
@@ -213,7 +210,7 @@ static int launch_fprop_tma(const FpropArgs& a) {
         set_error("weight pointer must be 4-byte aligned");
         return KDW_ERR_ALIGN;
     }
-    auto kern = fprop_tma_kernel<Cfg, ACC16>;
+    auto kern = fprop_tma_kernel<Cfg, MODE>;
     KDW_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     int occ = 0, sms = 0;
     KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::NT, Cfg::SMEM));
@@ -236,11 +233,13 @@ static int launch_fprop_tma(const FpropArgs& a) {
 typedef int (*FpropLaunch)(const FpropArgs&);
 struct FpropVariant {
     int cs;
-    FpropLaunch f32, f16;
+    FpropLaunch mode[3];  // indexed by KDW_ACC_*
 };
 #define KDW_VARIANT(ID, CS, DT, WT, M, CP, ST, MINB)                            \
-    {CS, &launch_fprop_tma<FCfg<CS, DT, WT, M, CP, ST, MINB>, false>,           \
-     &launch_fprop_tma<FCfg<CS, DT, WT, M, CP, ST, MINB>, true>},
+    {CS,                                                                        \
+     {&launch_fprop_tma<FCfg<CS, DT, WT, M, CP, ST, MINB>, 0>,                  \
+      &launch_fprop_tma<FCfg<CS, DT, WT, M, CP, ST, MINB>, 1>,                  \
+      &launch_fprop_tma<FCfg<CS, DT, WT, M, CP, ST, MINB>, 2>}},
 // index = id - 1
 static const FpropVariant g_fprop_variants[] = {
 #include "fprop_variants.inc"
@@ -268,8 +267,8 @@ static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N,
                   (long long)N, (long long)C, (long long)Hx, (long long)W, (long long)D);
         return KDW_ERR_ARG;
     }
-    if (acc_type != KDW_ACC_F32 && acc_type != KDW_ACC_F16) {
-        set_error("fprop: acc_type must be KDW_ACC_F32 or KDW_ACC_F16");
+    if (acc_type != KDW_ACC_F32 && acc_type != KDW_ACC_F16 && acc_type != KDW_ACC_F32_PLANE) {
+        set_error("fprop: acc_type must be KDW_ACC_F32, KDW_ACC_F16 or KDW_ACC_F32_PLANE");
         return KDW_ERR_ARG;
     }
     if (Hx > 0x7fffffff || W > 0x7fffffff || D > 0x7fffffff || N > 0x7fffffff || C > 0x7fffffff) {
@@ -298,7 +297,7 @@ static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N,
         fprop_plain_kernel<<<(unsigned)blocks, 256, 0, st>>>((const __half*)x, (const __half*)weight, (__half*)y,
                                                              total, (int)C, (int)Hx, (int)W, (int)D, xsN, xsH, xsW,
                                                              ysN, ysH, ysW, (int)h_begin, (int)(h_end - h_begin),
-                                                             (int)y_h0, acc_type == KDW_ACC_F16);
+                                                             (int)y_h0, acc_type == KDW_ACC_F16);  // the plain kernel has one fp32 mode
         KDW_CUDA(cudaGetLastError());
         return 0;
     }
@@ -309,7 +308,7 @@ static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N,
         return KDW_ERR_TUNE;
     }
     FpropArgs a{x, weight, y, N, C, Hx, W, D, xsN, xsH, xsW, Hy, ysN, ysH, ysW, (int)h_begin, (int)h_end, (int)y_h0, st};
-    return (acc_type == KDW_ACC_F16) ? v.f16(a) : v.f32(a);
+    return v.mode[acc_type](a);
 }
 
 }  // namespace kdw

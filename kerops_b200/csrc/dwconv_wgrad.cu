@@ -114,10 +114,10 @@ __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
         const uint32_t bar = bar0 + 8 * st;
         const bool with_g = prod.q + 1 < prod.g.he;  // grad plane q+1 is owned by the segment
         mbar_expect_tx(bar, Cfg::X_BYTES + (with_g ? Cfg::G_BYTES : 0));
-        tma_load_5d(smem_u32(stage_base + st * Cfg::STAGE), &tmx, bar, prod.g.c0, prod.g.d0 - 1, prod.g.w0 - 1, prod.q,
+        tma_load_5d(status, smem_u32(stage_base + st * Cfg::STAGE), &tmx, bar, prod.g.c0, prod.g.d0 - 1, prod.g.w0 - 1, prod.q,
                     prod.g.n);
         if (with_g)
-            tma_load_5d(smem_u32(stage_base + st * Cfg::STAGE + Cfg::X_STRIDE), &tmg, bar, prod.g.c0, prod.g.d0,
+            tma_load_5d(status, smem_u32(stage_base + st * Cfg::STAGE + Cfg::X_STRIDE), &tmg, bar, prod.g.c0, prod.g.d0,
                         prod.g.w0, prod.q + 1 - g_h0, prod.g.n);
         ++pi;
         prod.next(s);

@@ -22,6 +22,7 @@ namespace kdw {
 enum : int {
     KDW_STATUS_OK = 0,
     KDW_STATUS_TMA_TIMEOUT = 1,  // a bounded mbarrier wait ran out
+    KDW_STATUS_TMA_ARGS = 2,     // a TMA copy with a misaligned shared address or channel coordinate was skipped
 };
 
 // ------------------------------------------------------------------------------------------
@@ -174,16 +175,29 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1, int c2,
-                                            int c3, int c4) {
+// A tiled TMA copy needs a 128-byte aligned shared address and an innermost coordinate that is a
+// multiple of 16 bytes (8 halfs); a copy that breaks either rule raises an illegal-instruction fault.
+__device__ __forceinline__ bool tma_args_ok(uint32_t smem_addr, int c0) { return (smem_addr & 127u) == 0 && (c0 & 7) == 0; }
+
+// The copies below check those two rules first; an offending copy is skipped and reported in *status.
+__device__ __forceinline__ void tma_load_5d(int* status, uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1,
+                                            int c2, int c3, int c4) {
+    if (!tma_args_ok(dst, c0)) {
+        atomicExch(status, (int)KDW_STATUS_TMA_ARGS);
+        return;
+    }
     asm volatile(
         "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
         " [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
         ::"r"(dst), "l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(bar)
         : "memory");
 }
-__device__ __forceinline__ void tma_store_5d(const CUtensorMap* tm, uint32_t src, int c0, int c1, int c2, int c3,
-                                             int c4) {
+__device__ __forceinline__ void tma_store_5d(int* status, const CUtensorMap* tm, uint32_t src, int c0, int c1, int c2,
+                                             int c3, int c4) {
+    if (!tma_args_ok(src, c0)) {
+        atomicExch(status, (int)KDW_STATUS_TMA_ARGS);
+        return;
+    }
     asm volatile(
         "cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%1, %2, %3, %4, %5}], [%6];"
         ::"l"(tm), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(src)

@@ -44,15 +44,14 @@ static void emu_tma_store(__half* dst, const __half* tile, const Vol& v, int CS,
             }
 }
 
-template <class Cfg, bool ACC16>
+template <class Cfg, int MODE>
 static int emu_fprop_cfg(const __half* x, const __half* w, __half* y, Vol vx, Vol vy, int h_begin, int h_end, int y_h0,
                          int grid_target) {
     constexpr int M = Cfg::M, CP = Cfg::CP;
     struct TState {
         __half2 wgt[27][CP];
-        float2 A[M][CP];
-        __half2 A16[M][CP];
-        __half2 P0[M][CP];
+        float2 P1[M][CP], P2[M][CP];
+        __half2 H1[M][CP], H2[M][CP];
     };
     Sched s;
     const int grid = make_sched(&s, vx.N, vx.C, vx.W, vx.D, h_begin, h_end, Cfg::WT, Cfg::DT, Cfg::CS, grid_target);
@@ -79,12 +78,12 @@ static int emu_fprop_cfg(const __half* x, const __half* w, __half* y, Vol vx, Vo
                 const __half* in = stage.data() + th.in_off;
                 __half* ob = out.data() + th.out_off;
                 switch (am) {
-                    case 1: fprop_step<Cfg, ACC16, 1>(in, ob, t.wgt, t.A, t.A16, t.P0); break;
-                    case 2: fprop_step<Cfg, ACC16, 2>(in, ob, t.wgt, t.A, t.A16, t.P0); break;
-                    case 3: fprop_step<Cfg, ACC16, 3>(in, ob, t.wgt, t.A, t.A16, t.P0); break;
-                    case 4: fprop_step<Cfg, ACC16, 4>(in, ob, t.wgt, t.A, t.A16, t.P0); break;
-                    case 6: fprop_step<Cfg, ACC16, 6>(in, ob, t.wgt, t.A, t.A16, t.P0); break;
-                    case 7: fprop_step<Cfg, ACC16, 7>(in, ob, t.wgt, t.A, t.A16, t.P0); break;
+                    case 1: fprop_step<Cfg, MODE, 1>(in, ob, t.wgt, t.P1, t.P2, t.H1, t.H2); break;
+                    case 2: fprop_step<Cfg, MODE, 2>(in, ob, t.wgt, t.P1, t.P2, t.H1, t.H2); break;
+                    case 3: fprop_step<Cfg, MODE, 3>(in, ob, t.wgt, t.P1, t.P2, t.H1, t.H2); break;
+                    case 4: fprop_step<Cfg, MODE, 4>(in, ob, t.wgt, t.P1, t.P2, t.H1, t.H2); break;
+                    case 6: fprop_step<Cfg, MODE, 6>(in, ob, t.wgt, t.P1, t.P2, t.H1, t.H2); break;
+                    case 7: fprop_step<Cfg, MODE, 7>(in, ob, t.wgt, t.P1, t.P2, t.H1, t.H2); break;
                     default: return -100 - am;
                 }
             }
@@ -162,14 +161,14 @@ static int emu_wgrad_cfg(const __half* x, const __half* gr, float* dw, Vol vx, V
     return grid;
 }
 
-#define EMU_FV(ID, CS, DT, WT, M, CP, ST, MINB)                                                                       \
-    case ID:                                                                                                          \
-        return acc16 ? emu_fprop_cfg<FCfg<CS, DT, WT, M, CP, ST, MINB>, true>((const __half*)x, (const __half*)w,      \
-                                                                             (__half*)y, vx, vy, h_begin, h_end, y_h0, \
-                                                                             grid)                                    \
-                     : emu_fprop_cfg<FCfg<CS, DT, WT, M, CP, ST, MINB>, false>((const __half*)x, (const __half*)w,     \
-                                                                              (__half*)y, vx, vy, h_begin, h_end,     \
-                                                                              y_h0, grid);
+#define EMU_FV(ID, CS, DT, WT, M, CP, ST, MINB)                                                                     \
+    case ID: {                                                                                                      \
+        using Cfg = FCfg<CS, DT, WT, M, CP, ST, MINB>;                                                              \
+        const __half *xh = (const __half*)x, *wh = (const __half*)w;                                                \
+        if (mode == 0) return emu_fprop_cfg<Cfg, 0>(xh, wh, (__half*)y, vx, vy, h_begin, h_end, y_h0, grid);        \
+        if (mode == 1) return emu_fprop_cfg<Cfg, 1>(xh, wh, (__half*)y, vx, vy, h_begin, h_end, y_h0, grid);        \
+        return emu_fprop_cfg<Cfg, 2>(xh, wh, (__half*)y, vx, vy, h_begin, h_end, y_h0, grid);                       \
+    }
 #define EMU_WV(ID, CS, DT, WT, M, CP, ST, MINB)                                                                  \
     case ID:                                                                                                     \
         return emu_wgrad_cfg<WCfg<CS, DT, WT, M, CP, ST, MINB>>((const __half*)x, (const __half*)g, dw, vx, vg,  \
@@ -179,7 +178,7 @@ extern "C" {
 
 // Returns the emulated grid size (> 0) or a negative error.  Volumes are dense channels-last.
 int emu_fprop(int variant, const void* x, const void* w, void* y, int64_t N, int64_t C, int64_t Hx, int64_t W,
-              int64_t D, int64_t Hy, int h_begin, int h_end, int y_h0, int acc16, int grid) {
+              int64_t D, int64_t Hy, int h_begin, int h_end, int y_h0, int mode, int grid) {
     const Vol vx{N, C, Hx, W, D, Hx * W * D * C, W * D * C, D * C};
     const Vol vy{N, C, Hy, W, D, Hy * W * D * C, W * D * C, D * C};
     switch (variant) {

@@ -44,13 +44,13 @@ def test_emulated_fprop(kdw_lib, kdw_emu, shape):
     for v, cs in _variants(kdw_lib, 'fprop'):
         if C % cs:
             continue
-        for acc16 in (0, 1):
+        for mode in (0, 1, 2):  # KDW_ACC_F32, KDW_ACC_F16, KDW_ACC_F32_PLANE
             y = np.full_like(x, np.nan)
-            r = kdw_emu.emu_fprop(v, x.ctypes.data, w.ctypes.data, y.ctypes.data, N, C, H, W, D, H, 0, H, 0, acc16, grid)
+            r = kdw_emu.emu_fprop(v, x.ctypes.data, w.ctypes.data, y.ctypes.data, N, C, H, W, D, H, 0, H, 0, mode, grid)
             assert r > 0
             assert np.isfinite(y).all(), f'variant {v}: output not fully written'
-            assert np.allclose(y.astype(np.float32), y_exact, rtol=1e-3, atol=1e-2), f'variant {v} acc16={acc16}'
-            if not acc16:
+            assert np.allclose(y.astype(np.float32), y_exact, rtol=1e-3, atol=1e-2), f'variant {v} mode={mode}'
+            if mode == 0:
                 assert o.allclose_two_stage(y, y_exact, rtol_strict=1e-4, atol_strict=1e-3, rtol_narrow=1e-3,
                                             atol_narrow=2e-3), f'variant {v}'
 

@@ -29,12 +29,12 @@ def make_inputs(seed, N, C, H, W, D, device='cuda'):
     return x, grad, w
 
 
-def check_fprop(y, y_ref, acc16=False):
+def check_fprop(y, y_ref, strict=True):
     assert y.shape == y_ref.shape and y.dtype == torch.float16
     assert torch.isfinite(y).all()
     yf, rf = y.float(), y_ref.float()
     assert torch.allclose(yf, rf, rtol=1e-3, atol=1e-2), f'max abs err {(yf - rf).abs().max().item()}'
-    if not acc16:
+    if strict:  # the reference test's bound; the cheaper accumulate modes only meet the north-star bound
         assert o.allclose_two_stage(y.cpu().numpy(), y_ref.cpu().numpy(), rtol_strict=1e-4, atol_strict=1e-3,
                                     rtol_narrow=1e-3, atol_narrow=2e-3)
 
@@ -150,10 +150,10 @@ def test_all_fprop_variants(ops, kdw_lib):
             for (N, H, W, D) in [(2, 5, 19, 37), (1, 21, 9, 130)]:
                 x, _, w = make_inputs(31 * v + C, N, C, H, W, D)
                 ref = to.fprop_shift_fp32(x, w)
-                for acc in ('float32', 'float16'):
+                for acc in ('float32', 'float16', 'float32_plane'):
                     y = torch.full_like(x, float('nan'))
                     _launch.fprop(x, w, y, acc=acc, tune=v)
-                    check_fprop(y, ref, acc16=(acc == 'float16'))
+                    check_fprop(y, ref, strict=(acc == 'float32'))
 
 
 def test_all_wgrad_variants(ops, kdw_lib):
@@ -170,7 +170,8 @@ def test_all_wgrad_variants(ops, kdw_lib):
 def test_acctype_float16_keyword(ops):
     DWConv, _, _ = ops
     x, _, w = make_inputs(77, 1, 16, 20, 21, 22)
-    check_fprop(DWConv(x, w, ACCTYPE='float16'), to.fprop_shift_fp32(x, w), acc16=True)
+    check_fprop(DWConv(x, w, ACCTYPE='float16'), to.fprop_shift_fp32(x, w), strict=False)
+    check_fprop(DWConv(x, w, ACCTYPE='float32_plane'), to.fprop_shift_fp32(x, w), strict=False)
 
 
 def test_plain_kernels_small_channel_counts(ops):
