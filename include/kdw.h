@@ -33,9 +33,6 @@ extern "C" {
 /* accumulate types, mirror the ACCTYPE keyword of the reference ('float32' | 'float16', dwconv.py:35) */
 #define KDW_ACC_F32 0
 #define KDW_ACC_F16 1
-/* no reference counterpart: fp32 accumulation of per-plane (9-tap) fp16 partial sums; cheaper than
- * KDW_ACC_F32, less accurate (outside the reference test's two-stage tolerance) */
-#define KDW_ACC_F32_PLANE 2
 
 /* argument errors */
 #define KDW_ERR_ARG (-1)         /* null pointer, non-positive size, bad enum            */
@@ -62,9 +59,9 @@ int kdw_device_status(int* status);
  * _DWConv_cl3d_impl) by one launch over the whole batch.
  *   x, y      fp16 volumes (N, C, H, W, D), strides in elements; y may have different N/H/W strides
  *   weight    fp16 [3][3][3][C]
- *   acc_type  KDW_ACC_F32: the reference's arithmetic - the three d-taps of a row in a packed fp16 FMA chain,
- *             the nine row sums added in fp32;  KDW_ACC_F16: all 27 taps in one fp16 FMA chain;
- *             KDW_ACC_F32_PLANE: nine taps per fp16 chain, three plane sums added in fp32
+ *   acc_type  KDW_ACC_F32: exact fp16 x fp16 products accumulated in fp32 (mixed-precision FMA), rounded once to
+ *             fp16 - at least as accurate as the reference's 'float32' mode (fp16 products, fp16 sum of three,
+ *             fp32 sum of nine; kerops/kernels/dw_conv.py:49-52);  KDW_ACC_F16: all 27 taps in fp16 FMA chains
  *   tune      0 = built-in choice for this C; >0 = explicit kernel variant (see kdw_fprop_variants());
  *             takes the place of the num_warps / D_block keywords (dwconv.py:10-17)
  * C must be a power of two.  C >= 8 uses the TMA kernel (x, y 16-byte aligned, strides multiples of 8);

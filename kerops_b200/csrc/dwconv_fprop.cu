@@ -4,15 +4,17 @@
 // (kerops/ops/conv/dwconv.py:42-61).
 //
 // TMA kernel (C multiple of 8).  A CTA owns a column (w-tile x d-tile x channel-slice) and marches
-// along h.  Each step it receives ONE halo'd input plane [(WT+2) x (DT+2) x CS] by a tiled TMA load
-// (zero fill outside the volume = the padding on all three axes), and every thread - fixed
-// (channel pairs, d), M consecutive w positions - applies the plane to the three output planes
-// that use it:
-//     plane q+1 gets the a=0 taps, plane q the a=1 taps, plane q-1 the a=2 taps,
-// with packed-half FMAs (HFMA2) whose partial sums are added in fp32 by the sm_100 mixed-precision add
-// (three accumulate modes, see fprop_step); there is no index arithmetic in the inner loop.  A finished plane is staged in shared memory and leaves through a
-// TMA store (which clips the w/d tails).  Every input plane is read from shared memory exactly
-// once per thread-patch; the weights (27 x channel pairs) live in registers.
+// along h.  A producer warp streams ONE halo'd input plane [(WT+2) x (DT+2) x CS] per step into a ring of
+// shared-memory stages by tiled TMA loads (zero fill outside the volume = the padding on all three
+// axes); full/empty mbarriers are the only synchronisation between it and the consumer warps.  Every
+// consumer thread - fixed (channel pairs, d), M consecutive w positions - applies the plane to the three
+// output planes that use it (plane q+1 gets the a=0 taps, plane q the a=1 taps, plane q-1 the a=2 taps)
+// and carries the unfinished sums in registers, so each input plane is read from shared memory exactly
+// once and the 27 x (channel pairs) taps stay in registers.  KDW_ACC_F32 uses the sm_100 mixed-precision
+// FMA (fp16 operands, fp32 accumulator: exact products, one rounding to fp16 at the end);
+// KDW_ACC_F16 uses packed-half FMA chains.  Neither has index arithmetic in the inner loop.  A warp
+// stages its part of a finished plane in shared memory and stores it with its own TMA store, which
+// clips the w/d tails.
 //
 // Plain kernel (any C): one thread per output element, fp32 FMAs, bounds checks.  Used for C < 8.
 #include "../../include/kdw.h"
@@ -72,51 +74,68 @@ __global__ void __launch_bounds__(256) fprop_plain_kernel(const __half* __restri
 // TMA kernel
 // ------------------------------------------------------------------------------------------------
 template <class Cfg, int MODE>
-__global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
+__global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
     fprop_tma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
                      const __half* __restrict__ weight, const Sched s, const int C, const int y_h0, int* status) {
-    constexpr int M = Cfg::M, CP = Cfg::CP, ST = Cfg::ST;
+    constexpr int M = Cfg::M, CP = Cfg::CP, ST = Cfg::ST, NCW = Cfg::NCW;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
-    unsigned char* in_base = smem;
-    unsigned char* out_base = smem + ST * Cfg::IN_STRIDE;
-    const uint32_t bar0 = smem_u32(out_base + 2 * Cfg::OUT_BYTES);
+    unsigned char* in_base = smem;                         // ST input stages
+    unsigned char* out_base = smem + ST * Cfg::IN_STRIDE;  // per consumer warp: two output tiles
+    const uint32_t full0 = smem_u32(out_base + 2 * NCW * Cfg::OUTW_BYTES);  // full[ST], then empty[ST]
+    const uint32_t empty0 = full0 + 8 * ST;
 
     const int tid = threadIdx.x;
-    const FThread<Cfg> th(tid);
-    const int cg = th.cg, in_off = th.in_off, out_off = th.out_off;
-
+    const int warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         prefetch_tmap(&tmx);
         prefetch_tmap(&tmy);
-        for (int k = 0; k < ST; ++k) mbar_init(bar0 + 8 * k, 1);
+        for (int k = 0; k < ST; ++k) {
+            mbar_init(full0 + 8 * k, 1);     // the producer's arrive.expect_tx
+            mbar_init(empty0 + 8 * k, NCW);  // one arrive per consumer warp
+        }
         mbar_fence_init();
     }
-    __syncthreads();
+    __syncthreads();  // the only CTA-wide barrier: from here on the warps only meet through mbarriers
 
     const long long lo = (long long)blockIdx.x * s.total / gridDim.x;
     const long long hi = (long long)(blockIdx.x + 1) * s.total / gridDim.x;
 
-    StepIter cons;
-    cons.init(s, lo, hi);
-    StepIter prod;
-    prod.active = false;
-    uint32_t pi = 0;  // loads issued (thread 0 only)
-    if (tid == 0) {
-        prod.init(s, lo, hi);
-        for (int k = 0; k < ST && prod.active; ++k) {
-            const uint32_t bar = bar0 + 8 * (pi % ST);
-            mbar_expect_tx(bar, Cfg::IN_BYTES);
-            tma_load_5d(status, smem_u32(in_base + (pi % ST) * Cfg::IN_STRIDE), &tmx, bar, prod.g.c0, prod.g.d0 - 1,
-                        prod.g.w0 - 1, prod.q, prod.g.n);
+    if (warp == NCW) {
+        // ---------------- producer warp: one lane streams the input planes of the CTA's range ----------------
+        if (lane != 0) return;
+        StepIter it;
+        it.init(s, lo, hi);
+        uint32_t pi = 0;
+        bool ok = true;
+        while (it.active && ok) {
+            const uint32_t st = pi % ST;
+            if (pi >= ST) ok = mbar_wait_bounded(empty0 + 8 * st, ((pi / ST) & 1u) ^ 1u);  // consumers released it
+            if (!ok) break;
+            mbar_expect_tx(full0 + 8 * st, Cfg::IN_BYTES);
+            tma_load_5d(status, smem_u32(in_base + st * Cfg::IN_STRIDE), &tmx, full0 + 8 * st, it.g.c0, it.g.d0 - 1,
+                        it.g.w0 - 1, it.q, it.g.n);
             ++pi;
-            prod.next(s);
+            it.next(s);
         }
+        if (!ok) {
+            atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
+            // loads already issued still target this CTA's shared memory: give them a bounded chance to land
+            const uint32_t first = pi > ST ? pi - ST : 0;
+            for (uint32_t k = first; k < pi; ++k) (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u);
+        }
+        return;
     }
 
+    // ---------------- consumer warps ----------------
+    const FThread<Cfg> th(tid);
+    unsigned char* my_out = out_base + warp * 2 * Cfg::OUTW_BYTES;
+    StepIter it;
+    it.init(s, lo, hi);
+
     __half2 wgt[27][CP];
-    float2 P1[M][CP], P2[M][CP];  // carried fp32 partials (see fprop_step)
-    __half2 H1[M][CP], H2[M][CP];  // carried packed-half partials
+    float2 P1[M][CP], P2[M][CP];   // carried fp32 partial sums (see fprop_step)
+    __half2 H1[M][CP], H2[M][CP];  // carried packed-half partial sums
 #pragma unroll
     for (int m = 0; m < M; ++m)
 #pragma unroll
@@ -126,64 +145,44 @@ __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
         }
 
     uint32_t ci = 0;  // steps consumed
-    uint32_t oc = 0;  // planes stored
-    bool failed = false;
-    while (cons.active) {
-        const int q = cons.q;
-        if (q == cons.g.hb - 1) {  // new segment: this thread's taps for the segment's channel slice
-            const __half* wp = weight + cons.g.c0 + cg * 2 * CP;
+    uint32_t oc = 0;  // planes stored by this warp
+    while (it.active) {
+        const int q = it.q;
+        if (q == it.g.hb - 1) {  // new segment: this thread's taps for the segment's channel slice
+            const __half* wp = weight + it.g.c0 + th.cg * 2 * CP;
 #pragma unroll
             for (int k = 0; k < 27; ++k)
 #pragma unroll
                 for (int i = 0; i < CP; ++i)
                     wgt[k][i] = *reinterpret_cast<const __half2*>(wp + (size_t)k * C + 2 * i);
         }
-        const uint32_t stage = ci % ST;
-        const bool ok = mbar_wait_bounded(bar0 + 8 * stage, (ci / ST) & 1u);
-        const int am = cons.amask();
-        const __half* in = reinterpret_cast<const __half*>(in_base + stage * Cfg::IN_STRIDE) + in_off;
-        __half* ob = reinterpret_cast<__half*>(out_base + (oc & 1u) * Cfg::OUT_BYTES) + out_off;
-        switch (am) {
-            case 1: fprop_step<Cfg, MODE, 1>(in, ob, wgt, P1, P2, H1, H2); break;
-            case 2: fprop_step<Cfg, MODE, 2>(in, ob, wgt, P1, P2, H1, H2); break;
-            case 3: fprop_step<Cfg, MODE, 3>(in, ob, wgt, P1, P2, H1, H2); break;
-            case 4: fprop_step<Cfg, MODE, 4>(in, ob, wgt, P1, P2, H1, H2); break;
-            case 6: fprop_step<Cfg, MODE, 6>(in, ob, wgt, P1, P2, H1, H2); break;
-            default: fprop_step<Cfg, MODE, 7>(in, ob, wgt, P1, P2, H1, H2); break;
-        }
-        if (am & 4) fence_proxy_async_smem();  // the out tile must be visible to the TMA store
-        if (tid == 0) tma_wait_read_all();     // the previous store has finished reading the other out tile
-        if (__syncthreads_or(ok ? 0 : 1)) {
-            failed = true;
+        const uint32_t st = ci % ST;
+        const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u);
+        if (__any_sync(0xffffffffu, !ok)) {
+            if (lane == 0) atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
             break;
         }
-        if (tid == 0) {
-            if (am & 4) {
-                tma_store_5d(status, &tmy, smem_u32(out_base + (oc & 1u) * Cfg::OUT_BYTES), cons.g.c0, cons.g.d0, cons.g.w0,
-                             q - 1 - y_h0, cons.g.n);
+        const bool store = q - 1 >= it.g.hb;  // plane q-1 is owned by the segment (q-1 < he always holds)
+        unsigned char* ob_bytes = my_out + (oc & 1u) * Cfg::OUTW_BYTES;
+        if (store && lane == 0) tma_wait_read<1>();  // the store issued two planes ago has released this tile
+        __syncwarp();
+        const __half* in = reinterpret_cast<const __half*>(in_base + st * Cfg::IN_STRIDE) + th.in_off;
+        fprop_step<Cfg, MODE>(in, reinterpret_cast<__half*>(ob_bytes) + th.out_off, store, wgt, P1, P2, H1, H2);
+        if (store) fence_proxy_async_smem();  // the tile must be visible to the TMA store
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(empty0 + 8 * st);  // this warp is done with the input stage
+            if (store) {
+                tma_store_5d(status, &tmy, smem_u32(ob_bytes), it.g.c0, it.g.d0 + th.warp_d0, it.g.w0 + th.wg * M,
+                             q - 1 - y_h0, it.g.n);
                 tma_commit();
             }
-            if (prod.active) {  // the stage just consumed is free: refill it ST planes ahead
-                const uint32_t bar = bar0 + 8 * (pi % ST);
-                mbar_expect_tx(bar, Cfg::IN_BYTES);
-                tma_load_5d(status, smem_u32(in_base + (pi % ST) * Cfg::IN_STRIDE), &tmx, bar, prod.g.c0, prod.g.d0 - 1,
-                            prod.g.w0 - 1, prod.q, prod.g.n);
-                ++pi;
-                prod.next(s);
-            }
         }
-        if (am & 4) ++oc;
-        cons.next(s);
+        if (store) ++oc;
+        it.next(s);
         ++ci;
     }
-    if (tid == 0) {
-        if (failed) {
-            atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
-            // loads already issued still target this CTA's shared memory: give them a bounded chance to land
-            for (uint32_t k = ci; k < pi; ++k) (void)mbar_wait_bounded(bar0 + 8 * (k % ST), (k / ST) & 1u);
-        }
-        tma_wait_all();
-    }
+    if (lane == 0) tma_wait_all();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -204,7 +203,7 @@ static int launch_fprop_tma(const FpropArgs& a) {
     int rc = encode_volume_map(&tmx, a.x, a.N, a.C, a.Hx, a.W, a.D, a.xsN, a.xsH, a.xsW, Cfg::CS, Cfg::DT + 2,
                                Cfg::WT + 2);
     if (rc) return rc;
-    rc = encode_volume_map(&tmy, a.y, a.N, a.C, a.Hy, a.W, a.D, a.ysN, a.ysH, a.ysW, Cfg::CS, Cfg::DT, Cfg::WT);
+    rc = encode_volume_map(&tmy, a.y, a.N, a.C, a.Hy, a.W, a.D, a.ysN, a.ysH, a.ysW, Cfg::CS, Cfg::DPW, Cfg::M);
     if (rc) return rc;
     if (((uintptr_t)a.w & 3) != 0) {
         set_error("weight pointer must be 4-byte aligned");
@@ -213,7 +212,7 @@ static int launch_fprop_tma(const FpropArgs& a) {
     auto kern = fprop_tma_kernel<Cfg, MODE>;
     KDW_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     int occ = 0, sms = 0;
-    KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::NT, Cfg::SMEM));
+    KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::NT + 32, Cfg::SMEM));
     if (occ < 1) {
         set_error("fprop kernel variant does not fit on this device");
         return KDW_ERR_TUNE;
@@ -225,7 +224,7 @@ static int launch_fprop_tma(const FpropArgs& a) {
     if (rc) return rc;
     Sched s;
     const int grid = make_sched(&s, a.N, a.C, a.W, a.D, a.h_begin, a.h_end, Cfg::WT, Cfg::DT, Cfg::CS, sms * occ);
-    kern<<<grid, Cfg::NT, Cfg::SMEM, a.stream>>>(tmx, tmy, (const __half*)a.w, s, (int)a.C, a.y_h0, status);
+    kern<<<grid, Cfg::NT + 32, Cfg::SMEM, a.stream>>>(tmx, tmy, (const __half*)a.w, s, (int)a.C, a.y_h0, status);
     KDW_CUDA(cudaGetLastError());
     return 0;
 }
@@ -233,13 +232,12 @@ static int launch_fprop_tma(const FpropArgs& a) {
 typedef int (*FpropLaunch)(const FpropArgs&);
 struct FpropVariant {
     int cs;
-    FpropLaunch mode[3];  // indexed by KDW_ACC_*
+    FpropLaunch mode[2];  // indexed by KDW_ACC_*
 };
 #define KDW_VARIANT(ID, CS, DT, WT, M, CP, ST, MINB)                            \
     {CS,                                                                        \
      {&launch_fprop_tma<FCfg<CS, DT, WT, M, CP, ST, MINB>, 0>,                  \
-      &launch_fprop_tma<FCfg<CS, DT, WT, M, CP, ST, MINB>, 1>,                  \
-      &launch_fprop_tma<FCfg<CS, DT, WT, M, CP, ST, MINB>, 2>}},
+      &launch_fprop_tma<FCfg<CS, DT, WT, M, CP, ST, MINB>, 1>}},
 // index = id - 1
 static const FpropVariant g_fprop_variants[] = {
 #include "fprop_variants.inc"
@@ -250,8 +248,8 @@ static const int g_n_fprop_variants = (int)(sizeof(g_fprop_variants) / sizeof(g_
 static int auto_fprop_variant(int64_t C) {
     if (C == 8) return 1;
     if (C == 16) return 4;
-    if (C == 32) return 6;
-    return 9;
+    if (C == 32) return 7;
+    return 10;
 }
 
 static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N, int64_t C, int64_t Hx, int64_t W,
@@ -267,8 +265,8 @@ static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N,
                   (long long)N, (long long)C, (long long)Hx, (long long)W, (long long)D);
         return KDW_ERR_ARG;
     }
-    if (acc_type != KDW_ACC_F32 && acc_type != KDW_ACC_F16 && acc_type != KDW_ACC_F32_PLANE) {
-        set_error("fprop: acc_type must be KDW_ACC_F32, KDW_ACC_F16 or KDW_ACC_F32_PLANE");
+    if (acc_type != KDW_ACC_F32 && acc_type != KDW_ACC_F16) {
+        set_error("fprop: acc_type must be KDW_ACC_F32 or KDW_ACC_F16");
         return KDW_ERR_ARG;
     }
     if (Hx > 0x7fffffff || W > 0x7fffffff || D > 0x7fffffff || N > 0x7fffffff || C > 0x7fffffff) {

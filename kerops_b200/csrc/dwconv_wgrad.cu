@@ -3,15 +3,15 @@
 // Replaces kerops/kernels/dw_conv.py:147-287 (_DWConv_wgrad_cl3d_impl), the zero-filled fp16 partial
 // buffer and the torch sum over it (kerops/ops/conv/dwconv_wgrad.py:54-77).
 //
-// Pass 1 (TMA kernel, C multiple of 8).  Same column march as the forward kernel: per step a CTA
-// receives the halo'd x plane q and the grad plane q+1 by TMA.  A thread - fixed (channel pairs, d),
-// M consecutive w positions - keeps the grad values of planes q-1, q, q+1 in registers and multiplies
-// every x value it reads with the (up to) nine grad values whose tap it is:
-//     dw[a][b][t] += grad[q+1-a][m] * x[q][m+b][d+t].
-// The 27 products of a step go into packed-half chains of M terms, which are then added to fp32
-// accumulators (mixed-precision add).  At the end of a segment the CTA reduces over its threads
-// (warp shuffles, then warps in fixed order through shared memory) and adds the [27][CS] result to
-// its own fp32 row of the workspace.
+// Pass 1 (TMA kernel, C multiple of 8).  Same column march as the forward kernel: a producer warp streams,
+// per step, the halo'd x plane q and the grad plane q+1 into a ring of shared-memory stages by TMA; full /
+// empty mbarriers connect it to the consumer warps.  A consumer thread - fixed (channel pairs, d), M
+// consecutive w positions - keeps the grad values of planes q-1, q, q+1 in registers and multiplies every x
+// value it reads with the (up to) nine grad values whose tap it is:
+//     dw[a][b][t] += grad[q+1-a][m] * x[q][m+b][d+t],
+// each product one sm_100 mixed-precision FMA (fp16 operands, exact product, fp32 accumulator).  At the end
+// of a segment the consumer warps reduce over their threads (warp shuffles, then warps in fixed order
+// through shared memory) and add the [27][CS] result to the CTA's own fp32 row of the workspace.
 // Pass 2 adds the rows in CTA order and writes the fp32 and fp16 [3][3][3][C] results.
 // There are no atomics anywhere, so results are bitwise reproducible.
 //
@@ -75,57 +75,72 @@ __global__ void __launch_bounds__(128) wgrad_plain_kernel(const __half* __restri
 // TMA pass 1
 // ------------------------------------------------------------------------------------------------
 template <class Cfg>
-__global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
+__global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
     wgrad_tma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmg,
                      float* __restrict__ ws, const Sched s, const int C, const int g_h0, int* status) {
-    constexpr int CS = Cfg::CS, M = Cfg::M, CP = Cfg::CP, ST = Cfg::ST, CPG = Cfg::CPG;
+    constexpr int CS = Cfg::CS, M = Cfg::M, CP = Cfg::CP, ST = Cfg::ST, CPG = Cfg::CPG, NCW = Cfg::NCW;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
-    unsigned char* stage_base = smem;
+    unsigned char* stage_base = smem;  // ST stages of [x tile | grad tile]
     float* red = reinterpret_cast<float*>(smem + ST * Cfg::STAGE);
-    const uint32_t bar0 = smem_u32(smem + ST * Cfg::STAGE + Cfg::RED_BYTES);
+    const uint32_t full0 = smem_u32(smem + ST * Cfg::STAGE + Cfg::RED_BYTES);  // full[ST], then empty[ST]
+    const uint32_t empty0 = full0 + 8 * ST;
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
-    const WThread<Cfg> th(tid);
-    const int cg = th.cg, x_off = th.x_off, g_off = th.g_off;
     const int KC = 27 * C;
-    float* row = ws + (size_t)blockIdx.x * KC;
+    float* row = ws + (size_t)blockIdx.x * KC;  // this CTA's fp32 [27][C] row of the workspace
 
     if (tid == 0) {
         prefetch_tmap(&tmx);
         prefetch_tmap(&tmg);
-        for (int k = 0; k < ST; ++k) mbar_init(bar0 + 8 * k, 1);
+        for (int k = 0; k < ST; ++k) {
+            mbar_init(full0 + 8 * k, 1);
+            mbar_init(empty0 + 8 * k, NCW);
+        }
         mbar_fence_init();
     }
-    for (int k = tid; k < KC; k += Cfg::NT) row[k] = 0.f;  // this CTA's workspace row
-    __syncthreads();
+    for (int k = tid; k < KC; k += Cfg::NT + 32) row[k] = 0.f;
+    __syncthreads();  // the only CTA-wide barrier
 
     const long long lo = (long long)blockIdx.x * s.total / gridDim.x;
     const long long hi = (long long)(blockIdx.x + 1) * s.total / gridDim.x;
 
-    StepIter cons;
-    cons.init(s, lo, hi);
-    StepIter prod;
-    prod.active = false;
-    uint32_t pi = 0;
-    auto issue = [&]() {
-        const uint32_t st = pi % ST;
-        const uint32_t bar = bar0 + 8 * st;
-        const bool with_g = prod.q + 1 < prod.g.he;  // grad plane q+1 is owned by the segment
-        mbar_expect_tx(bar, Cfg::X_BYTES + (with_g ? Cfg::G_BYTES : 0));
-        tma_load_5d(status, smem_u32(stage_base + st * Cfg::STAGE), &tmx, bar, prod.g.c0, prod.g.d0 - 1, prod.g.w0 - 1, prod.q,
-                    prod.g.n);
-        if (with_g)
-            tma_load_5d(status, smem_u32(stage_base + st * Cfg::STAGE + Cfg::X_STRIDE), &tmg, bar, prod.g.c0, prod.g.d0,
-                        prod.g.w0, prod.q + 1 - g_h0, prod.g.n);
-        ++pi;
-        prod.next(s);
-    };
-    if (tid == 0) {
-        prod.init(s, lo, hi);
-        for (int k = 0; k < ST && prod.active; ++k) issue();
+    if (warp == NCW) {
+        // ---------------- producer warp ----------------
+        if (lane != 0) return;
+        StepIter it;
+        it.init(s, lo, hi);
+        uint32_t pi = 0;
+        bool ok = true;
+        while (it.active) {
+            const uint32_t st = pi % ST;
+            if (pi >= ST) ok = mbar_wait_bounded(empty0 + 8 * st, ((pi / ST) & 1u) ^ 1u);
+            if (!ok) break;
+            const bool with_g = it.q + 1 < it.g.he;  // grad plane q+1 is owned by the segment
+            const uint32_t bar = full0 + 8 * st;
+            mbar_expect_tx(bar, Cfg::X_BYTES + (with_g ? Cfg::G_BYTES : 0));
+            tma_load_5d(status, smem_u32(stage_base + st * Cfg::STAGE), &tmx, bar, it.g.c0, it.g.d0 - 1, it.g.w0 - 1,
+                        it.q, it.g.n);
+            if (with_g)
+                tma_load_5d(status, smem_u32(stage_base + st * Cfg::STAGE + Cfg::X_STRIDE), &tmg, bar, it.g.c0, it.g.d0,
+                            it.g.w0, it.q + 1 - g_h0, it.g.n);
+            ++pi;
+            it.next(s);
+        }
+        if (!ok) {
+            atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
+            const uint32_t first = pi > ST ? pi - ST : 0;
+            for (uint32_t k = first; k < pi; ++k) (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u);
+        }
+        return;
     }
+
+    // ---------------- consumer warps ----------------
+    const WThread<Cfg> th(tid);
+    const int cg = th.cg;
+    StepIter it;
+    it.init(s, lo, hi);
 
     __half2 G[3][M][CP];
     float2 acc[27][CP];
@@ -140,28 +155,36 @@ __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
 
     uint32_t ci = 0;
     bool failed = false;
-    while (cons.active) {
-        const uint32_t stage = ci % ST;
-        const bool ok = mbar_wait_bounded(bar0 + 8 * stage, (ci / ST) & 1u);
-        const int am = cons.amask();
-        const __half* xin = reinterpret_cast<const __half*>(stage_base + stage * Cfg::STAGE) + x_off;
-        const __half* gin = reinterpret_cast<const __half*>(stage_base + stage * Cfg::STAGE + Cfg::X_STRIDE) + g_off;
-        switch (am) {
-            case 1: wgrad_step<Cfg, 1>(xin, gin, G, acc); break;
-            case 2: wgrad_step<Cfg, 2>(xin, gin, G, acc); break;
-            case 3: wgrad_step<Cfg, 3>(xin, gin, G, acc); break;
-            case 4: wgrad_step<Cfg, 4>(xin, gin, G, acc); break;
-            case 6: wgrad_step<Cfg, 6>(xin, gin, G, acc); break;
-            default: wgrad_step<Cfg, 7>(xin, gin, G, acc); break;
-        }
-        if (__syncthreads_or(ok ? 0 : 1)) {
+    while (it.active) {
+        const uint32_t st = ci % ST;
+        const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u);
+        if (__any_sync(0xffffffffu, !ok)) {
+            if (lane == 0) atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
             failed = true;
             break;
         }
-        if (tid == 0 && prod.active) issue();  // the stage just consumed is free
-        if (cons.q == cons.g.he) {
-            // Segment finished: reduce over the threads of the CTA that share channels.
-            const int c0 = cons.g.c0;
+        const int q = it.q;
+        if (q == it.g.hb - 1) {
+            // new segment: grad planes of the previous segment must not be paired with this segment's x
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+#pragma unroll
+                for (int i = 0; i < CP; ++i) G[0][m][i] = G[1][m][i] = G[2][m][i] = __float2half2_rn(0.f);
+        }
+        const bool load_g = q + 1 < it.g.he;
+        const __half* xin = reinterpret_cast<const __half*>(stage_base + st * Cfg::STAGE) + th.x_off;
+        const __half* gin = reinterpret_cast<const __half*>(stage_base + st * Cfg::STAGE + Cfg::X_STRIDE) + th.g_off;
+        switch (ci % 3) {
+            case 0: wgrad_step<Cfg, 0>(xin, gin, load_g, G, acc); break;
+            case 1: wgrad_step<Cfg, 1>(xin, gin, load_g, G, acc); break;
+            default: wgrad_step<Cfg, 2>(xin, gin, load_g, G, acc); break;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8 * st);  // this warp is done with the stage
+        if (q == it.g.he) {
+            // Segment finished: reduce over the consumer threads that share channels, then add the [27][CS]
+            // result to the CTA's workspace row.  Warps take turns in a fixed order (no atomics).
+            const int c0 = it.g.c0;
 #pragma unroll
             for (int k = 0; k < 27; ++k)
 #pragma unroll
@@ -174,42 +197,38 @@ __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
                     }
                     acc[k][i] = v;
                 }
-            for (int wi = 0; wi < Cfg::NW; ++wi) {  // warps in fixed order
+            for (int wi = 0; wi < NCW; ++wi) {
                 if (warp == wi && lane < CPG) {
 #pragma unroll
                     for (int k = 0; k < 27; ++k)
 #pragma unroll
                         for (int i = 0; i < CP; ++i) {
-                            float2* dst = reinterpret_cast<float2*>(red + k * CS + cg * 2 * CP + 2 * i);
+                            float* dst = red + k * CS + cg * 2 * CP + 2 * i;
                             if (wi == 0) {
-                                *dst = acc[k][i];
+                                dst[0] = acc[k][i].x;
+                                dst[1] = acc[k][i].y;
                             } else {
-                                float2 o = *dst;
-                                o.x += acc[k][i].x;
-                                o.y += acc[k][i].y;
-                                *dst = o;
+                                dst[0] += acc[k][i].x;
+                                dst[1] += acc[k][i].y;
                             }
                         }
                 }
-                __syncthreads();
+                named_barrier_sync(1, Cfg::NT);
             }
             for (int e = tid; e < 27 * CS; e += Cfg::NT) {
                 const int k = e / CS, c = e % CS;
                 row[k * C + c0 + c] += red[e];
             }
-            __syncthreads();
+            named_barrier_sync(1, Cfg::NT);
 #pragma unroll
             for (int k = 0; k < 27; ++k)
 #pragma unroll
                 for (int i = 0; i < CP; ++i) acc[k][i] = make_float2(0.f, 0.f);
         }
-        cons.next(s);
+        it.next(s);
         ++ci;
     }
-    if (tid == 0 && failed) {
-        atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
-        for (uint32_t k = ci; k < pi; ++k) (void)mbar_wait_bounded(bar0 + 8 * (k % ST), (k / ST) & 1u);
-    }
+    (void)failed;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -236,7 +255,7 @@ static int launch_wgrad_tma(const WgradArgs& a, int* rows_used) {
     auto kern = wgrad_tma_kernel<Cfg>;
     KDW_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     int occ = 0, sms = 0;
-    KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::NT, Cfg::SMEM));
+    KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::NT + 32, Cfg::SMEM));
     if (occ < 1) {
         set_error("wgrad kernel variant does not fit on this device");
         return KDW_ERR_TUNE;
@@ -250,7 +269,7 @@ static int launch_wgrad_tma(const WgradArgs& a, int* rows_used) {
     if (target > a.ws_rows) target = a.ws_rows;
     Sched s;
     const int grid = make_sched(&s, a.N, a.C, a.W, a.D, a.h_begin, a.h_end, Cfg::WT, Cfg::DT, Cfg::CS, (int)target);
-    kern<<<grid, Cfg::NT, Cfg::SMEM, a.stream>>>(tmx, tmg, a.ws, s, (int)a.C, a.g_h0, status);
+    kern<<<grid, Cfg::NT + 32, Cfg::SMEM, a.stream>>>(tmx, tmg, a.ws, s, (int)a.C, a.g_h0, status);
     KDW_CUDA(cudaGetLastError());
     *rows_used = grid;
     return 0;
@@ -270,10 +289,9 @@ static const WgradVariant g_wgrad_variants[] = {
 static const int g_n_wgrad_variants = (int)(sizeof(g_wgrad_variants) / sizeof(g_wgrad_variants[0]));
 
 static int auto_wgrad_variant(int64_t C) {
-    if (C == 8) return 1;
-    if (C == 16) return 3;
-    if (C == 32) return 5;
-    return 7;
+    if (C <= 16) return 1;
+    if (C == 32) return 3;
+    return 5;
 }
 
 static int64_t ws_rows_for_device(int* rc_out) {

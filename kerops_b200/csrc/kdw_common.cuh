@@ -141,6 +141,13 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_fence_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Barrier among `nthreads` threads of the CTA (a multiple of 32) that does not involve the other warps.
+__device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
@@ -204,6 +211,11 @@ __device__ __forceinline__ void tma_store_5d(int* status, const CUtensorMap* tm,
         : "memory");
 }
 __device__ __forceinline__ void tma_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's committed bulk stores still read their shared-memory source.
+template <int N>
+__device__ __forceinline__ void tma_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
 __device__ __forceinline__ void tma_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* tm) {
@@ -238,6 +250,27 @@ KDW_HD __half2 h2_fma(__half2 a, __half2 b, __half2 c) {
     const double lo = (double)fa.x * (double)fb.x + (double)fc.x;
     const double hi = (double)fa.y * (double)fb.y + (double)fc.y;
     return __halves2half2(__double2half(lo), __double2half(hi));
+#endif
+}
+
+// c + a * b per lane with fp16 a, b and fp32 c: the sm_100 mixed-precision FMA.  The fp16 x fp16 product is
+// exact, the sum is rounded once to fp32 - fp32 accumulation without separate converts.
+KDW_HD float2 fma_h2_f2(__half2 a, __half2 b, float2 c) {
+#ifdef __CUDA_ARCH__
+    H2Pack<1> ka, kb;
+    ka.h[0] = a;
+    kb.h[0] = b;
+    asm("{\n\t.reg .b16 al, ah, bl, bh;\n\t"
+        "mov.b32 {al, ah}, %2;\n\t"
+        "mov.b32 {bl, bh}, %3;\n\t"
+        "fma.rn.f32.f16 %0, al, bl, %0;\n\t"
+        "fma.rn.f32.f16 %1, ah, bh, %1;\n\t}"
+        : "+f"(c.x), "+f"(c.y)
+        : "r"(ka.u1), "r"(kb.u1));
+    return c;
+#else
+    const float2 fa = __half22float2(a), fb = __half22float2(b);
+    return make_float2(fmaf(fa.x, fb.x, c.x), fmaf(fa.y, fb.y, c.y));
 #endif
 }
 

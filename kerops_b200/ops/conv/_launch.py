@@ -6,8 +6,8 @@ import torch
 
 from ... import _lib
 
-# ACCTYPE keyword -> KDW_ACC_* (include/kdw.h); 'float32_plane' has no counterpart in the reference
-ACC_TYPES = {'float32': 0, 'float16': 1, 'float32_plane': 2}
+# ACCTYPE keyword -> KDW_ACC_* (include/kdw.h)
+ACC_TYPES = {'float32': 0, 'float16': 1}
 
 
 def _stream_ptr(device):

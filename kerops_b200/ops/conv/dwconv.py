@@ -33,9 +33,7 @@ def DWConv(x, weight, *, ACCTYPE: ConfigurableArg, num_warps: ConfigurableArg, D
 
     x       (N, C, H, W, D) fp16 CUDA tensor, contiguous in channels_last_3d
     weight  [3, 3, 3, C] fp16 contiguous: weight[a, b, t, c] = torch_weight[c, 0, a, b, t]
-    ACCTYPE 'float32' (the reference's arithmetic: fp16 products, the three d-taps summed in fp16, fp32 sum of
-            the nine partials), 'float16' (one fp16 chain), or 'float32_plane' (nine taps per fp16 chain,
-            fp32 sum of three; faster, outside the reference test's tolerance)
+    ACCTYPE 'float32' (exact products accumulated in fp32, one rounding to fp16) or 'float16' (fp16 FMA chains)
     num_warps, D_block  accepted for call compatibility; D_block must be a power of two
     Returns a new tensor with the shape, strides and dtype of x.
     """

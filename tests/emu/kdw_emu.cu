@@ -55,7 +55,8 @@ static int emu_fprop_cfg(const __half* x, const __half* w, __half* y, Vol vx, Vo
     };
     Sched s;
     const int grid = make_sched(&s, vx.N, vx.C, vx.W, vx.D, h_begin, h_end, Cfg::WT, Cfg::DT, Cfg::CS, grid_target);
-    std::vector<__half> stage(Cfg::IN_BYTES / 2), out(Cfg::OUT_BYTES / 2);
+    std::vector<__half> stage(Cfg::IN_BYTES / 2);
+    std::vector<__half> out((size_t)Cfg::NCW * Cfg::OUTW_BYTES / 2);  // one tile per consumer warp
     std::vector<TState> ts(Cfg::NT);
     for (int blk = 0; blk < grid; ++blk) {
         const long long lo = (long long)blk * s.total / grid, hi = (long long)(blk + 1) * s.total / grid;
@@ -66,7 +67,7 @@ static int emu_fprop_cfg(const __half* x, const __half* w, __half* y, Vol vx, Vo
             const int q = cons.q;
             const Seg& g = cons.g;
             emu_tma_load(stage.data(), x, vx, Cfg::CS, Cfg::DT + 2, Cfg::WT + 2, g.c0, g.d0 - 1, g.w0 - 1, q, g.n);
-            const int am = cons.amask();
+            const bool store = q - 1 >= g.hb;
             for (int tid = 0; tid < Cfg::NT; ++tid) {
                 TState& t = ts[tid];
                 const FThread<Cfg> th(tid);
@@ -76,18 +77,16 @@ static int emu_fprop_cfg(const __half* x, const __half* w, __half* y, Vol vx, Vo
                         for (int i = 0; i < CP; ++i) t.wgt[k][i] = *reinterpret_cast<const __half2*>(wp + (size_t)k * vx.C + 2 * i);
                 }
                 const __half* in = stage.data() + th.in_off;
-                __half* ob = out.data() + th.out_off;
-                switch (am) {
-                    case 1: fprop_step<Cfg, MODE, 1>(in, ob, t.wgt, t.P1, t.P2, t.H1, t.H2); break;
-                    case 2: fprop_step<Cfg, MODE, 2>(in, ob, t.wgt, t.P1, t.P2, t.H1, t.H2); break;
-                    case 3: fprop_step<Cfg, MODE, 3>(in, ob, t.wgt, t.P1, t.P2, t.H1, t.H2); break;
-                    case 4: fprop_step<Cfg, MODE, 4>(in, ob, t.wgt, t.P1, t.P2, t.H1, t.H2); break;
-                    case 6: fprop_step<Cfg, MODE, 6>(in, ob, t.wgt, t.P1, t.P2, t.H1, t.H2); break;
-                    case 7: fprop_step<Cfg, MODE, 7>(in, ob, t.wgt, t.P1, t.P2, t.H1, t.H2); break;
-                    default: return -100 - am;
+                __half* ob = out.data() + (size_t)(tid / 32) * (Cfg::OUTW_BYTES / 2) + th.out_off;
+                fprop_step<Cfg, MODE>(in, ob, store, t.wgt, t.P1, t.P2, t.H1, t.H2);
+            }
+            if (store) {
+                for (int wp = 0; wp < Cfg::NCW; ++wp) {  // every warp stores its own box
+                    const FThread<Cfg> th(wp * 32);
+                    emu_tma_store(y, out.data() + (size_t)wp * (Cfg::OUTW_BYTES / 2), vy, Cfg::CS, Cfg::DPW, Cfg::M, g.c0,
+                                  g.d0 + th.warp_d0, g.w0 + th.wg * Cfg::M, q - 1 - y_h0, g.n);
                 }
             }
-            if (am & 4) emu_tma_store(y, out.data(), vy, Cfg::CS, Cfg::DT, Cfg::WT, g.c0, g.d0, g.w0, q - 1 - y_h0, g.n);
             cons.next(s);
         }
     }
@@ -114,29 +113,26 @@ static int emu_wgrad_cfg(const __half* x, const __half* gr, float* dw, Vol vx, V
         float* row = rows.data() + (size_t)blk * KC;
         StepIter cons;
         cons.init(s, lo, hi);
+        unsigned ci = 0;
         while (cons.active) {
             const int q = cons.q;
             const Seg& g = cons.g;
             emu_tma_load(xs.data(), x, vx, CS, Cfg::DT + 2, Cfg::WT + 2, g.c0, g.d0 - 1, g.w0 - 1, q, g.n);
-            const bool with_g = q + 1 < g.he;
-            if (with_g)
+            const bool load_g = q + 1 < g.he;
+            if (load_g)
                 emu_tma_load(gs.data(), gr, vg, CS, Cfg::DT, Cfg::WT, g.c0, g.d0, g.w0, q + 1 - g_h0, g.n);
             else
                 for (auto& e : gs) e = __float2half(12345.f);  // stale data must never be used
-            const int am = cons.amask();
             for (int tid = 0; tid < Cfg::NT; ++tid) {
                 TState& t = ts[tid];
                 const WThread<Cfg> th(tid);
+                if (q == g.hb - 1) memset(t.G, 0, sizeof(t.G));
                 const __half* xin = xs.data() + th.x_off;
                 const __half* gin = gs.data() + th.g_off;
-                switch (am) {
-                    case 1: wgrad_step<Cfg, 1>(xin, gin, t.G, t.acc); break;
-                    case 2: wgrad_step<Cfg, 2>(xin, gin, t.G, t.acc); break;
-                    case 3: wgrad_step<Cfg, 3>(xin, gin, t.G, t.acc); break;
-                    case 4: wgrad_step<Cfg, 4>(xin, gin, t.G, t.acc); break;
-                    case 6: wgrad_step<Cfg, 6>(xin, gin, t.G, t.acc); break;
-                    case 7: wgrad_step<Cfg, 7>(xin, gin, t.G, t.acc); break;
-                    default: return -100 - am;
+                switch (ci % 3) {
+                    case 0: wgrad_step<Cfg, 0>(xin, gin, load_g, t.G, t.acc); break;
+                    case 1: wgrad_step<Cfg, 1>(xin, gin, load_g, t.G, t.acc); break;
+                    default: wgrad_step<Cfg, 2>(xin, gin, load_g, t.G, t.acc); break;
                 }
             }
             if (q == g.he) {
@@ -151,6 +147,7 @@ static int emu_wgrad_cfg(const __half* x, const __half* gr, float* dw, Vol vx, V
                 }
             }
             cons.next(s);
+            ++ci;
         }
     }
     for (int k = 0; k < KC; ++k) {
@@ -166,8 +163,7 @@ static int emu_wgrad_cfg(const __half* x, const __half* gr, float* dw, Vol vx, V
         using Cfg = FCfg<CS, DT, WT, M, CP, ST, MINB>;                                                              \
         const __half *xh = (const __half*)x, *wh = (const __half*)w;                                                \
         if (mode == 0) return emu_fprop_cfg<Cfg, 0>(xh, wh, (__half*)y, vx, vy, h_begin, h_end, y_h0, grid);        \
-        if (mode == 1) return emu_fprop_cfg<Cfg, 1>(xh, wh, (__half*)y, vx, vy, h_begin, h_end, y_h0, grid);        \
-        return emu_fprop_cfg<Cfg, 2>(xh, wh, (__half*)y, vx, vy, h_begin, h_end, y_h0, grid);                       \
+        return emu_fprop_cfg<Cfg, 1>(xh, wh, (__half*)y, vx, vy, h_begin, h_end, y_h0, grid);                       \
     }
 #define EMU_WV(ID, CS, DT, WT, M, CP, ST, MINB)                                                                  \
     case ID:                                                                                                     \

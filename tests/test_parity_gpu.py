@@ -150,7 +150,7 @@ def test_all_fprop_variants(ops, kdw_lib):
             for (N, H, W, D) in [(2, 5, 19, 37), (1, 21, 9, 130)]:
                 x, _, w = make_inputs(31 * v + C, N, C, H, W, D)
                 ref = to.fprop_shift_fp32(x, w)
-                for acc in ('float32', 'float16', 'float32_plane'):
+                for acc in ('float32', 'float16'):
                     y = torch.full_like(x, float('nan'))
                     _launch.fprop(x, w, y, acc=acc, tune=v)
                     check_fprop(y, ref, strict=(acc == 'float32'))
@@ -171,7 +171,6 @@ def test_acctype_float16_keyword(ops):
     DWConv, _, _ = ops
     x, _, w = make_inputs(77, 1, 16, 20, 21, 22)
     check_fprop(DWConv(x, w, ACCTYPE='float16'), to.fprop_shift_fp32(x, w), strict=False)
-    check_fprop(DWConv(x, w, ACCTYPE='float32_plane'), to.fprop_shift_fp32(x, w), strict=False)
 
 
 def test_plain_kernels_small_channel_counts(ops):
