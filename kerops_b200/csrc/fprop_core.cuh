@@ -52,7 +52,8 @@ struct FThread {
 // the a=1 taps, plane q-1 the a=2 taps.  The thread sweeps its M+2 input columns once; an input column j
 // feeds output m = j - b through tap b.  Carried between steps, per output m:
 //   MODE 0 (KDW_ACC_F32): P1 = fp32 sum of plane q's a=0 taps, P2 = fp32 sum of plane q-1's a=0,1 taps;
-//          every tap is one mixed-precision FMA (exact fp16 product, fp32 accumulate).
+//          every tap is one mixed-precision FMA (fp16 operands, exact product, fp32 accumulator), so the
+//          only rounding to fp16 is the final one.
 //   MODE 1 (KDW_ACC_F16): the same sums as packed-half chains (H1, H2), two channels per HFMA2.
 // When `store` is set the finished plane q-1 is written to the warp's output tile `ob`.
 template <class Cfg, int MODE>
