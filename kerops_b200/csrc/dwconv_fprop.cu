@@ -98,14 +98,11 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
     }
     __syncthreads();  // the only CTA-wide barrier: from here on the warps only meet through mbarriers
 
-    const long long lo = (long long)blockIdx.x * s.total / gridDim.x;
-    const long long hi = (long long)(blockIdx.x + 1) * s.total / gridDim.x;
-
     if (warp == NCW) {
         // ---------------- producer warp: one lane streams the input planes of the CTA's range ----------------
         if (lane != 0) return;
         StepIter it;
-        it.init(s, lo, hi);
+        it.init(s, (int)blockIdx.x, (int)gridDim.x);
         uint32_t pi = 0;
         bool ok = true;
         while (it.active && ok) {
@@ -131,7 +128,7 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
     const FThread<Cfg> th(tid);
     unsigned char* my_out = out_base + warp * 2 * Cfg::OUTW_BYTES;
     StepIter it;
-    it.init(s, lo, hi);
+    it.init(s, (int)blockIdx.x, (int)gridDim.x);
 
     __half2 wgt[27][CP];           // taps of this thread's channels
     float2 P1[M][CP], P2[M][CP];   // carried fp32 partial sums (see fprop_step)

@@ -12,7 +12,7 @@
 // each product one sm_100 mixed-precision FMA (fp16 operands, exact product, fp32 accumulator).  At the end
 // of a segment the consumer warps reduce over their threads (warp shuffles, then warps in fixed order
 // through shared memory) and add the [27][CS] result to the CTA's own fp32 row of the workspace.
-// Pass 2 adds the rows in CTA order and writes the fp32 and fp16 [3][3][3][C] results.
+// Pass 2 adds the rows in a fixed order and writes the fp32 and fp16 [3][3][3][C] results.
 // There are no atomics anywhere, so results are bitwise reproducible.
 //
 // Plain pass 1 (any C, used for C < 8): one thread per (tap, channel), fp32 FMAs.
@@ -27,14 +27,21 @@ static constexpr int kMaxRowsFloor = 1184;  // workspace rows are max(8 * SMs, t
 // ------------------------------------------------------------------------------------------------
 // Pass 2: fixed-order sum over the CTA rows
 // ------------------------------------------------------------------------------------------------
+// One warp per output element k: lane l adds rows l, l+32, ... in order, then the 32 lane sums are combined
+// by a fixed shuffle tree - the same order on every run.
 __global__ void __launch_bounds__(128) wgrad_reduce_kernel(const float* __restrict__ ws, int rows, int KC,
                                                           float* __restrict__ dw32, __half* __restrict__ dw16) {
-    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    const int k = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
     if (k >= KC) return;
     float acc = 0.f;
-    for (int r = 0; r < rows; ++r) acc += ws[(size_t)r * KC + k];
-    if (dw32) dw32[k] = acc;
-    if (dw16) dw16[k] = __float2half_rn(acc);
+    for (int r = lane; r < rows; r += 32) acc += ws[(size_t)r * KC + k];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) {
+        if (dw32) dw32[k] = acc;
+        if (dw16) dw16[k] = __float2half_rn(acc);
+    }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -103,14 +110,11 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
     for (int k = tid; k < KC; k += Cfg::NT + 32) row[k] = 0.f;
     __syncthreads();  // the only CTA-wide barrier
 
-    const long long lo = (long long)blockIdx.x * s.total / gridDim.x;
-    const long long hi = (long long)(blockIdx.x + 1) * s.total / gridDim.x;
-
     if (warp == NCW) {
         // ---------------- producer warp ----------------
         if (lane != 0) return;
         StepIter it;
-        it.init(s, lo, hi);
+        it.init(s, (int)blockIdx.x, (int)gridDim.x);
         uint32_t pi = 0;
         bool ok = true;
         while (it.active) {
@@ -140,7 +144,7 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
     const WThread<Cfg> th(tid);
     const int cg = th.cg;
     StepIter it;
-    it.init(s, lo, hi);
+    it.init(s, (int)blockIdx.x, (int)gridDim.x);
 
     __half2 G[3][M][CP];
     float2 acc[27][CP];
@@ -376,7 +380,7 @@ static int wgrad_dispatch(const void* x, const void* grad, void* workspace, int6
         rc = v.f(a, &rows);
         if (rc) return rc;
     }
-    wgrad_reduce_kernel<<<(KC + 127) / 128, 128, 0, st>>>(ws, rows, KC, dw_f32, (__half*)dw_f16);
+    wgrad_reduce_kernel<<<(KC + 3) / 4, 128, 0, st>>>(ws, rows, KC, dw_f32, (__half*)dw_f16);
     KDW_CUDA(cudaGetLastError());
     return 0;
 }

@@ -48,16 +48,23 @@ int device_sm_count(int* sms);
 // Device address (on the current device) of the library's status word.
 int status_ptr(int** p);
 
-// Work decomposition shared by fprop and wgrad (see decode_segment).
+// Work decomposition shared by fprop and wgrad.  A COLUMN is (sample, w-tile, d-tile, channel-slice); a CTA
+// marches a column along h.  With G CTAs and K columns:
+//   * the first R = K / G "rounds" give CTA g the whole column r*G + g, so at any time the G resident CTAs
+//     work on G neighbouring columns at about the same h and their halos hit in L2;
+//   * the remaining K - R*G columns are cut along h into chunks, the (chunk, column, plane) space is
+//     linearised and split into G equal ranges (+-1 plane), so the tail is balanced too.
 struct Sched {
-    long long total;  // N * Kc * Hr plane units
-    int Kc;           // columns per sample = nWT * nDT * nCS
-    int Hr;           // planes in [h_begin, h_end)
-    int PH;           // planes per h-chunk
-    int nh;           // h-chunks
+    long long rem_total;  // plane units of the remainder phase = Krem * Hr
+    int R;                // full rounds
+    int Krem;             // columns of the remainder phase
+    int Kc;               // columns per sample = nWT * nDT * nCS
+    int Hr;               // planes in [h_begin, h_end)
+    int PH;               // planes per h-chunk (remainder phase)
+    int nh;               // h-chunks (remainder phase)
     int nWT, nDT, nCS;
     int h_begin;
-    int WT, DT, CS;   // tile extents (w, d, channels)
+    int WT, DT, CS;       // tile extents (w, d, channels)
 };
 
 // Fills the schedule for `grid_target` CTAs; returns the grid size to launch.
@@ -76,60 +83,70 @@ struct Seg {
     int hb, he;         // owned planes [hb, he)
 };
 
-// Decodes the segment that starts at linear position `pos` (< end); returns the number of plane
-// units it covers.  Linear order: sample, h-chunk, w-tile, d-tile, channel-slice, plane-in-chunk.
-KDW_HD int decode_segment(const Sched& s, long long pos, long long end, Seg& g) {
-    const long long per_n = (long long)s.Kc * s.Hr;
-    const int n = (int)(pos / per_n);
-    const long long r = pos - (long long)n * per_n;
-    const long long chunk_units = (long long)s.Kc * s.PH;
-    int j = (int)(r / chunk_units);
-    if (j > s.nh - 1) j = s.nh - 1;
-    const int len = (j < s.nh - 1) ? s.PH : s.Hr - (s.nh - 1) * s.PH;
-    const long long r2 = r - (long long)j * chunk_units;
-    int col = (int)(r2 / len);
-    const int p = (int)(r2 - (long long)col * len);
-    long long take = len - p;
-    if (take > end - pos) take = end - pos;
+// Column index over all samples -> sample and tile origin.  Order: channel-slice fastest, then d-tile, w-tile, sample.
+KDW_HD void decode_column(const Sched& s, int col_all, Seg& g) {
+    g.n = col_all / s.Kc;
+    int col = col_all - g.n * s.Kc;
     const int ics = col % s.nCS;
     col /= s.nCS;
     const int idt = col % s.nDT;
     const int iwt = col / s.nDT;
-    g.n = n;
     g.w0 = iwt * s.WT;
     g.d0 = idt * s.DT;
     g.c0 = ics * s.CS;
+}
+
+// Remainder phase: decodes the segment that starts at linear position `pos` (< end) of the (h-chunk, column,
+// plane) space; returns the number of plane units it covers.
+KDW_HD int decode_remainder(const Sched& s, int first_col, long long pos, long long end, Seg& g) {
+    const long long chunk_units = (long long)s.Krem * s.PH;
+    int j = (int)(pos / chunk_units);
+    if (j > s.nh - 1) j = s.nh - 1;
+    const int len = (j < s.nh - 1) ? s.PH : s.Hr - (s.nh - 1) * s.PH;
+    const long long r2 = pos - (long long)j * chunk_units;
+    const int col = (int)(r2 / len);
+    const int p = (int)(r2 - (long long)col * len);
+    long long take = len - p;
+    if (take > end - pos) take = end - pos;
+    decode_column(s, first_col + col, g);
     g.hb = s.h_begin + j * s.PH + p;
     g.he = g.hb + (int)take;
     return (int)take;
 }
 
-// Walks the input planes hb-1 .. he of every segment of a CTA's range.
+// Walks the input planes hb-1 .. he of every segment of CTA `cta` of `ncta`.
 struct StepIter {
-    long long pos, end;
+    long long pos, end;  // remainder-phase range still to decode
+    int r, cta, ncta;    // next full round
     Seg g;
     int q;
     bool active;
     KDW_HD void next_segment(const Sched& s) {
-        if (pos < end) {
-            pos += decode_segment(s, pos, end, g);
+        if (r < s.R) {
+            decode_column(s, r * ncta + cta, g);
+            g.hb = s.h_begin;
+            g.he = s.h_begin + s.Hr;
+            ++r;
+            q = g.hb - 1;
+            active = true;
+        } else if (pos < end) {
+            pos += decode_remainder(s, s.R * ncta, pos, end, g);
             q = g.hb - 1;
             active = true;
         } else {
             active = false;
         }
     }
-    KDW_HD void init(const Sched& s, long long p, long long e) {
-        pos = p;
-        end = e;
+    KDW_HD void init(const Sched& s, int cta_, int ncta_) {
+        cta = cta_;
+        ncta = ncta_;
+        r = 0;
+        pos = (long long)cta_ * s.rem_total / ncta_;
+        end = (long long)(cta_ + 1) * s.rem_total / ncta_;
         next_segment(s);
     }
     KDW_HD void next(const Sched& s) {
         if (++q > g.he) next_segment(s);
-    }
-    // bit a set <=> the owned-plane test holds for plane q + 1 - a
-    KDW_HD int amask() const {
-        return ((q + 1 < g.he) ? 1 : 0) | ((q >= g.hb && q < g.he) ? 2 : 0) | ((q - 1 >= g.hb) ? 4 : 0);
     }
 };
 

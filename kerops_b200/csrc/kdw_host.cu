@@ -104,17 +104,26 @@ int make_sched(Sched* s, int64_t N, int64_t C, int64_t W, int64_t D, int h_begin
     s->Kc = s->nWT * s->nDT * s->nCS;
     s->Hr = h_end - h_begin;
     s->h_begin = h_begin;
-    s->total = (long long)N * s->Kc * s->Hr;
+    const long long Kall = (long long)N * s->Kc;
+    const long long total = Kall * s->Hr;
     long long grid = grid_target;
-    if (grid > s->total) grid = s->total;
+    if (grid > total) grid = total;
     if (grid < 1) grid = 1;
-    // planes per CTA; chunk the h range so that one chunk of all columns ~ a whole number of CTA shares
-    const double ppc = (double)s->total / (double)grid;
-    long long nh = (long long)((double)s->Hr / ppc + 0.5);
-    if (nh < 1) nh = 1;
-    if (nh > s->Hr) nh = s->Hr;
-    s->PH = (int)((s->Hr + nh - 1) / nh);
-    s->nh = (s->Hr + s->PH - 1) / s->PH;
+    s->R = (int)(Kall / grid);
+    s->Krem = (int)(Kall - (long long)s->R * grid);
+    s->rem_total = (long long)s->Krem * s->Hr;
+    s->PH = s->Hr;
+    s->nh = 1;
+    if (s->Krem > 0) {
+        // planes per CTA in the remainder; chunk the h range so that one chunk row of all remaining columns is
+        // about a whole number of CTA shares
+        const double ppc = (double)s->rem_total / (double)grid;
+        long long nh = (long long)((double)s->Hr / ppc + 0.5);
+        if (nh < 1) nh = 1;
+        if (nh > s->Hr) nh = s->Hr;
+        s->PH = (int)((s->Hr + nh - 1) / nh);
+        s->nh = (s->Hr + s->PH - 1) / s->PH;
+    }
     return (int)grid;
 }
 

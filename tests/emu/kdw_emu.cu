@@ -59,10 +59,9 @@ static int emu_fprop_cfg(const __half* x, const __half* w, __half* y, Vol vx, Vo
     std::vector<__half> out((size_t)Cfg::NCW * Cfg::OUTW_BYTES / 2);  // one tile per consumer warp
     std::vector<TState> ts(Cfg::NT);
     for (int blk = 0; blk < grid; ++blk) {
-        const long long lo = (long long)blk * s.total / grid, hi = (long long)(blk + 1) * s.total / grid;
         memset(ts.data(), 0, sizeof(TState) * ts.size());
         StepIter cons;
-        cons.init(s, lo, hi);
+        cons.init(s, blk, grid);
         while (cons.active) {
             const int q = cons.q;
             const Seg& g = cons.g;
@@ -108,11 +107,10 @@ static int emu_wgrad_cfg(const __half* x, const __half* gr, float* dw, Vol vx, V
     std::vector<__half> xs(Cfg::X_BYTES / 2), gs(Cfg::G_BYTES / 2);
     std::vector<TState> ts(Cfg::NT);
     for (int blk = 0; blk < grid; ++blk) {
-        const long long lo = (long long)blk * s.total / grid, hi = (long long)(blk + 1) * s.total / grid;
         memset(ts.data(), 0, sizeof(TState) * ts.size());
         float* row = rows.data() + (size_t)blk * KC;
         StepIter cons;
-        cons.init(s, lo, hi);
+        cons.init(s, blk, grid);
         unsigned ci = 0;
         while (cons.active) {
             const int q = cons.q;

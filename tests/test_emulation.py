@@ -33,6 +33,10 @@ SHAPES = [
     (1, 16, 7, 17, 3, 1),
     (1, 128, 2, 3, 11, 11),
     (1, 8, 9, 3, 70, 6),
+    # many columns, few CTAs: whole-column rounds followed by a split remainder
+    (1, 8, 5, 40, 70, 4),
+    (2, 16, 3, 20, 40, 5),
+    (1, 32, 4, 17, 33, 7),
 ]
 
 
