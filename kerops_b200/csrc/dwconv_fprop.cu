@@ -4,10 +4,10 @@
 // (kerops/ops/conv/dwconv.py:42-61).
 //
 // TMA kernel (C multiple of 8).  A CTA owns a column (w-tile x d-tile x channel-slice) and marches
-// along h.  One thread streams ONE halo'd input plane [(WT+2) x (DT+2) x CS] per step into a ring of
+// along h.  A producer warp streams ONE halo'd input plane [(WT+2) x (DT+2) x CS] per step into a ring of
 // shared-memory stages by tiled TMA loads (zero fill outside the volume = the padding on all three
-// axes); full/empty mbarriers are the only synchronisation between the loads and the warps.  Every
-// thread - fixed (channel pairs, d), M consecutive w positions - applies the plane to the three
+// axes); full/empty mbarriers are the only synchronisation between it and the consumer warps.  Every
+// consumer thread - fixed (channel pairs, d), M consecutive w positions - applies the plane to the three
 // output planes that use it (plane q+1 gets the a=0 taps, plane q the a=1 taps, plane q-1 the a=2 taps)
 // and carries the unfinished sums in registers, so each input plane is read from shared memory exactly
 // once and the 27 x (channel pairs) taps stay in registers.  KDW_ACC_F32 uses the sm_100 mixed-precision
@@ -74,14 +74,14 @@ __global__ void __launch_bounds__(256) fprop_plain_kernel(const __half* __restri
 // TMA kernel
 // ------------------------------------------------------------------------------------------------
 template <class Cfg, int MODE>
-__global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
+__global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
     fprop_tma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
                      const __half* __restrict__ weight, const Sched s, const int C, const int y_h0, int* status) {
     constexpr int M = Cfg::M, CP = Cfg::CP, ST = Cfg::ST, NCW = Cfg::NCW;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
     unsigned char* in_base = smem;                         // ST input stages
-    unsigned char* out_base = smem + ST * Cfg::IN_STRIDE;  // per warp: two output tiles
+    unsigned char* out_base = smem + ST * Cfg::IN_STRIDE;  // per consumer warp: two output tiles
     const uint32_t full0 = smem_u32(out_base + 2 * NCW * Cfg::OUTW_BYTES);  // full[ST], then empty[ST]
     const uint32_t empty0 = full0 + 8 * ST;
 
@@ -92,47 +92,45 @@ __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
         prefetch_tmap(&tmy);
         for (int k = 0; k < ST; ++k) {
             mbar_init(full0 + 8 * k, 1);     // the producer's arrive.expect_tx
-            mbar_init(empty0 + 8 * k, NCW);  // one arrive per warp
+            mbar_init(empty0 + 8 * k, NCW);  // one arrive per consumer warp
         }
         mbar_fence_init();
     }
     __syncthreads();  // the only CTA-wide barrier: from here on the warps only meet through mbarriers
 
-    // Thread 0 doubles as the TMA producer.  It walks the same plane sequence as the consumers, `pi` loads
-    // ahead.  issue(blocking): stage pi % ST can be refilled once every warp has released its previous use.
-    StepIter pit;
-    pit.active = false;
-    uint32_t pi = 0;
-    if (tid == 0) pit.init(s, (int)blockIdx.x, (int)gridDim.x);
-    auto issue = [&](bool blocking) -> bool {
-        if (!pit.active) return false;
-        const uint32_t st = pi % ST;
-        if (pi >= ST) {
-            const uint32_t par = ((pi / ST) & 1u) ^ 1u;
-            if (blocking) {
-                if (!mbar_wait_bounded(empty0 + 8 * st, par)) {
-                    atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
-                    return false;
-                }
-            } else if (!mbar_try_wait(empty0 + 8 * st, par)) {
-                return false;
-            }
+    if (warp == NCW) {
+        // ---------------- producer warp: one lane streams the input planes of the CTA's range ----------------
+        if (lane != 0) return;
+        StepIter it;
+        it.init(s, (int)blockIdx.x, (int)gridDim.x);
+        uint32_t pi = 0;
+        bool ok = true;
+        while (it.active && ok) {
+            const uint32_t st = pi % ST;
+            if (pi >= ST) ok = mbar_wait_bounded(empty0 + 8 * st, ((pi / ST) & 1u) ^ 1u);  // consumers released it
+            if (!ok) break;
+            mbar_expect_tx(full0 + 8 * st, Cfg::IN_BYTES);
+            tma_load_5d(status, smem_u32(in_base + st * Cfg::IN_STRIDE), &tmx, full0 + 8 * st, it.g.c0, it.g.d0 - 1,
+                        it.g.w0 - 1, it.q, it.g.n);
+            ++pi;
+            it.next(s);
         }
-        mbar_expect_tx(full0 + 8 * st, Cfg::IN_BYTES);
-        tma_load_5d(status, smem_u32(in_base + st * Cfg::IN_STRIDE), &tmx, full0 + 8 * st, pit.g.c0, pit.g.d0 - 1,
-                    pit.g.w0 - 1, pit.q, pit.g.n);
-        ++pi;
-        pit.next(s);
-        return true;
-    };
+        if (!ok) {
+            atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
+            // loads already issued still target this CTA's shared memory: give them a bounded chance to land
+            const uint32_t first = pi > ST ? pi - ST : 0;
+            for (uint32_t k = first; k < pi; ++k) (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u);
+        }
+        return;
+    }
 
+    // ---------------- consumer warps ----------------
     const FThread<Cfg> th(tid);
     unsigned char* my_out = out_base + warp * 2 * Cfg::OUTW_BYTES;
     StepIter it;
     it.init(s, (int)blockIdx.x, (int)gridDim.x);
 
-    __half2 wgt[27][CP];           // taps of this thread's channel pairs, packed (MODE 1)
-    __half wl[27][CP], wh[27][CP];  // the same taps, one channel per register (MODE 0)
+    __half2 wgt[27][CP];           // taps of this thread's channels
     float2 P1[M][CP], P2[M][CP];   // carried fp32 partial sums (see fprop_step)
     __half2 H1[M][CP], H2[M][CP];  // carried packed-half partial sums
 #pragma unroll
@@ -146,24 +144,14 @@ __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
     uint32_t ci = 0;  // steps consumed
     uint32_t oc = 0;  // planes stored by this warp
     while (it.active) {
-        if (tid == 0) {
-            while (pi <= ci && pit.active)  // the load of this step must be on its way before anyone waits for it
-                if (!issue(true)) break;
-            while (pi < ci + ST && issue(false)) {  // refill whatever stages the other warps have released
-            }
-        }
-        __syncwarp();
         const int q = it.q;
         if (q == it.g.hb - 1) {  // new segment: this thread's taps for the segment's channel slice
             const __half* wp = weight + it.g.c0 + th.cg * 2 * CP;
 #pragma unroll
             for (int k = 0; k < 27; ++k)
 #pragma unroll
-                for (int i = 0; i < CP; ++i) {
+                for (int i = 0; i < CP; ++i)
                     wgt[k][i] = *reinterpret_cast<const __half2*>(wp + (size_t)k * C + 2 * i);
-                    wl[k][i] = __low2half(wgt[k][i]);
-                    wh[k][i] = __high2half(wgt[k][i]);
-                }
         }
         const uint32_t st = ci % ST;
         const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u);
@@ -176,7 +164,7 @@ __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
         if (store && lane == 0) tma_wait_read<1>();  // the store issued two planes ago has released this tile
         __syncwarp();
         const __half* in = reinterpret_cast<const __half*>(in_base + st * Cfg::IN_STRIDE) + th.in_off;
-        fprop_step<Cfg, MODE>(in, reinterpret_cast<__half*>(ob_bytes) + th.out_off, store, wgt, wl, wh, P1, P2, H1, H2);
+        fprop_step<Cfg, MODE>(in, reinterpret_cast<__half*>(ob_bytes) + th.out_off, store, wgt, P1, P2, H1, H2);
         if (store) fence_proxy_async_smem();  // the tile must be visible to the TMA store
         __syncwarp();
         if (lane == 0) {
@@ -192,10 +180,6 @@ __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
         ++ci;
     }
     if (lane == 0) tma_wait_all();
-    if (tid == 0 && pi > ci) {
-        // left early (timeout): loads already issued still target this CTA's shared memory
-        for (uint32_t k = ci; k < pi; ++k) (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u);
-    }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -225,7 +209,7 @@ static int launch_fprop_tma(const FpropArgs& a) {
     auto kern = fprop_tma_kernel<Cfg, MODE>;
     KDW_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     int occ = 0, sms = 0;
-    KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::NT, Cfg::SMEM));
+    KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::NT + 32, Cfg::SMEM));
     if (occ < 1) {
         set_error("fprop kernel variant does not fit on this device");
         return KDW_ERR_TUNE;
@@ -237,7 +221,7 @@ static int launch_fprop_tma(const FpropArgs& a) {
     if (rc) return rc;
     Sched s;
     const int grid = make_sched(&s, a.N, a.C, a.W, a.D, a.h_begin, a.h_end, Cfg::WT, Cfg::DT, Cfg::CS, sms * occ);
-    kern<<<grid, Cfg::NT, Cfg::SMEM, a.stream>>>(tmx, tmy, (const __half*)a.w, s, (int)a.C, a.y_h0, status);
+    kern<<<grid, Cfg::NT + 32, Cfg::SMEM, a.stream>>>(tmx, tmy, (const __half*)a.w, s, (int)a.C, a.y_h0, status);
     KDW_CUDA(cudaGetLastError());
     return 0;
 }
@@ -259,10 +243,12 @@ static const FpropVariant g_fprop_variants[] = {
 static const int g_n_fprop_variants = (int)(sizeof(g_fprop_variants) / sizeof(g_fprop_variants[0]));
 
 static int auto_fprop_variant(int64_t C) {
+    // fastest KDW_ACC_F32 variant measured at (1, C, 350, 350, 128) on B200
     if (C == 8) return 1;
-    if (C == 16) return 2;
-    if (C == 32) return 3;
-    return 4;
+    if (C == 16) return 10;
+    if (C == 32) return 11;
+    if (C == 64) return 11;
+    return 6;
 }
 
 static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N, int64_t C, int64_t Hx, int64_t W,

@@ -3,14 +3,14 @@
 // Replaces kerops/kernels/dw_conv.py:147-287 (_DWConv_wgrad_cl3d_impl), the zero-filled fp16 partial
 // buffer and the torch sum over it (kerops/ops/conv/dwconv_wgrad.py:54-77).
 //
-// Pass 1 (TMA kernel, C multiple of 8).  Same column march as the forward kernel: one thread streams,
+// Pass 1 (TMA kernel, C multiple of 8).  Same column march as the forward kernel: a producer warp streams,
 // per step, the halo'd x plane q and the grad plane q+1 into a ring of shared-memory stages by TMA; full /
-// empty mbarriers connect the loads to the warps.  A thread - fixed (channel pairs, d), M
+// empty mbarriers connect it to the consumer warps.  A consumer thread - fixed (channel pairs, d), M
 // consecutive w positions - keeps the grad values of planes q-1, q, q+1 in registers and multiplies every x
 // value it reads with the (up to) nine grad values whose tap it is:
 //     dw[a][b][t] += grad[q+1-a][m] * x[q][m+b][d+t],
 // each product one sm_100 mixed-precision FMA (fp16 operands, exact product, fp32 accumulator).  At the end
-// of a segment the warps reduce over their threads (warp shuffles, then warps in fixed order
+// of a segment the consumer warps reduce over their threads (warp shuffles, then warps in fixed order
 // through shared memory) and add the [27][CS] result to the CTA's own fp32 row of the workspace.
 // Pass 2 adds the rows in a fixed order and writes the fp32 and fp16 [3][3][3][C] results.
 // There are no atomics anywhere, so results are bitwise reproducible.
@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(128) wgrad_plain_kernel(const __half* __restri
 // TMA pass 1
 // ------------------------------------------------------------------------------------------------
 template <class Cfg>
-__global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
+__global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
     wgrad_tma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmg,
                      float* __restrict__ ws, const Sched s, const int C, const int g_h0, int* status) {
     constexpr int CS = Cfg::CS, M = Cfg::M, CP = Cfg::CP, ST = Cfg::ST, CPG = Cfg::CPG, NCW = Cfg::NCW;
@@ -107,92 +107,87 @@ __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
         }
         mbar_fence_init();
     }
-    for (int k = tid; k < KC; k += Cfg::NT) row[k] = 0.f;
-    __syncthreads();
+    for (int k = tid; k < KC; k += Cfg::NT + 32) row[k] = 0.f;
+    __syncthreads();  // the only CTA-wide barrier
 
-    // Thread 0 doubles as the TMA producer (see the forward kernel): per step the x plane q and, when the
-    // segment owns it, the grad plane q+1.
-    StepIter pit;
-    pit.active = false;
-    uint32_t pi = 0;
-    if (tid == 0) pit.init(s, (int)blockIdx.x, (int)gridDim.x);
-    auto issue = [&](bool blocking) -> bool {
-        if (!pit.active) return false;
-        const uint32_t st = pi % ST;
-        if (pi >= ST) {
-            const uint32_t par = ((pi / ST) & 1u) ^ 1u;
-            if (blocking) {
-                if (!mbar_wait_bounded(empty0 + 8 * st, par)) {
-                    atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
-                    return false;
-                }
-            } else if (!mbar_try_wait(empty0 + 8 * st, par)) {
-                return false;
-            }
+    if (warp == NCW) {
+        // ---------------- producer warp ----------------
+        if (lane != 0) return;
+        StepIter it;
+        it.init(s, (int)blockIdx.x, (int)gridDim.x);
+        uint32_t pi = 0;
+        bool ok = true;
+        while (it.active) {
+            const uint32_t st = pi % ST;
+            if (pi >= ST) ok = mbar_wait_bounded(empty0 + 8 * st, ((pi / ST) & 1u) ^ 1u);
+            if (!ok) break;
+            const bool with_g = it.q + 1 < it.g.he;  // grad plane q+1 is owned by the segment
+            const uint32_t bar = full0 + 8 * st;
+            mbar_expect_tx(bar, Cfg::X_BYTES + (with_g ? Cfg::G_BYTES : 0));
+            tma_load_5d(status, smem_u32(stage_base + st * Cfg::STAGE), &tmx, bar, it.g.c0, it.g.d0 - 1, it.g.w0 - 1,
+                        it.q, it.g.n);
+            if (with_g)
+                tma_load_5d(status, smem_u32(stage_base + st * Cfg::STAGE + Cfg::X_STRIDE), &tmg, bar, it.g.c0, it.g.d0,
+                            it.g.w0, it.q + 1 - g_h0, it.g.n);
+            ++pi;
+            it.next(s);
         }
-        const bool with_g = pit.q + 1 < pit.g.he;  // grad plane q+1 is owned by the segment
-        const uint32_t bar = full0 + 8 * st;
-        mbar_expect_tx(bar, Cfg::X_BYTES + (with_g ? Cfg::G_BYTES : 0));
-        tma_load_5d(status, smem_u32(stage_base + st * Cfg::STAGE), &tmx, bar, pit.g.c0, pit.g.d0 - 1, pit.g.w0 - 1,
-                    pit.q, pit.g.n);
-        if (with_g)
-            tma_load_5d(status, smem_u32(stage_base + st * Cfg::STAGE + Cfg::X_STRIDE), &tmg, bar, pit.g.c0, pit.g.d0,
-                        pit.g.w0, pit.q + 1 - g_h0, pit.g.n);
-        ++pi;
-        pit.next(s);
-        return true;
-    };
+        if (!ok) {
+            atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
+            const uint32_t first = pi > ST ? pi - ST : 0;
+            for (uint32_t k = first; k < pi; ++k) (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u);
+        }
+        return;
+    }
 
+    // ---------------- consumer warps ----------------
     const WThread<Cfg> th(tid);
     const int cg = th.cg;
     StepIter it;
     it.init(s, (int)blockIdx.x, (int)gridDim.x);
 
-    __half Gl[3][M][CP], Gh[3][M][CP];
+    __half2 G[3][M][CP];
     float2 acc[27][CP];
+#pragma unroll
+    for (int m = 0; m < M; ++m)
+#pragma unroll
+        for (int i = 0; i < CP; ++i) G[0][m][i] = G[1][m][i] = G[2][m][i] = __float2half2_rn(0.f);
 #pragma unroll
     for (int k = 0; k < 27; ++k)
 #pragma unroll
         for (int i = 0; i < CP; ++i) acc[k][i] = make_float2(0.f, 0.f);
 
     uint32_t ci = 0;
+    bool failed = false;
     while (it.active) {
-        if (tid == 0) {
-            while (pi <= ci && pit.active)
-                if (!issue(true)) break;
-            while (pi < ci + ST && issue(false)) {
-            }
-        }
-        __syncwarp();
         const uint32_t st = ci % ST;
         const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u);
         if (__any_sync(0xffffffffu, !ok)) {
             if (lane == 0) atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
+            failed = true;
             break;
         }
         const int q = it.q;
         if (q == it.g.hb - 1) {
             // new segment: grad planes of the previous segment must not be paired with this segment's x
 #pragma unroll
-            for (int r = 0; r < 3; ++r)
+            for (int m = 0; m < M; ++m)
 #pragma unroll
-                for (int m = 0; m < M; ++m)
-#pragma unroll
-                    for (int i = 0; i < CP; ++i) Gl[r][m][i] = Gh[r][m][i] = __float2half(0.f);
+                for (int i = 0; i < CP; ++i) G[0][m][i] = G[1][m][i] = G[2][m][i] = __float2half2_rn(0.f);
         }
         const bool load_g = q + 1 < it.g.he;
         const __half* xin = reinterpret_cast<const __half*>(stage_base + st * Cfg::STAGE) + th.x_off;
         const __half* gin = reinterpret_cast<const __half*>(stage_base + st * Cfg::STAGE + Cfg::X_STRIDE) + th.g_off;
         switch (ci % 3) {
-            case 0: wgrad_step<Cfg, 0>(xin, gin, load_g, Gl, Gh, acc); break;
-            case 1: wgrad_step<Cfg, 1>(xin, gin, load_g, Gl, Gh, acc); break;
-            default: wgrad_step<Cfg, 2>(xin, gin, load_g, Gl, Gh, acc); break;
+            case 0: wgrad_step<Cfg, 0>(xin, gin, load_g, G, acc); break;
+            case 1: wgrad_step<Cfg, 1>(xin, gin, load_g, G, acc); break;
+            default: wgrad_step<Cfg, 2>(xin, gin, load_g, G, acc); break;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + 8 * st);  // this warp is done with the stage
         if (q == it.g.he) {
-            // Segment finished: reduce over the threads that share channels, then add the [27][CS] result to
-            // the CTA's workspace row.  Warps take turns in a fixed order (no atomics).
+            // Segment finished: reduce over the consumer threads that share channels, then add the [27][CS]
+            // result to the CTA's workspace row.  Warps take turns in a fixed order (no atomics).
             const int c0 = it.g.c0;
 #pragma unroll
             for (int k = 0; k < 27; ++k)
@@ -222,13 +217,13 @@ __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
                             }
                         }
                 }
-                __syncthreads();
+                named_barrier_sync(1, Cfg::NT);
             }
             for (int e = tid; e < 27 * CS; e += Cfg::NT) {
                 const int k = e / CS, c = e % CS;
                 row[k * C + c0 + c] += red[e];
             }
-            __syncthreads();
+            named_barrier_sync(1, Cfg::NT);
 #pragma unroll
             for (int k = 0; k < 27; ++k)
 #pragma unroll
@@ -237,10 +232,7 @@ __global__ void __launch_bounds__(Cfg::NT, Cfg::MINB)
         it.next(s);
         ++ci;
     }
-    if (tid == 0 && pi > ci) {
-        // left early (timeout): loads already issued still target this CTA's shared memory
-        for (uint32_t k = ci; k < pi; ++k) (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u);
-    }
+    (void)failed;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -267,7 +259,7 @@ static int launch_wgrad_tma(const WgradArgs& a, int* rows_used) {
     auto kern = wgrad_tma_kernel<Cfg>;
     KDW_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     int occ = 0, sms = 0;
-    KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::NT, Cfg::SMEM));
+    KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::NT + 32, Cfg::SMEM));
     if (occ < 1) {
         set_error("wgrad kernel variant does not fit on this device");
         return KDW_ERR_TUNE;
@@ -281,7 +273,7 @@ static int launch_wgrad_tma(const WgradArgs& a, int* rows_used) {
     if (target > a.ws_rows) target = a.ws_rows;
     Sched s;
     const int grid = make_sched(&s, a.N, a.C, a.W, a.D, a.h_begin, a.h_end, Cfg::WT, Cfg::DT, Cfg::CS, (int)target);
-    kern<<<grid, Cfg::NT, Cfg::SMEM, a.stream>>>(tmx, tmg, a.ws, s, (int)a.C, a.g_h0, status);
+    kern<<<grid, Cfg::NT + 32, Cfg::SMEM, a.stream>>>(tmx, tmg, a.ws, s, (int)a.C, a.g_h0, status);
     KDW_CUDA(cudaGetLastError());
     *rows_used = grid;
     return 0;
@@ -302,8 +294,8 @@ static const int g_n_wgrad_variants = (int)(sizeof(g_wgrad_variants) / sizeof(g_
 
 static int auto_wgrad_variant(int64_t C) {
     if (C <= 16) return 1;
-    if (C == 32) return 2;
-    return 3;
+    if (C == 32) return 3;
+    return 5;
 }
 
 static int64_t ws_rows_for_device(int* rc_out) {

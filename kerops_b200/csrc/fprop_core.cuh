@@ -16,8 +16,8 @@ struct FCfg {
     static constexpr int MINB = MINB_;  // CTAs per SM the register budget is set for
     static constexpr int CPG = CS / (2 * CP);  // threads that share a voxel
     static constexpr int WG = WT / M;
-    static constexpr int NT = CPG * DT * WG;   // threads
-    static constexpr int NCW = NT / 32;        // warps (all compute; lane 0 of warp 0 also issues the TMA loads)
+    static constexpr int NT = CPG * DT * WG;   // consumer threads
+    static constexpr int NCW = NT / 32;        // consumer warps; warp NCW is the TMA producer
     static constexpr int DPW = 32 / CPG;       // d positions covered by one warp
     static constexpr int IN_BYTES = (WT + 2) * (DT + 2) * CS * 2;
     static constexpr int IN_STRIDE = (IN_BYTES + 127) / 128 * 128;
@@ -25,7 +25,7 @@ struct FCfg {
     static constexpr int SMEM = ST * IN_STRIDE + 2 * NCW * OUTW_BYTES + 16 * ST + 128;
     static_assert(CS % (2 * CP) == 0 && WT % M == 0, "tile/thread shape");
     static_assert(CPG <= 32 && 32 % CPG == 0 && DT % DPW == 0, "a warp must cover whole voxels of one w group");
-    static_assert(NT % 32 == 0 && NT <= 1024, "thread count");
+    static_assert(NT % 32 == 0 && NT + 32 <= 1024, "thread count");
     static_assert(OUTW_BYTES % 128 == 0, "out tile alignment");
     static_assert(DT + 2 <= 256 && WT + 2 <= 256 && CS <= 256, "TMA box limits");
 };
@@ -53,14 +53,12 @@ struct FThread {
 // feeds output m = j - b through tap b.  Carried between steps, per output m:
 //   MODE 0 (KDW_ACC_F32): P1 = fp32 sum of plane q's a=0 taps, P2 = fp32 sum of plane q-1's a=0,1 taps;
 //          every tap is one mixed-precision FMA (fp16 operands, exact product, fp32 accumulator), so the
-//          only rounding to fp16 is the final one.  The taps are kept split (wl = even channel, wh = odd
-//          channel of a pair) so that no half has to be extracted in the inner loop.
+//          only rounding to fp16 is the final one.
 //   MODE 1 (KDW_ACC_F16): the same sums as packed-half chains (H1, H2), two channels per HFMA2.
 // When `store` is set the finished plane q-1 is written to the warp's output tile `ob`.
 template <class Cfg, int MODE>
 KDW_HD void fprop_step(const __half* __restrict__ in, __half* __restrict__ ob, bool store,
-                       const __half2 (&wgt)[27][Cfg::CP], const __half (&wl)[27][Cfg::CP],
-                       const __half (&wh)[27][Cfg::CP], float2 (&P1)[Cfg::M][Cfg::CP], float2 (&P2)[Cfg::M][Cfg::CP],
+                       const __half2 (&wgt)[27][Cfg::CP], float2 (&P1)[Cfg::M][Cfg::CP], float2 (&P2)[Cfg::M][Cfg::CP],
                        __half2 (&H1)[Cfg::M][Cfg::CP], __half2 (&H2)[Cfg::M][Cfg::CP]) {
     constexpr int CS = Cfg::CS, DT = Cfg::DT, M = Cfg::M, CP = Cfg::CP, DPW = Cfg::DPW;
     float2 F[3][3][CP];   // MODE 0: running fp32 sums of [a][output slot m % 3]
@@ -70,16 +68,6 @@ KDW_HD void fprop_step(const __half* __restrict__ in, __half* __restrict__ ob, b
         __half2 xv[3][CP];
 #pragma unroll
         for (int t = 0; t < 3; ++t) lds_h2<CP>(xv[t], in + (j * (DT + 2) + t) * CS);
-        __half xl[3][CP], xh[3][CP];  // MODE 0: the two channels of each pair, split once per read
-        if (MODE == 0) {
-#pragma unroll
-            for (int t = 0; t < 3; ++t)
-#pragma unroll
-                for (int i = 0; i < CP; ++i) {
-                    xl[t][i] = __low2half(xv[t][i]);
-                    xh[t][i] = __high2half(xv[t][i]);
-                }
-        }
 #pragma unroll
         for (int a = 0; a < 3; ++a) {
 #pragma unroll
@@ -88,21 +76,19 @@ KDW_HD void fprop_step(const __half* __restrict__ in, __half* __restrict__ ob, b
                 if (m < 0 || m >= M) continue;
 #pragma unroll
                 for (int i = 0; i < CP; ++i) {
-                    const int k0 = (a * 3 + b) * 3;
+                    const __half2 w0 = wgt[(a * 3 + b) * 3 + 0][i];
+                    const __half2 w1 = wgt[(a * 3 + b) * 3 + 1][i];
+                    const __half2 w2 = wgt[(a * 3 + b) * 3 + 2][i];
                     if (MODE == 0) {
                         float2 f;
                         if (b == 0)
                             f = (a == 0) ? make_float2(0.f, 0.f) : (a == 1 ? P1[m][i] : P2[m][i]);
                         else
                             f = F[a][m % 3][i];
-#pragma unroll
-                        for (int t = 0; t < 3; ++t) {
-                            f.x = fma_h_f(wl[k0 + t][i], xl[t][i], f.x);
-                            f.y = fma_h_f(wh[k0 + t][i], xh[t][i], f.y);
-                        }
-                        F[a][m % 3][i] = f;
+                        f = fma_h2_f2(w0, xv[0][i], f);
+                        f = fma_h2_f2(w1, xv[1][i], f);
+                        F[a][m % 3][i] = fma_h2_f2(w2, xv[2][i], f);
                     } else {
-                        const __half2 w0 = wgt[k0 + 0][i], w1 = wgt[k0 + 1][i], w2 = wgt[k0 + 2][i];
                         __half2 T;
                         if (b == 0) {
                             if (a == 0)

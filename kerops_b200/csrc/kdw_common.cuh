@@ -291,16 +291,6 @@ KDW_HD float2 fma_h2_f2(__half2 a, __half2 b, float2 c) {
 #endif
 }
 
-// Scalar form of the mixed-precision FMA: c + a * b with fp16 a, b held in the low half of a register each.
-KDW_HD float fma_h_f(__half a, __half b, float c) {
-#ifdef __CUDA_ARCH__
-    asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(c) : "h"(__half_as_ushort(a)), "h"(__half_as_ushort(b)));
-    return c;
-#else
-    return fmaf(__half2float(a), __half2float(b), c);
-#endif
-}
-
 // c + float(h), element-wise; on the device one sm_100 mixed-precision add per lane (no separate convert).
 KDW_HD float2 add_h2_f2(__half2 h, float2 c) {
 #ifdef __CUDA_ARCH__

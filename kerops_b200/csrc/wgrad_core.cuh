@@ -10,8 +10,8 @@ struct WCfg {
     static constexpr int CS = CS_, DT = DT_, WT = WT_, M = M_, CP = CP_, ST = ST_, MINB = MINB_;
     static constexpr int CPG = CS / (2 * CP);
     static constexpr int WG = WT / M;
-    static constexpr int NT = CPG * DT * WG;  // threads
-    static constexpr int NCW = NT / 32;       // warps (all compute; lane 0 of warp 0 also issues the TMA loads)
+    static constexpr int NT = CPG * DT * WG;  // consumer threads
+    static constexpr int NCW = NT / 32;       // consumer warps; warp NCW is the TMA producer
     static constexpr int X_BYTES = (WT + 2) * (DT + 2) * CS * 2;
     static constexpr int X_STRIDE = (X_BYTES + 127) / 128 * 128;
     static constexpr int G_BYTES = WT * DT * CS * 2;
@@ -19,7 +19,7 @@ struct WCfg {
     static constexpr int RED_BYTES = 27 * CS * 4;
     static constexpr int SMEM = ST * STAGE + RED_BYTES + 16 * ST + 128;
     static_assert(CS % (2 * CP) == 0 && WT % M == 0, "tile/thread shape");
-    static_assert(NT % 32 == 0 && NT <= 1024, "thread count");
+    static_assert(NT % 32 == 0 && NT + 32 <= 1024, "thread count");
     static_assert(CPG <= 32 && (CPG & (CPG - 1)) == 0, "channel groups must fit a warp");
     static_assert(G_BYTES % 128 == 0, "grad tile alignment");
     static_assert(DT + 2 <= 256 && WT + 2 <= 256 && CS <= 256, "TMA box limits");
@@ -41,44 +41,28 @@ struct WThread {
 // x plane q against the grad planes q+1 (tap a=0), q (a=1) and q-1 (a=2):
 //     acc[a][b][t] += grad[q+1-a][m] * x[q][m+b][d+t]      for the thread's M positions m,
 // every product one mixed-precision FMA (exact fp16 product, fp32 accumulate).  The three grad planes sit
-// in registers, the two channels of a pair in separate registers (Gl, Gh) so that no half has to be
-// extracted in the inner loop; R = (step count) % 3 says which slot holds which plane, so the window
-// slides without register moves: slot (R+2)%3 receives plane q+1 (zeros when that plane is not owned by
-// the segment), slot (R+1)%3 holds plane q, slot R holds plane q-1.
+// in registers G[.]; R = (step count) % 3 says which slot holds which plane, so the window slides without
+// register moves: slot (R+2)%3 receives plane q+1 (zeros when that plane is not owned by the segment),
+// slot (R+1)%3 holds plane q, slot R holds plane q-1.
 template <class Cfg, int R>
 KDW_HD void wgrad_step(const __half* __restrict__ xin, const __half* __restrict__ gin, bool load_g,
-                       __half (&Gl)[3][Cfg::M][Cfg::CP], __half (&Gh)[3][Cfg::M][Cfg::CP],
-                       float2 (&acc)[27][Cfg::CP]) {
+                       __half2 (&G)[3][Cfg::M][Cfg::CP], float2 (&acc)[27][Cfg::CP]) {
     constexpr int CS = Cfg::CS, DT = Cfg::DT, M = Cfg::M, CP = Cfg::CP;
     constexpr int SLOT[3] = {(R + 2) % 3, (R + 1) % 3, R % 3};  // slot of the grad plane paired with tap a
 #pragma unroll
     for (int m = 0; m < M; ++m) {
-        __half2 gv[CP];
         if (load_g) {
-            lds_h2<CP>(gv, gin + (m * DT) * CS);
+            lds_h2<CP>(G[SLOT[0]][m], gin + (m * DT) * CS);
         } else {
 #pragma unroll
-            for (int i = 0; i < CP; ++i) gv[i] = __float2half2_rn(0.f);
-        }
-#pragma unroll
-        for (int i = 0; i < CP; ++i) {
-            Gl[SLOT[0]][m][i] = __low2half(gv[i]);
-            Gh[SLOT[0]][m][i] = __high2half(gv[i]);
+            for (int i = 0; i < CP; ++i) G[SLOT[0]][m][i] = __float2half2_rn(0.f);
         }
     }
 #pragma unroll
     for (int j = 0; j < M + 2; ++j) {
-        __half xl[3][CP], xh[3][CP];
+        __half2 xv[3][CP];
 #pragma unroll
-        for (int t = 0; t < 3; ++t) {
-            __half2 xv[CP];
-            lds_h2<CP>(xv, xin + (j * (DT + 2) + t) * CS);
-#pragma unroll
-            for (int i = 0; i < CP; ++i) {
-                xl[t][i] = __low2half(xv[i]);
-                xh[t][i] = __high2half(xv[i]);
-            }
-        }
+        for (int t = 0; t < 3; ++t) lds_h2<CP>(xv[t], xin + (j * (DT + 2) + t) * CS);
 #pragma unroll
         for (int a = 0; a < 3; ++a) {
 #pragma unroll
@@ -90,8 +74,7 @@ KDW_HD void wgrad_step(const __half* __restrict__ xin, const __half* __restrict_
 #pragma unroll
                     for (int i = 0; i < CP; ++i) {
                         const int k = (a * 3 + b) * 3 + t;
-                        acc[k][i].x = fma_h_f(Gl[SLOT[a]][m][i], xl[t][i], acc[k][i].x);
-                        acc[k][i].y = fma_h_f(Gh[SLOT[a]][m][i], xh[t][i], acc[k][i].y);
+                        acc[k][i] = fma_h2_f2(G[SLOT[a]][m][i], xv[t][i], acc[k][i]);
                     }
                 }
             }

@@ -50,7 +50,6 @@ static int emu_fprop_cfg(const __half* x, const __half* w, __half* y, Vol vx, Vo
     constexpr int M = Cfg::M, CP = Cfg::CP;
     struct TState {
         __half2 wgt[27][CP];
-        __half wl[27][CP], wh[27][CP];
         float2 P1[M][CP], P2[M][CP];
         __half2 H1[M][CP], H2[M][CP];
     };
@@ -74,15 +73,11 @@ static int emu_fprop_cfg(const __half* x, const __half* w, __half* y, Vol vx, Vo
                 if (q == g.hb - 1) {
                     const __half* wp = w + g.c0 + th.cg * 2 * CP;
                     for (int k = 0; k < 27; ++k)
-                        for (int i = 0; i < CP; ++i) {
-                            t.wgt[k][i] = *reinterpret_cast<const __half2*>(wp + (size_t)k * vx.C + 2 * i);
-                            t.wl[k][i] = __low2half(t.wgt[k][i]);
-                            t.wh[k][i] = __high2half(t.wgt[k][i]);
-                        }
+                        for (int i = 0; i < CP; ++i) t.wgt[k][i] = *reinterpret_cast<const __half2*>(wp + (size_t)k * vx.C + 2 * i);
                 }
                 const __half* in = stage.data() + th.in_off;
                 __half* ob = out.data() + (size_t)(tid / 32) * (Cfg::OUTW_BYTES / 2) + th.out_off;
-                fprop_step<Cfg, MODE>(in, ob, store, t.wgt, t.wl, t.wh, t.P1, t.P2, t.H1, t.H2);
+                fprop_step<Cfg, MODE>(in, ob, store, t.wgt, t.P1, t.P2, t.H1, t.H2);
             }
             if (store) {
                 for (int wp = 0; wp < Cfg::NCW; ++wp) {  // every warp stores its own box
@@ -102,7 +97,7 @@ static int emu_wgrad_cfg(const __half* x, const __half* gr, float* dw, Vol vx, V
                          int grid_target) {
     constexpr int M = Cfg::M, CP = Cfg::CP, CS = Cfg::CS;
     struct TState {
-        __half Gl[3][M][CP], Gh[3][M][CP];
+        __half2 G[3][M][CP];
         float2 acc[27][CP];
     };
     Sched s;
@@ -129,16 +124,13 @@ static int emu_wgrad_cfg(const __half* x, const __half* gr, float* dw, Vol vx, V
             for (int tid = 0; tid < Cfg::NT; ++tid) {
                 TState& t = ts[tid];
                 const WThread<Cfg> th(tid);
-                if (q == g.hb - 1) {
-                    memset(t.Gl, 0, sizeof(t.Gl));
-                    memset(t.Gh, 0, sizeof(t.Gh));
-                }
+                if (q == g.hb - 1) memset(t.G, 0, sizeof(t.G));
                 const __half* xin = xs.data() + th.x_off;
                 const __half* gin = gs.data() + th.g_off;
                 switch (ci % 3) {
-                    case 0: wgrad_step<Cfg, 0>(xin, gin, load_g, t.Gl, t.Gh, t.acc); break;
-                    case 1: wgrad_step<Cfg, 1>(xin, gin, load_g, t.Gl, t.Gh, t.acc); break;
-                    default: wgrad_step<Cfg, 2>(xin, gin, load_g, t.Gl, t.Gh, t.acc); break;
+                    case 0: wgrad_step<Cfg, 0>(xin, gin, load_g, t.G, t.acc); break;
+                    case 1: wgrad_step<Cfg, 1>(xin, gin, load_g, t.G, t.acc); break;
+                    default: wgrad_step<Cfg, 2>(xin, gin, load_g, t.G, t.acc); break;
                 }
             }
             if (q == g.he) {
