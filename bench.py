@@ -39,9 +39,18 @@ VOX = SHAPE[0] * SHAPE[1] * SHAPE[2]
 ALL_CHANNELS = [8, 16, 32, 64, 128]
 FALLBACK_HBM_GBS = 6650.0
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
-# profiles/ (bytes; None where no capture has been taken).
-NCU_TRAFFIC = {'fprop': None, 'wgrad': None}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture summarised in
+# profiles/fprop_wgrad_c8_c32_c128_planes100.md: captured on (1, C, 100, 350, 128) volumes and scaled by
+# 350/100 planes (traffic grows in proportion to the planes a launch processes).  Bytes per (1,C,350,350,128)
+# launch; None where no capture has been taken.
+NCU_TRAFFIC = {
+    ('fprop', 8): int((0.078771 + 0.026808) * 3.5e9),
+    ('wgrad', 8): int((0.151665 + 0.004278) * 3.5e9),
+    ('fprop', 32): int((0.290659 + 0.248993) * 3.5e9),
+    ('wgrad', 32): int((0.578764 + 0.005286) * 3.5e9),
+    ('fprop', 128): int((1.467924 + 1.127809) * 3.5e9),
+    ('wgrad', 128): int((2.405677 + 0.015345) * 3.5e9),
+}
 
 
 def set_planes(h):
@@ -317,14 +326,22 @@ def run_ours(args):
     detail['clone'] = clone
 
     def roof(kind):
+        """All launches of one operator in the timed region (one per C)."""
         ms, nbytes = tot[kind]
         ach = nbytes / (ms * 1e-3) / 1e9
-        traffic = NCU_TRAFFIC.get(kind)
-        return {'bound': 'hbm', 'kernel': kind, 'achieved': round(ach, 1), 'peak': peak, 'peak_kind': peak_kind,
-                'unit': 'GB/s', 'frac': round(ach / peak, 4), 'traffic': traffic,
+        return {'bound': 'hbm', 'kernel': f'{kind}, all C', 'achieved': round(ach, 1), 'peak': peak,
+                'peak_kind': peak_kind, 'unit': 'GB/s', 'frac': round(ach / peak, 4), 'traffic': None,
                 'avg_launch_ms': round(ms / len(channels), 4)}
 
-    dominant = 'wgrad' if tot['wgrad'][0] >= tot['fprop'][0] else 'fprop'
+    # the single kernel launch with the largest share of a step
+    dom_kind, dom_C = max(((k, C) for k in ('fprop', 'wgrad') for C in channels),
+                          key=lambda kc: detail[kc[0]][str(kc[1])]['ms'])
+    dom = detail[dom_kind][str(dom_C)]
+    full_size = SHAPE[0] == 350
+    roofline = {'bound': 'hbm', 'kernel': f'{dom_kind}_tma_kernel at C={dom_C}', 'achieved': dom['gbs'], 'peak': peak,
+                'peak_kind': peak_kind, 'unit': 'GB/s', 'frac': dom['frac'],
+                'traffic': NCU_TRAFFIC.get((dom_kind, dom_C)) if full_size else None,
+                'algorithmic_bytes': algorithmic_bytes(dom_C), 'avg_launch_ms': dom['ms']}
     step_bytes = sum(2 * algorithmic_bytes(C) for C in channels) * world
     value = step_bytes * args.steps / (total_ms * 1e-3) / 1e9
 
@@ -351,7 +368,7 @@ def run_ours(args):
                 'l2': 'inputs larger than L2 (smallest tensor 251 MB; 31 GB touched per step)',
                 'parallelism': f'dp{world}' if world > 1 else 'single',
             },
-            'roofline': roof(dominant), 'roofline_fprop': roof('fprop'), 'roofline_wgrad': roof('wgrad'),
+            'roofline': roofline, 'roofline_fprop': roof('fprop'), 'roofline_wgrad': roof('wgrad'),
             'cpu_baseline': cpu_baseline, 'e2e': e2e, 'clocks': clocks,
             'gpu_launches': 3 * len(channels) * args.steps, 'detail': detail, 'device_status': status,
         }
