@@ -119,6 +119,26 @@ int kdw_wgrad_f16_range(const void* x, const void* grad, void* workspace, int64_
                         int64_t x_strideH, int64_t x_strideW, int64_t Hg, int64_t g_strideN, int64_t g_strideH,
                         int64_t g_strideW, int64_t h_begin, int64_t h_end, int64_t g_h0, int tune, void* stream);
 
+/*
+ * Weight gradient of a whole volume without a caller-provided workspace (no counterpart in the reference).
+ * For callers that must not allocate device memory around the call: a latency-critical training or serving
+ * loop where cudaMalloc (a call that synchronises the device) is off limits, a process running under a fixed
+ * device-memory budget, and embedders without access to an allocator (a plain C host, a plugin that is handed
+ * only input and output buffers).  The per-CTA fp32 rows that kdw_wgrad_f16 keeps in `workspace` live in an
+ * array built into the library instead.
+ *   - Limit: C <= 128 (KDW_ERR_WORKSPACE beyond); the array is 296 x 27 x 128 floats = 3.9 MiB and stays
+ *     resident on every GPU that loads the library until the process exits.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make that
+ *     first call before any stream capture.  No call allocates or frees device memory.
+ *   - All calls on a device share the array: calls that may overlap on the GPU (different streams) race and
+ *     must be serialised by the caller.  Rows are re-initialised by every launch, so no state carries over.
+ * Arguments and results as kdw_wgrad_f16; same kernels, so the result matches it to fp32 rounding (bit for bit
+ * when both use the same number of CTAs).
+ */
+int kdw_wgrad_f16_static(const void* x, const void* grad, float* dw_f32, void* dw_f16, int64_t N, int64_t C, int64_t H,
+                         int64_t W, int64_t D, int64_t x_strideN, int64_t x_strideH, int64_t x_strideW,
+                         int64_t g_strideN, int64_t g_strideH, int64_t g_strideW, void* stream);
+
 int kdw_wgrad_variants(void);
 int kdw_wgrad_variant_channels(int id);
 

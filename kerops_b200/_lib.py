@@ -31,6 +31,7 @@ SIGNATURES = {
         _int,
         [_ptr, _ptr, _ptr, _i64, _ptr, _ptr] + [_i64] * 5 + [_i64] * 3 + [_i64] * 4 + [_i64] * 3 + [_int, _ptr],
     ),
+    'kdw_wgrad_f16_static': (_int, [_ptr, _ptr, _ptr, _ptr] + [_i64] * 5 + [_i64] * 6 + [_ptr]),
     'kdw_wgrad_variants': (_int, []),
     'kdw_wgrad_variant_channels': (_int, [_int]),
 }

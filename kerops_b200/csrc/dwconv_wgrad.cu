@@ -16,6 +16,8 @@
 // There are no atomics anywhere, so results are bitwise reproducible.
 //
 // Plain pass 1 (any C, used for C < 8): one thread per (tap, channel), fp32 FMAs.
+#include <mutex>
+
 #include "../../include/kdw.h"
 #include "kdw_common.cuh"
 #include "wgrad_core.cuh"
@@ -385,6 +387,82 @@ static int wgrad_dispatch(const void* x, const void* grad, void* workspace, int6
     return 0;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Weight gradient with a built-in workspace (no caller-provided scratch)
+// ------------------------------------------------------------------------------------------------
+// One fp32 [27][C] row per CTA, for at most kStaticRows CTAs and C <= kStaticMaxC: 296 * 27 * 128 * 4 bytes
+// (3.9 MiB), resident on every GPU that loads the library until the process exits.
+static constexpr int kStaticRows = 296;
+static constexpr int kStaticMaxC = 128;
+static __device__ __align__(256) float g_static_ws[kStaticRows * 27 * kStaticMaxC];
+
+// In host code `g_static_ws` is only a handle for the runtime, not a device address: the address is looked up
+// once per device (with that device current) and cached.
+static int static_ws_ptr(float** out) {
+    static float* cache[64] = {nullptr};
+    static std::mutex mu;
+    int dev = 0;
+    KDW_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        set_error("wgrad_static: device index %d is outside the supported range 0..63", dev);
+        return KDW_ERR_ARG;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!cache[dev]) {
+        void* addr = nullptr;
+        KDW_CUDA(cudaGetSymbolAddress(&addr, g_static_ws));
+        cache[dev] = (float*)addr;
+    }
+    *out = cache[dev];
+    return 0;
+}
+
+static int wgrad_static_dispatch(const void* x, const void* grad, float* dw_f32, void* dw_f16, int64_t N, int64_t C,
+                                 int64_t H, int64_t W, int64_t D, int64_t xsN, int64_t xsH, int64_t xsW, int64_t gsN,
+                                 int64_t gsH, int64_t gsW, void* stream) {
+    if (!x || !grad || (!dw_f32 && !dw_f16)) {
+        set_error("wgrad_static: null pointer (x, grad and at least one output are required)");
+        return KDW_ERR_ARG;
+    }
+    if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || D <= 0 || (C & (C - 1)) != 0) {
+        set_error("wgrad_static: sizes must be positive and C a power of two (N=%lld C=%lld H=%lld W=%lld D=%lld)",
+                  (long long)N, (long long)C, (long long)H, (long long)W, (long long)D);
+        return KDW_ERR_ARG;
+    }
+    if (C > kStaticMaxC) {
+        set_error("wgrad_static: C=%lld exceeds the built-in workspace (C <= %d); use kdw_wgrad_f16 with a "
+                  "caller-provided workspace", (long long)C, kStaticMaxC);
+        return KDW_ERR_WORKSPACE;
+    }
+    if (H > 0x7fffffff || W > 0x7fffffff || D > 0x7fffffff || N > 0x7fffffff) {
+        set_error("wgrad_static: extent does not fit in 32 bits");
+        return KDW_ERR_ARG;
+    }
+    float* ws = nullptr;
+    int rc = static_ws_ptr(&ws);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int KC = (int)(27 * C);
+    int rows = 0;
+    if (C < 8) {
+        const long long voxels = (long long)N * H * W * D;
+        const long long blocks = voxels < kStaticRows ? voxels : kStaticRows;
+        wgrad_plain_kernel<<<(unsigned)blocks, 128, 0, st>>>((const __half*)x, (const __half*)grad, ws, voxels, (int)C,
+                                                             (int)H, (int)W, (int)D, xsN, xsH, xsW, gsN, gsH, gsW, 0,
+                                                             (int)H, 0);
+        KDW_CUDA(cudaGetLastError());
+        rows = (int)blocks;
+    } else {
+        const WgradVariant& v = g_wgrad_variants[auto_wgrad_variant(C) - 1];
+        WgradArgs a{x, grad, ws, kStaticRows, N, C, H, W, D, xsN, xsH, xsW, H, gsN, gsH, gsW, 0, (int)H, 0, st};
+        rc = v.f(a, &rows);  // the launcher never uses more CTAs (= rows) than a.ws_rows
+        if (rc) return rc;
+    }
+    wgrad_reduce_kernel<<<(KC + 3) / 4, 128, 0, st>>>(ws, rows, KC, dw_f32, (__half*)dw_f16);
+    KDW_CUDA(cudaGetLastError());
+    return 0;
+}
+
 }  // namespace kdw
 
 extern "C" {
@@ -414,6 +492,13 @@ int kdw_wgrad_f16(const void* x, const void* grad, void* workspace, int64_t work
                   int tune, void* stream) {
     return kdw::wgrad_dispatch(x, grad, workspace, workspace_bytes, dw_f32, dw_f16, N, C, H, W, D, x_strideN,
                                x_strideH, x_strideW, H, g_strideN, g_strideH, g_strideW, 0, H, 0, tune, stream);
+}
+
+int kdw_wgrad_f16_static(const void* x, const void* grad, float* dw_f32, void* dw_f16, int64_t N, int64_t C, int64_t H,
+                         int64_t W, int64_t D, int64_t x_strideN, int64_t x_strideH, int64_t x_strideW,
+                         int64_t g_strideN, int64_t g_strideH, int64_t g_strideW, void* stream) {
+    return kdw::wgrad_static_dispatch(x, grad, dw_f32, dw_f16, N, C, H, W, D, x_strideN, x_strideH, x_strideW, g_strideN,
+                                      g_strideH, g_strideW, stream);
 }
 
 int kdw_wgrad_f16_range(const void* x, const void* grad, void* workspace, int64_t workspace_bytes, float* dw_f32,
