@@ -461,6 +461,92 @@ def measure_triton_reference(channels, data, dev):
     return out
 
 
+def run_dshard(args):
+    """configs[3]: one (1, 128, 1400, 350, 128) volume sharded along H over the ranks (1-plane halos exchanged
+    point to point, fp32 weight gradient all-reduced); strong scaling.  A step = forward + weight gradient."""
+    import torch
+    import torch.distributed as dist
+
+    from kerops_b200 import _lib
+    from kerops_b200 import dist as kd
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    dev = torch.device('cuda', local)
+    torch.cuda.set_device(dev)
+    _lib.load()
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+    C, H, W, D = 128, args.dshard_planes, SHAPE[1], SHAPE[2]
+    hb, he = kd.shard_planes(H, world, rank)
+    Hs = he - hb
+    g = torch.Generator(device=dev).manual_seed(50 + rank)
+    xh = kd.alloc_halo_volume(1, C, Hs, W, D, dev)
+    xh[:, :, 1:-1].copy_(torch.randn(1, Hs, W, D, C, generator=g, device=dev, dtype=torch.float16).permute(0, 4, 1, 2, 3))
+    grad = torch.randn(1, Hs, W, D, C, generator=g, device=dev, dtype=torch.float16).permute(0, 4, 1, 2, 3)
+    w = ((torch.rand(3, 3, 3, C, generator=g, device=dev) * 2 - 1) / math.sqrt(27)).to(torch.float16)
+
+    class Single:  # one rank: no neighbours, the halo planes stay zero
+        @staticmethod
+        def finish():
+            return None
+
+    def step():
+        if world > 1:
+            fin = kd.exchange_halo(xh)
+            y = kd.hsharded_fprop(xh, w, halo_ready=fin)
+            dw = kd.hsharded_wgrad(xh, grad, halo_ready=lambda: None)  # halo already in place
+        else:
+            y = kd.hsharded_fprop(xh, w, halo_ready=Single.finish)
+            dw = kd.hsharded_wgrad(xh, grad, halo_ready=Single.finish, reduce=False)
+        return y, dw
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(dev)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    status = _lib.device_status()
+    peak, peak_kind = measured_peak()
+    nbytes = 2 * 4 * H * W * D * C  # forward + weight gradient over the whole volume
+    value = nbytes * args.steps / (ms * 1e-3) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            'metric': 'DWConv + DWConvWGRAD algorithmic HBM GB/s on one H-sharded (1,128,%d,350,128) fp16 volume' % H,
+            'value': round(value, 1), 'unit': 'GB/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
+            'ms_per_step': round(ms / args.steps, 4), 'higher_is_better': True, 'scaling': 'strong',
+            'vs_baseline': None, 'dtype': 'f16 products, f32 accumulation', 'data': 'synthetic',
+            'config': {'workload': f'configs[3]: (1,128,{H},350,128) split along H over {world} rank(s), 1-plane halos '
+                                   'over NCCL point-to-point, fp32 [27][128] gradient all-reduced',
+                       'l2': 'inputs larger than L2', 'parallelism': f'hshard{world}'},
+            'roofline': {'bound': 'hbm', 'kernel': 'fprop + wgrad, whole step', 'achieved': round(value / world, 1),
+                         'peak': peak, 'peak_kind': peak_kind, 'unit': 'GB/s', 'frac': round(value / world / peak, 4),
+                         'traffic': None},
+            'clocks': clocks, 'gpu_launches': (9 if world > 1 else 3) * args.steps, 'device_status': status,
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -470,6 +556,10 @@ def main():
     ap.add_argument('--channels', default=','.join(map(str, ALL_CHANNELS)))
     ap.add_argument('--planes', type=int, default=SHAPE[0],
                     help='h extent of the volume (default 350); smaller values are for profiler captures only')
+    ap.add_argument('--workload', default='sweep', choices=['sweep', 'dshard'],
+                    help="'sweep' (default): the headline per-C sweep, one sample per GPU; 'dshard': one large volume "
+                         'sharded along H over the GPUs')
+    ap.add_argument('--dshard-planes', type=int, default=1400)
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--compare-triton', action='store_true',
@@ -480,6 +570,8 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
     if args.impl == 'reference':
         run_reference(args)
+    elif args.workload == 'dshard':
+        run_dshard(args)
     else:
         run_ours(args)
 

@@ -1,0 +1,149 @@
+"""Multi-GPU use of the depthwise-conv path: one process per GPU, torch.distributed for the plumbing.
+
+The reference is single-GPU (no distributed code anywhere in kerops); this module adds the two ways the path
+shards, neither of which needs a collective on the activation data:
+
+* by SAMPLE - every rank convolves its own samples; the only exchange is one all-reduce of the fp32
+  [3,3,3,C] weight gradient (864 B at C=8 ... 13.8 KB at C=128);
+* along H (torch dim 2, the outermost spatial axis, whose planes are contiguous slabs) for one large volume -
+  rank r owns planes [r*H/G, (r+1)*H/G); a 3-tap stencil needs ONE halo plane from each neighbour.  The local
+  buffer holds Hs+2 planes (halo, owned..., halo); neighbours' boundary planes are received into the halo planes
+  (point-to-point over NVLink), zero at the two ends of the volume.  The interior planes do not depend on the halo
+  and are computed while the exchange is in flight; the two boundary planes follow.  The weight gradient needs
+  only the x halo (grad is read at the owned voxel).
+
+The device work goes through `LocalOps`, by default the CUDA kernels behind the C-ABI plane-range entry points
+(kdw_fprop_f16_range / kdw_wgrad_f16_range).  Tests of the host logic on CPU (gloo) pass their own LocalOps.
+"""
+import torch
+import torch.distributed as dist
+
+
+class LocalOps:
+    """Device work on one rank: plane-range forward and weight gradient of a halo'd local volume."""
+
+    def fprop_range(self, x_halo, weight, y, h_begin, h_end, y_h0):
+        """y[:, :, h - y_h0] = conv(x_halo)[h] for h in [h_begin, h_end)."""
+        raise NotImplementedError
+
+    def wgrad_range(self, x_halo, grad, h_begin, h_end, g_h0):
+        """fp32 [3,3,3,C]: sum over grad planes h in [h_begin, h_end) (x plane numbering), grad plane h - g_h0."""
+        raise NotImplementedError
+
+
+class CudaOps(LocalOps):
+    def fprop_range(self, x_halo, weight, y, h_begin, h_end, y_h0):
+        from .ops.conv import _launch
+
+        _launch.fprop(x_halo, weight, y, h_begin=h_begin, h_end=h_end, y_h0=y_h0)
+
+    def wgrad_range(self, x_halo, grad, h_begin, h_end, g_h0):
+        from .ops.conv import _launch
+
+        dw32, _ = _launch.wgrad(x_halo, grad, h_begin=h_begin, h_end=h_end, g_h0=g_h0, want_f32=True, want_f16=False)
+        return dw32
+
+
+def shard_planes(H, world, rank):
+    """Plane range [begin, end) of the H axis owned by `rank` (contiguous, sizes differ by at most one)."""
+    base, extra = divmod(H, world)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def alloc_halo_volume(N, C, Hs, W, D, device, dtype=torch.float16):
+    """channels_last_3d (N, C, Hs+2, W, D) buffer; planes 0 and Hs+1 are the halo planes (zero-initialised)."""
+    buf = torch.zeros((N, Hs + 2, W, D, C), dtype=dtype, device=device)
+    return buf.permute(0, 4, 1, 2, 3)
+
+
+def exchange_halo(x_halo, group=None):
+    """Fills the two halo planes of a local H-shard from the neighbouring ranks (zero at the volume's ends).
+
+    Starts the transfers and returns a `finish()` callable; call it before anything reads planes 0 and Hs+1.
+    On NCCL the transfers run on the process group's own stream and `finish()` only makes the current stream wait
+    for them, so kernels launched in between overlap with the exchange."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    Hs = x_halo.shape[2] - 2
+    phys = x_halo.permute(0, 2, 3, 4, 1)  # (N, Hs+2, W, D, C) contiguous view
+    ops = []
+    # planes are contiguous only within one sample, so a plane of every sample is sent as one strided tensor
+    if rank > 0:
+        ops.append(dist.P2POp(dist.isend, phys[:, 1].contiguous(), rank - 1, group))
+    if rank < world - 1:
+        ops.append(dist.P2POp(dist.isend, phys[:, Hs].contiguous(), rank + 1, group))
+    recv_lo = recv_hi = None
+    if rank > 0:
+        recv_lo = phys[:, 0] if phys[:, 0].is_contiguous() else torch.empty_like(phys[:, 0])
+        ops.append(dist.P2POp(dist.irecv, recv_lo, rank - 1, group))
+    else:
+        phys[:, 0].zero_()
+    if rank < world - 1:
+        recv_hi = phys[:, Hs + 1] if phys[:, Hs + 1].is_contiguous() else torch.empty_like(phys[:, Hs + 1])
+        ops.append(dist.P2POp(dist.irecv, recv_hi, rank + 1, group))
+    else:
+        phys[:, Hs + 1].zero_()
+    reqs = dist.batch_isend_irecv(ops) if ops else []
+
+    def finish():
+        for r in reqs:
+            r.wait()
+        if recv_lo is not None and recv_lo.data_ptr() != phys[:, 0].data_ptr():
+            phys[:, 0].copy_(recv_lo)
+        if recv_hi is not None and recv_hi.data_ptr() != phys[:, Hs + 1].data_ptr():
+            phys[:, Hs + 1].copy_(recv_hi)
+
+    return finish
+
+
+def hsharded_fprop(x_halo, weight, group=None, ops=None, halo_ready=None):
+    """Forward pass of the local H-shard.  x_halo: (N, C, Hs+2, W, D) with the owned planes at 1..Hs.
+    If `halo_ready` is None the halo exchange is started here and overlapped with the interior planes.
+    Returns y (N, C, Hs, W, D)."""
+    ops = ops or CudaOps()
+    N, C, Hp, W, D = x_halo.shape
+    Hs = Hp - 2
+    y = torch.empty((N, Hs, W, D, C), dtype=x_halo.dtype, device=x_halo.device).permute(0, 4, 1, 2, 3)
+    finish = halo_ready if halo_ready is not None else exchange_halo(x_halo, group)
+    if Hs > 2:
+        ops.fprop_range(x_halo, weight, y, 2, Hs, 1)  # planes that do not touch the halo
+    finish()
+    if Hs > 2:
+        ops.fprop_range(x_halo, weight, y, 1, 2, 1)
+        ops.fprop_range(x_halo, weight, y, Hs, Hs + 1, 1)
+    else:
+        ops.fprop_range(x_halo, weight, y, 1, Hs + 1, 1)
+    return y
+
+
+def hsharded_wgrad(x_halo, grad, group=None, ops=None, halo_ready=None, reduce=True):
+    """Weight gradient of the whole (sharded) volume, fp32 [3,3,3,C], identical on every rank when reduce=True.
+    grad: (N, C, Hs, W, D), the owned planes only."""
+    ops = ops or CudaOps()
+    Hs = x_halo.shape[2] - 2
+    finish = halo_ready if halo_ready is not None else exchange_halo(x_halo, group)
+    dw = None
+    if Hs > 2:
+        dw = ops.wgrad_range(x_halo, grad, 2, Hs, 1)
+    finish()
+    if Hs > 2:
+        dw = dw + ops.wgrad_range(x_halo, grad, 1, 2, 1) + ops.wgrad_range(x_halo, grad, Hs, Hs + 1, 1)
+    else:
+        dw = ops.wgrad_range(x_halo, grad, 1, Hs + 1, 1)
+    if reduce:
+        dist.all_reduce(dw, group=group)
+    return dw
+
+
+def sample_sharded_step(x, weight, grad, group=None, ops=None):
+    """Data-parallel slice of a training step: y = DWConv(x) for the local samples and the weight gradient of
+    the global batch.  Returns (y, dw_fp32): the local output and the all-reduced fp32 [3,3,3,C] gradient."""
+    ops = ops or CudaOps()
+    N, C, H, W, D = x.shape
+    y = torch.empty((N, H, W, D, C), dtype=x.dtype, device=x.device).permute(0, 4, 1, 2, 3)
+    ops.fprop_range(x, weight, y, 0, H, 0)
+    dw = ops.wgrad_range(x, grad, 0, H, 0)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(dw, group=group)
+    return y, dw
