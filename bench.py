@@ -7,8 +7,8 @@
 A STEP is one pass over the headline sweep: for every C in {8, 16, 32, 64, 128}, DWConv of a
 (1, C, 350, 350, 128) fp16 channels_last_3d volume followed by DWConvWGRAD of the same volume against
 an independent gradient (seeded synthetic N(0,1) data, weights U(+-1/sqrt(27))).  With N GPUs every rank
-runs the sweep on its own sample (weak scaling) and the fp32 [27][C] weight gradients are summed with
-one NCCL all-reduce per C - the only exchange the sample-sharded path has.
+runs the sweep on its own sample (weak scaling) and the fp32 [27][C] weight gradients of a step are summed
+with one NCCL all-reduce - the only exchange the sample-sharded path has.
 
 `value` = algorithmic bytes of all ranks / max-over-ranks device time; algorithmic bytes are 4*V*C per
 operator call (read x + write y, or read x + read grad; V = 350*350*128 voxels).
@@ -254,6 +254,12 @@ def run_ours(args):
     channels = args.channels
     data = {C: make_gpu_inputs(C, dev, seed=1000 * rank + C) for C in channels}
     ws = {C: _launch.wgrad_workspace(data[C][0]) for C in channels}
+    # one bucket for the fp32 weight gradients of a step: a single all-reduce per step when sharded by sample
+    bucket = torch.empty(27 * sum(channels), dtype=torch.float32, device=dev)
+    slot, off = {}, 0
+    for C in channels:
+        slot[C] = bucket[off:off + 27 * C]
+        off += 27 * C
 
     def step(events=None):
         for C in channels:
@@ -264,13 +270,13 @@ def run_ours(args):
             y = DWConv(x, w)
             if events is not None:
                 e1.record()
-            dw32, dw16 = _launch.wgrad(x, grad, want_f32=True, want_f16=(world == 1), workspace=ws[C])
+            dw32, dw16 = _launch.wgrad(x, grad, want_f16=(world == 1), workspace=ws[C], out_f32=slot[C])
             if events is not None:
                 e2.record()
                 events.append((C, e0, e1, e2))
-            if world > 1:
-                dist.all_reduce(dw32)
             del y
+        if world > 1:
+            dist.all_reduce(bucket)
 
     def barrier():
         torch.cuda.synchronize()

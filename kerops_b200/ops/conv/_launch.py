@@ -58,9 +58,12 @@ def wgrad_workspace(x):
     return torch.empty(nbytes, dtype=torch.uint8, device=x.device)
 
 
-def wgrad(x, grad, h_begin=None, h_end=None, g_h0=0, want_f32=False, want_f16=True, tune=0, workspace=None):
+def wgrad(x, grad, h_begin=None, h_end=None, g_h0=0, want_f32=False, want_f16=True, tune=0, workspace=None,
+          out_f32=None):
     """Enqueues the weight gradient over grad planes [h_begin, h_end) (x plane numbering).
 
+    `out_f32`, if given, is a contiguous fp32 buffer of 27*C elements that receives the fp32 result (e.g. a slice
+    of a gradient bucket that is all-reduced in one call).
     Returns (dw_f32 or None, dw_f16 or None), each [3, 3, 3, C]."""
     lib = _lib.load()
     N, C, Hx, W, D = x.shape
@@ -70,7 +73,11 @@ def wgrad(x, grad, h_begin=None, h_end=None, g_h0=0, want_f32=False, want_f16=Tr
     xs = volume_strides(x)
     gs = volume_strides(grad)
     ws = workspace if workspace is not None else wgrad_workspace(x)
-    dw32 = torch.empty([3, 3, 3, C], dtype=torch.float32, device=x.device) if want_f32 else None
+    if out_f32 is not None:
+        assert out_f32.dtype == torch.float32 and out_f32.is_contiguous() and out_f32.numel() == 27 * C
+        dw32, want_f32 = out_f32.view(3, 3, 3, C), True
+    else:
+        dw32 = torch.empty([3, 3, 3, C], dtype=torch.float32, device=x.device) if want_f32 else None
     dw16 = torch.empty([3, 3, 3, C], dtype=torch.float16, device=x.device) if want_f16 else None
     tune = tune or _env_tune('KDW_WGRAD_TUNE')
     with torch.cuda.device(x.device):
