@@ -240,7 +240,14 @@ static const FpropVariant g_fprop_variants[] = {
 #include "fprop_variants.inc"
 };
 #undef KDW_VARIANT
-static const int g_n_fprop_variants = (int)(sizeof(g_fprop_variants) / sizeof(g_fprop_variants[0]));
+static const int g_n_table_variants = (int)(sizeof(g_fprop_variants) / sizeof(g_fprop_variants[0]));
+
+// tensor-core variants (dwconv_fprop_mma.cu) are numbered after the table; they implement KDW_ACC_F32 only
+int fprop_mma_variants();
+int launch_fprop_mma_variant(int which, const void* x, const void* w, void* y, int64_t N, int64_t C, int64_t Hx,
+                             int64_t W, int64_t D, int64_t xsN, int64_t xsH, int64_t xsW, int64_t Hy, int64_t ysN,
+                             int64_t ysH, int64_t ysW, int h_begin, int h_end, int y_h0, cudaStream_t stream);
+static int n_fprop_variants() { return g_n_table_variants + fprop_mma_variants(); }
 
 static int auto_fprop_variant(int64_t C) {
     // fastest KDW_ACC_F32 variant measured at (1, C, 350, 350, 128) on B200
@@ -279,8 +286,8 @@ static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N,
     }
     if (h_begin == h_end) return 0;
     cudaStream_t st = (cudaStream_t)stream;
-    if (tune < 0 || tune > g_n_fprop_variants) {
-        set_error("fprop: tune=%d names no kernel variant (1..%d)", tune, g_n_fprop_variants);
+    if (tune < 0 || tune > n_fprop_variants()) {
+        set_error("fprop: tune=%d names no kernel variant (1..%d)", tune, n_fprop_variants());
         return KDW_ERR_TUNE;
     }
     if (C < 8) {
@@ -299,6 +306,14 @@ static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N,
         return 0;
     }
     const int id = tune ? tune : auto_fprop_variant(C);
+    if (id > g_n_table_variants) {
+        if (acc_type != KDW_ACC_F32) {
+            set_error("fprop: variant %d (tensor cores) implements KDW_ACC_F32 only", id);
+            return KDW_ERR_TUNE;
+        }
+        return launch_fprop_mma_variant(id - g_n_table_variants - 1, x, weight, y, N, C, Hx, W, D, xsN, xsH, xsW, Hy, ysN,
+                                        ysH, ysW, (int)h_begin, (int)h_end, (int)y_h0, st);
+    }
     const FpropVariant& v = g_fprop_variants[id - 1];
     if (C % v.cs != 0) {
         set_error("fprop: variant %d works on %d-channel slices, C=%lld is not a multiple", id, v.cs, (long long)C);
@@ -312,10 +327,11 @@ static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N,
 
 extern "C" {
 
-int kdw_fprop_variants(void) { return kdw::g_n_fprop_variants; }
+int kdw_fprop_variants(void) { return kdw::n_fprop_variants(); }
 
 int kdw_fprop_variant_channels(int id) {
-    if (id < 1 || id > kdw::g_n_fprop_variants) return KDW_ERR_TUNE;
+    if (id < 1 || id > kdw::n_fprop_variants()) return KDW_ERR_TUNE;
+    if (id > kdw::g_n_table_variants) return 8;
     return kdw::g_fprop_variants[id - 1].cs;
 }
 

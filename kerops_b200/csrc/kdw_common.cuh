@@ -43,6 +43,10 @@ int cuda_fail(cudaError_t e, const char* what);  // records the message, returns
 int encode_volume_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
                       int64_t strideN, int64_t strideH, int64_t strideW, int boxC, int boxD, int boxW);
 
+// As encode_volume_map with the D and C axes merged (see kdw_host.cu).
+int encode_merged_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
+                      int64_t strideN, int64_t strideH, int64_t strideW, int boxDC, int boxW);
+
 int device_sm_count(int* sms);
 
 // Device address (on the current device) of the library's status word.

@@ -93,6 +93,41 @@ int encode_volume_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, 
     return 0;
 }
 
+// The same volume with the D and C axes merged into one contiguous axis of D*C elements: dims (D*C, W, H, N, 1),
+// box (boxDC, boxW, 1, 1, 1).  Rows of a box are then boxDC*2 bytes long instead of C*2, which matters for small
+// C (a 16-byte row per voxel makes poor use of the TMA unit).  Zero fill works as before because W stays an
+// axis of its own; only usable when a CTA takes all channels of a voxel.
+int encode_merged_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
+                      int64_t strideN, int64_t strideH, int64_t strideW, int boxDC, int boxW) {
+    EncodeTiledFn fn;
+    int rc = get_encode_fn(&fn);
+    if (rc) return rc;
+    if (((uintptr_t)base & 15) != 0 || (C % 8) != 0 || (strideW % 8) != 0 || (strideH % 8) != 0 ||
+        (strideN % 8) != 0) {
+        set_error("TMA path needs 16-byte aligned base and strides (C, strideW, strideH, strideN multiples of 8)");
+        return KDW_ERR_ALIGN;
+    }
+    if (boxDC < 8 || boxDC > 256 || (boxDC % 8) != 0 || boxW < 1 || boxW > 256) {
+        set_error("tensor-map box out of range");
+        return KDW_ERR_ARG;
+    }
+    const cuuint64_t dims[5] = {(cuuint64_t)(D * C), (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N, 1};
+    cuuint64_t strides[4] = {(cuuint64_t)strideW * 2, (cuuint64_t)strideH * 2, (cuuint64_t)strideN * 2,
+                             (cuuint64_t)strideN * 2 * (cuuint64_t)N};
+    for (int i = 0; i < 4; ++i)
+        if (strides[i] == 0) strides[i] = 16;
+    const cuuint32_t box[5] = {(cuuint32_t)boxDC, (cuuint32_t)boxW, 1, 1, 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (merged D*C axis) failed with CUresult %d", (int)r);
+        return (int)r;
+    }
+    return 0;
+}
+
 int make_sched(Sched* s, int64_t N, int64_t C, int64_t W, int64_t D, int h_begin, int h_end, int WT, int DT, int CS,
                int grid_target) {
     s->WT = WT;

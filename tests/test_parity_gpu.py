@@ -11,6 +11,7 @@ import numpy as np
 import pytest
 import torch
 
+from kerops_b200._lib import KdwError
 from oracle import dwconv_oracle as o
 from oracle import torch_oracle as to
 
@@ -152,7 +153,12 @@ def test_all_fprop_variants(ops, kdw_lib):
                 ref = to.fprop_shift_fp32(x, w)
                 for acc in ('float32', 'float16'):
                     y = torch.full_like(x, float('nan'))
-                    _launch.fprop(x, w, y, acc=acc, tune=v)
+                    try:
+                        _launch.fprop(x, w, y, acc=acc, tune=v)
+                    except KdwError as e:
+                        # tensor-core variants: float32 accumulate type only, some of them C == 8 only
+                        assert e.code == -4 and (acc == 'float16' or 'C == 8' in str(e)), e
+                        continue
                     check_fprop(y, ref, strict=(acc == 'float32'))
 
 
