@@ -553,6 +553,86 @@ def run_dshard(args):
         dist.destroy_process_group()
 
 
+def run_dpstep(args):
+    """configs[4]: data-parallel slice of a training step.  A batch of 8 samples (32, 350, 350, 128) is split by
+    sample over the ranks (8, 4, 2, 1 samples per rank on 1, 2, 4, 8 GPUs); a step is DWConv of the local samples,
+    DWConvWGRAD against an N(0,1) gradient, and one all-reduce of the fp32 [27][32] weight gradient.  Strong
+    scaling: the batch is fixed."""
+    import torch
+    import torch.distributed as dist
+
+    from kerops_b200 import _lib
+    from kerops_b200 import dist as kd
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    dev = torch.device('cuda', local)
+    torch.cuda.set_device(dev)
+    _lib.load()
+    if world > 1:
+        dist.init_process_group('nccl', device_id=dev)
+    batch, C = args.dp_batch, 32
+    H, W, D = SHAPE
+    if batch % world:
+        raise SystemExit(f'--dp-batch {batch} is not a multiple of the {world} ranks')
+    n_local = batch // world
+    xs, gs = [], []
+    for i in range(n_local):  # one seed per global sample index, so any sharding sees the same batch
+        g = torch.Generator(device=dev).manual_seed(9000 + rank * n_local + i)
+        xs.append(torch.randn(1, H, W, D, C, generator=g, device=dev, dtype=torch.float16))
+        gs.append(torch.randn(1, H, W, D, C, generator=g, device=dev, dtype=torch.float16))
+    x = torch.cat(xs).permute(0, 4, 1, 2, 3)
+    grad = torch.cat(gs).permute(0, 4, 1, 2, 3)
+    del xs, gs
+    gw = torch.Generator(device=dev).manual_seed(77)
+    w = ((torch.rand(3, 3, 3, C, generator=gw, device=dev) * 2 - 1) / math.sqrt(27)).to(torch.float16)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        kd.sample_sharded_step(x, w, grad)
+    barrier()
+    sampler = ClockSampler(dev)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        kd.sample_sharded_step(x, w, grad)
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    status = _lib.device_status()
+    peak, peak_kind = measured_peak()
+    nbytes = 2 * algorithmic_bytes(C, batch)
+    value = nbytes * args.steps / (ms * 1e-3) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            'metric': 'DWConv + DWConvWGRAD algorithmic HBM GB/s, batch of %d (32,%d,350,128) fp16 samples' % (batch, H),
+            'value': round(value, 1), 'unit': 'GB/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
+            'ms_per_step': round(ms / args.steps, 4), 'higher_is_better': True, 'scaling': 'strong',
+            'vs_baseline': None, 'dtype': 'f16 products, f32 accumulation', 'data': 'synthetic',
+            'config': {'workload': f'configs[4]: batch {batch} x (32,{H},350,128), {n_local} sample(s) per rank; DWConv, '
+                                   'DWConvWGRAD, all-reduce of the fp32 [27][32] gradient',
+                       'l2': 'inputs larger than L2', 'parallelism': f'dp{world}'},
+            'roofline': {'bound': 'hbm', 'kernel': 'fprop + wgrad, whole step', 'achieved': round(value / world, 1),
+                         'peak': peak, 'peak_kind': peak_kind, 'unit': 'GB/s', 'frac': round(value / world / peak, 4),
+                         'traffic': None},
+            'clocks': clocks, 'gpu_launches': 3 * args.steps, 'device_status': status,
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -562,9 +642,10 @@ def main():
     ap.add_argument('--channels', default=','.join(map(str, ALL_CHANNELS)))
     ap.add_argument('--planes', type=int, default=SHAPE[0],
                     help='h extent of the volume (default 350); smaller values are for profiler captures only')
-    ap.add_argument('--workload', default='sweep', choices=['sweep', 'dshard'],
+    ap.add_argument('--workload', default='sweep', choices=['sweep', 'dshard', 'dpstep'],
                     help="'sweep' (default): the headline per-C sweep, one sample per GPU; 'dshard': one large volume "
-                         'sharded along H over the GPUs')
+                         "sharded along H over the GPUs; 'dpstep': a batch of (32,350,350,128) samples split by sample")
+    ap.add_argument('--dp-batch', type=int, default=8)
     ap.add_argument('--dshard-planes', type=int, default=1400)
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-cpu-baseline', action='store_true')
@@ -578,6 +659,8 @@ def main():
         run_reference(args)
     elif args.workload == 'dshard':
         run_dshard(args)
+    elif args.workload == 'dpstep':
+        run_dpstep(args)
     else:
         run_ours(args)
 

@@ -50,7 +50,9 @@ const char* kdw_last_error(void);
 /*
  * Reads and clears the device-side status word of the CURRENT device (synchronises the device):
  * 0 = ok, 1 = a bounded wait on a TMA barrier ran out inside a kernel (the kernel stopped early and its
- * output is invalid), 2 = a TMA copy with a misaligned shared address or channel coordinate was skipped.  No reference counterpart (the reference has no device-side waits).
+ * output is invalid), 2 = a TMA copy with a misaligned shared address or channel coordinate was skipped,
+ * 3 = kdw_allreduce_push_f32 gave up waiting for a peer's flag (its outputs were not written).  No reference
+ * counterpart (the reference has no device-side waits).
  */
 int kdw_device_status(int* status);
 
@@ -141,6 +143,33 @@ int kdw_wgrad_f16_static(const void* x, const void* grad, float* dw_f32, void* d
 
 int kdw_wgrad_variants(void);
 int kdw_wgrad_variant_channels(int id);
+
+/*
+ * Multi-GPU sum of weight gradients by peer stores (no reference counterpart: the reference is single-GPU).
+ *
+ * Every rank owns one exchange buffer of kdw_allreduce_buffer_bytes(n, world) bytes, zero-filled once before the
+ * first call, and can address the buffers of all ranks (`buffers[r]`, device pointers valid in the calling
+ * process: CUDA IPC mappings or any other peer mapping; buffers[rank] is the rank's own).  One kernel on each
+ * rank writes `local` (n fp32 values, e.g. the [3][3][3][C] gradient from kdw_wgrad_f16) into its slot of
+ * every buffer, raises a flag there, waits for the flags of all ranks in its own buffer and writes the sum,
+ * added in rank order, to out_f32 and/or out_f16 - the same bits on every rank.
+ *   seq         call counter, the same on every rank: 1 for the first call on these buffers, then 2, 3, ...
+ *   timeout_ns  limit of the wait for the peers' flags; when it runs out the kernel sets the device status
+ *               word to 3 (kdw_device_status) and leaves the outputs unwritten
+ * All calls that use one set of buffers must be enqueued on the same stream of their rank.  world <= 16.
+ * The function itself only enqueues the kernel; it returns KDW_ERR_ARG / KDW_ERR_ALIGN for bad arguments
+ * (buffers must be 128-byte aligned).
+ */
+int64_t kdw_allreduce_buffer_bytes(int64_t n, int world);
+int kdw_allreduce_push_f32(const float* local, float* out_f32, void* out_f16, void* const* buffers, int64_t n, int rank,
+                           int world, uint32_t seq, int64_t timeout_ns, void* stream);
+
+/*
+ * Lets kernels on the CURRENT device address memory of `peer_device` (cudaDeviceEnablePeerAccess; already
+ * enabled is not an error).  Needed once per peer before kdw_allreduce_push_f32 when the peer buffers were
+ * mapped without it.  No reference counterpart.
+ */
+int kdw_enable_peer_access(int peer_device);
 
 #ifdef __cplusplus
 }

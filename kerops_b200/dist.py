@@ -14,7 +14,12 @@ shards, neither of which needs a collective on the activation data:
 
 The device work goes through `LocalOps`, by default the CUDA kernels behind the C-ABI plane-range entry points
 (kdw_fprop_f16_range / kdw_wgrad_f16_range).  Tests of the host logic on CPU (gloo) pass their own LocalOps.
+
+The gradient all-reduce is NCCL's by default; `GradPushAllReduce` is the library's own one-kernel version over
+peer memory (kdw_allreduce_push_f32) and can be passed as `reducer=` to the helpers below.
 """
+import ctypes
+
 import torch
 import torch.distributed as dist
 
@@ -42,6 +47,73 @@ class CudaOps(LocalOps):
 
         dw32, _ = _launch.wgrad(x_halo, grad, h_begin=h_begin, h_end=h_end, g_h0=g_h0, want_f32=True, want_f16=False)
         return dw32
+
+
+class GradPushAllReduce:
+    """All-reduce (sum) of small fp32 tensors - the [3,3,3,C] weight gradients - through peer stores: one kernel
+    per rank pushes its values into every rank's exchange buffer, waits (with a time limit) for the others and
+    adds the slots in rank order, so every rank gets the same bits.  A collective: construct it and call it on
+    every rank of `group`, always from the same stream.
+
+    The exchange buffers come from torch's allocator and are shared with the other ranks of the node as CUDA
+    IPC mappings (the same mechanism torch.multiprocessing uses to pass CUDA tensors between processes)."""
+
+    def __init__(self, max_numel, group=None, device=None, timeout_s=10.0):
+        from torch.multiprocessing.reductions import reduce_tensor
+
+        from . import _lib
+
+        self._lib = _lib
+        self.lib = _lib.load()
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = torch.device(device) if device is not None else torch.device('cuda', torch.cuda.current_device())
+        self.max_numel = int(max_numel)
+        self.timeout_ns = int(timeout_s * 1e9)
+        nbytes = self.lib.kdw_allreduce_buffer_bytes(self.max_numel, self.world)
+        if nbytes <= 0:
+            raise ValueError(f'GradPushAllReduce: max_numel={max_numel}, world={self.world} not supported')
+        # an allocation of its own (not a slice of a cached block), zero = "no flag raised yet"
+        self.buffer = torch.zeros(max(nbytes, 2 << 20) // 4, dtype=torch.float32, device=self.device)
+        self.peers = [self.buffer]
+        if self.world > 1:
+            torch.cuda.synchronize(self.device)
+            handles = [None] * self.world
+            dist.all_gather_object(handles, reduce_tensor(self.buffer), group=group)
+            self.peers = []
+            for r, (rebuild, rebuild_args) in enumerate(handles):
+                self.peers.append(self.buffer if r == self.rank else rebuild(*rebuild_args))
+            with torch.cuda.device(self.device):
+                for t in self.peers:
+                    if t.device != self.device:
+                        _lib.check(self.lib.kdw_enable_peer_access(t.device.index))
+            dist.barrier(group)  # every buffer is zeroed and mapped before anybody pushes
+        self._ptrs = (ctypes.c_void_p * self.world)(*[t.data_ptr() for t in self.peers])
+        self.seq = 0
+
+    def __call__(self, local, out=None):
+        """Returns the sum over ranks of `local` (fp32, contiguous, on this rank's device, numel <= max_numel)."""
+        assert local.dtype == torch.float32 and local.is_contiguous() and local.device == self.device
+        n = local.numel()
+        assert 0 < n <= self.max_numel, f'numel {n} exceeds the {self.max_numel} this reducer was built for'
+        if out is None:
+            out = torch.empty_like(local)
+        assert out.dtype == torch.float32 and out.is_contiguous() and out.numel() == n
+        self.seq = self.seq % 0xFFFFFFFE + 1  # 1, 2, ..., 2^32-2, 1, ...: never 0, parity always alternates
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            self._lib.check(self.lib.kdw_allreduce_push_f32(local.data_ptr(), out.data_ptr(), None, self._ptrs, n,
+                                                             self.rank, self.world, self.seq,
+                                                             self.timeout_ns, ctypes.c_void_p(stream)))
+        return out
+
+
+def _reduce(dw, group, reducer):
+    if reducer is not None:
+        return reducer(dw)
+    dist.all_reduce(dw, group=group)
+    return dw
 
 
 def shard_planes(H, world, rank):
@@ -117,9 +189,9 @@ def hsharded_fprop(x_halo, weight, group=None, ops=None, halo_ready=None):
     return y
 
 
-def hsharded_wgrad(x_halo, grad, group=None, ops=None, halo_ready=None, reduce=True):
+def hsharded_wgrad(x_halo, grad, group=None, ops=None, halo_ready=None, reduce=True, reducer=None):
     """Weight gradient of the whole (sharded) volume, fp32 [3,3,3,C], identical on every rank when reduce=True.
-    grad: (N, C, Hs, W, D), the owned planes only."""
+    grad: (N, C, Hs, W, D), the owned planes only.  `reducer`: a GradPushAllReduce to use instead of NCCL."""
     ops = ops or CudaOps()
     Hs = x_halo.shape[2] - 2
     finish = halo_ready if halo_ready is not None else exchange_halo(x_halo, group)
@@ -132,11 +204,11 @@ def hsharded_wgrad(x_halo, grad, group=None, ops=None, halo_ready=None, reduce=T
     else:
         dw = ops.wgrad_range(x_halo, grad, 1, Hs + 1, 1)
     if reduce:
-        dist.all_reduce(dw, group=group)
+        dw = _reduce(dw, group, reducer)
     return dw
 
 
-def sample_sharded_step(x, weight, grad, group=None, ops=None):
+def sample_sharded_step(x, weight, grad, group=None, ops=None, reducer=None):
     """Data-parallel slice of a training step: y = DWConv(x) for the local samples and the weight gradient of
     the global batch.  Returns (y, dw_fp32): the local output and the all-reduced fp32 [3,3,3,C] gradient."""
     ops = ops or CudaOps()
@@ -145,5 +217,5 @@ def sample_sharded_step(x, weight, grad, group=None, ops=None):
     ops.fprop_range(x, weight, y, 0, H, 0)
     dw = ops.wgrad_range(x, grad, 0, H, 0)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_reduce(dw, group=group)
+        dw = _reduce(dw, group, reducer)
     return y, dw

@@ -46,8 +46,25 @@ def _worker(rank, world, port, shape, out_dir):
         dw = kd.hsharded_wgrad(xh, gl)
         ys, dws = kd.sample_sharded_step(x[rank::world].contiguous(memory_format=torch.channels_last_3d), w,
                                          grad[rank::world].contiguous(memory_format=torch.channels_last_3d))
+        # the library's own all-reduce over peer memory against NCCL's
+        red = kd.GradPushAllReduce(27 * C, timeout_s=5.0)
+        gl_ = torch.Generator(device=dev).manual_seed(1234 + rank)
+        push_equal, push_err = True, 0.0
+        for it in range(6):
+            local = torch.randn(27 * C, generator=gl_, device=dev)
+            ref = local.clone()
+            dist.all_reduce(ref)
+            got = red(local)
+            push_err = max(push_err, float((got - ref).abs().max() / ref.abs().max()))
+            push_equal = push_equal and bool(torch.equal(got, ref))
+        _, dws_push = kd.sample_sharded_step(x[rank::world].contiguous(memory_format=torch.channels_last_3d), w,
+                                             grad[rank::world].contiguous(memory_format=torch.channels_last_3d),
+                                             reducer=red)
         torch.cuda.synchronize()
         ok = {
+            'push_err': push_err,
+            'push_equal': push_equal,
+            'dp_wgrad_push': float((dws_push.double() - dw_full.double()).norm() / dw_full.double().norm()),
             'fprop': bool(torch.equal(y, y_full[:, :, hb:he])),
             'wgrad': float((dw.double() - dw_full.double()).norm() / dw_full.double().norm()),
             'dp_fprop': bool(torch.equal(ys, y_full[rank::world])),
@@ -69,4 +86,7 @@ def test_sharded_paths_on_gpus(tmp_path, shape):
         res = torch.load(os.path.join(str(tmp_path), f'rank{r}.pt'))
         assert res['fprop'] and res['dp_fprop'], res
         assert res['wgrad'] <= 1e-5 and res['dp_wgrad'] <= 1e-5, res
+        assert res['push_err'] <= 1e-6 and res['dp_wgrad_push'] <= 1e-5, res
+        if world == 2:
+            assert res['push_equal'], res  # two addends: any order gives the same bits
         assert res['status'] == 0
