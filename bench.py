@@ -220,6 +220,28 @@ METRIC = 'DWConv + DWConvWGRAD algorithmic HBM GB/s at (1,C,350,350,128) fp16 ch
 # ----------------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------------
+def make_reducer(args, numel, world):
+    """The library's one-kernel all-reduce over peer memory, or None for NCCL's (also when the peer mappings
+    cannot be set up on this machine)."""
+    if world == 1 or args.allreduce != 'push':
+        return None
+    import torch.distributed as dist
+
+    from kerops_b200 import dist as kd
+
+    red, ok = None, 1
+    try:
+        red = kd.GradPushAllReduce(numel)
+    except Exception as e:  # e.g. no CUDA IPC between the ranks
+        print(f'bench: peer-memory all-reduce unavailable ({type(e).__name__}: {e}); using NCCL', file=sys.stderr)
+        ok = 0
+    import torch
+
+    flag = torch.tensor([ok], device='cuda')
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return red if int(flag.item()) == 1 else None
+
+
 def make_gpu_inputs(C, device, seed):
     import torch
 
@@ -261,6 +283,8 @@ def run_ours(args):
         slot[C] = bucket[off:off + 27 * C]
         off += 27 * C
 
+    reducer, bucket_out = make_reducer(args, bucket.numel(), world), torch.empty_like(bucket)
+
     def step(events=None):
         for C in channels:
             x, grad, w = data[C]
@@ -276,7 +300,10 @@ def run_ours(args):
                 events.append((C, e0, e1, e2))
             del y
         if world > 1:
-            dist.all_reduce(bucket)
+            if reducer is not None:
+                reducer(bucket, out=bucket_out)
+            else:
+                dist.all_reduce(bucket)
 
     def barrier():
         torch.cuda.synchronize()
@@ -373,10 +400,11 @@ def run_ours(args):
                             + ','.join(map(str, channels)) + '; one sample per GPU',
                 'l2': 'inputs larger than L2 (smallest tensor 251 MB; 31 GB touched per step)',
                 'parallelism': f'dp{world}' if world > 1 else 'single',
+                'allreduce': ('push kernel over peer memory' if reducer is not None else 'nccl') if world > 1 else None,
             },
             'roofline': roofline, 'roofline_fprop': roof('fprop'), 'roofline_wgrad': roof('wgrad'),
             'cpu_baseline': cpu_baseline, 'e2e': e2e, 'clocks': clocks,
-            'gpu_launches': 3 * len(channels) * args.steps, 'detail': detail, 'device_status': status,
+            'gpu_launches': (3 * len(channels) + (1 if reducer is not None else 0)) * args.steps, 'detail': detail, 'device_status': status,
         }
         if triton_ref is not None:
             line['reference_triton_on_this_gpu'] = triton_ref
@@ -493,6 +521,8 @@ def run_dshard(args):
     grad = torch.randn(1, Hs, W, D, C, generator=g, device=dev, dtype=torch.float16).permute(0, 4, 1, 2, 3)
     w = ((torch.rand(3, 3, 3, C, generator=g, device=dev) * 2 - 1) / math.sqrt(27)).to(torch.float16)
 
+    reducer = make_reducer(args, 27 * C, world)
+
     class Single:  # one rank: no neighbours, the halo planes stay zero
         @staticmethod
         def finish():
@@ -502,7 +532,7 @@ def run_dshard(args):
         if world > 1:
             fin = kd.exchange_halo(xh)
             y = kd.hsharded_fprop(xh, w, halo_ready=fin)
-            dw = kd.hsharded_wgrad(xh, grad, halo_ready=lambda: None)  # halo already in place
+            dw = kd.hsharded_wgrad(xh, grad, halo_ready=lambda: None, reducer=reducer)  # halo already in place
         else:
             y = kd.hsharded_fprop(xh, w, halo_ready=Single.finish)
             dw = kd.hsharded_wgrad(xh, grad, halo_ready=Single.finish, reduce=False)
@@ -542,12 +572,14 @@ def run_dshard(args):
             'ms_per_step': round(ms / args.steps, 4), 'higher_is_better': True, 'scaling': 'strong',
             'vs_baseline': None, 'dtype': 'f16 products, f32 accumulation', 'data': 'synthetic',
             'config': {'workload': f'configs[3]: (1,128,{H},350,128) split along H over {world} rank(s), 1-plane halos '
-                                   'over NCCL point-to-point, fp32 [27][128] gradient all-reduced',
+                                   'over NCCL point-to-point, fp32 [27][128] gradient all-reduced ('
+                                   + ('push kernel over peer memory' if reducer is not None else 'nccl') + ')',
                        'l2': 'inputs larger than L2', 'parallelism': f'hshard{world}'},
             'roofline': {'bound': 'hbm', 'kernel': 'fprop + wgrad, whole step', 'achieved': round(value / world, 1),
                          'peak': peak, 'peak_kind': peak_kind, 'unit': 'GB/s', 'frac': round(value / world / peak, 4),
                          'traffic': None},
-            'clocks': clocks, 'gpu_launches': (9 if world > 1 else 3) * args.steps, 'device_status': status,
+            'clocks': clocks, 'gpu_launches': ((9 if world > 1 else 3) + (1 if reducer is not None else 0)) * args.steps,
+            'device_status': status,
         }), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -594,15 +626,16 @@ def run_dpstep(args):
             dist.barrier()
             torch.cuda.synchronize()
 
+    reducer = make_reducer(args, 27 * C, world)
     for _ in range(args.warmup):
-        kd.sample_sharded_step(x, w, grad)
+        kd.sample_sharded_step(x, w, grad, reducer=reducer)
     barrier()
     sampler = ClockSampler(dev)
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        kd.sample_sharded_step(x, w, grad)
+        kd.sample_sharded_step(x, w, grad, reducer=reducer)
     e1.record()
     barrier()
     clocks = sampler.stop()
@@ -622,12 +655,14 @@ def run_dpstep(args):
             'ms_per_step': round(ms / args.steps, 4), 'higher_is_better': True, 'scaling': 'strong',
             'vs_baseline': None, 'dtype': 'f16 products, f32 accumulation', 'data': 'synthetic',
             'config': {'workload': f'configs[4]: batch {batch} x (32,{H},350,128), {n_local} sample(s) per rank; DWConv, '
-                                   'DWConvWGRAD, all-reduce of the fp32 [27][32] gradient',
+                                   'DWConvWGRAD, all-reduce of the fp32 [27][32] gradient ('
+                                   + ('push kernel over peer memory' if reducer is not None else 'nccl') + ')',
                        'l2': 'inputs larger than L2', 'parallelism': f'dp{world}'},
             'roofline': {'bound': 'hbm', 'kernel': 'fprop + wgrad, whole step', 'achieved': round(value / world, 1),
                          'peak': peak, 'peak_kind': peak_kind, 'unit': 'GB/s', 'frac': round(value / world / peak, 4),
                          'traffic': None},
-            'clocks': clocks, 'gpu_launches': 3 * args.steps, 'device_status': status,
+            'clocks': clocks, 'gpu_launches': (3 + (1 if reducer is not None else 0)) * args.steps,
+            'device_status': status,
         }), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -646,6 +681,9 @@ def main():
                     help="'sweep' (default): the headline per-C sweep, one sample per GPU; 'dshard': one large volume "
                          "sharded along H over the GPUs; 'dpstep': a batch of (32,350,350,128) samples split by sample")
     ap.add_argument('--dp-batch', type=int, default=8)
+    ap.add_argument('--allreduce', default='push', choices=['nccl', 'push'],
+                    help="how the fp32 weight gradients are summed over the ranks: NCCL, or the library's own "
+                         'push/flag/sum kernel over peer memory')
     ap.add_argument('--dshard-planes', type=int, default=1400)
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-cpu-baseline', action='store_true')

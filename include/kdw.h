@@ -149,7 +149,8 @@ int kdw_wgrad_variant_channels(int id);
  *
  * Every rank owns one exchange buffer of kdw_allreduce_buffer_bytes(n, world) bytes, zero-filled once before the
  * first call, and can address the buffers of all ranks (`buffers[r]`, device pointers valid in the calling
- * process: CUDA IPC mappings or any other peer mapping; buffers[rank] is the rank's own).  One kernel on each
+ * process, mapped with access for the calling GPU, e.g. torch symmetric memory or cuMemMap +
+ * cuMemSetAccess; buffers[rank] is the rank's own).  One kernel on each
  * rank writes `local` (n fp32 values, e.g. the [3][3][3][C] gradient from kdw_wgrad_f16) into its slot of
  * every buffer, raises a flag there, waits for the flags of all ranks in its own buffer and writes the sum,
  * added in rank order, to out_f32 and/or out_f16 - the same bits on every rank.
@@ -163,13 +164,6 @@ int kdw_wgrad_variant_channels(int id);
 int64_t kdw_allreduce_buffer_bytes(int64_t n, int world);
 int kdw_allreduce_push_f32(const float* local, float* out_f32, void* out_f16, void* const* buffers, int64_t n, int rank,
                            int world, uint32_t seq, int64_t timeout_ns, void* stream);
-
-/*
- * Lets kernels on the CURRENT device address memory of `peer_device` (cudaDeviceEnablePeerAccess; already
- * enabled is not an error).  Needed once per peer before kdw_allreduce_push_f32 when the peer buffers were
- * mapped without it.  No reference counterpart.
- */
-int kdw_enable_peer_access(int peer_device);
 
 #ifdef __cplusplus
 }

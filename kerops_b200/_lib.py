@@ -36,7 +36,6 @@ SIGNATURES = {
     'kdw_wgrad_variant_channels': (_int, [_int]),
     'kdw_allreduce_buffer_bytes': (_i64, [_i64, _int]),
     'kdw_allreduce_push_f32': (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _int, _int, ctypes.c_uint32, _i64, _ptr]),
-    'kdw_enable_peer_access': (_int, [_int]),
 }
 
 _lib = None

@@ -131,23 +131,4 @@ int kdw_allreduce_push_f32(const float* local, float* out_f32, void* out_f16, vo
     return 0;
 }
 
-int kdw_enable_peer_access(int peer_device) {
-    int dev = 0;
-    KDW_CUDA(cudaGetDevice(&dev));
-    if (peer_device == dev) return 0;
-    int can = 0;
-    KDW_CUDA(cudaDeviceCanAccessPeer(&can, dev, peer_device));
-    if (!can) {
-        kdw::set_error("device %d cannot access device %d directly", dev, peer_device);
-        return (int)cudaErrorPeerAccessUnsupported;
-    }
-    cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
-    if (e == cudaErrorPeerAccessAlreadyEnabled) {
-        (void)cudaGetLastError();  // not an error: clear it
-        return 0;
-    }
-    KDW_CUDA(e);
-    return 0;
-}
-
 }  // extern "C"

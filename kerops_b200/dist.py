@@ -55,12 +55,11 @@ class GradPushAllReduce:
     adds the slots in rank order, so every rank gets the same bits.  A collective: construct it and call it on
     every rank of `group`, always from the same stream.
 
-    The exchange buffers come from torch's allocator and are shared with the other ranks of the node as CUDA
-    IPC mappings (the same mechanism torch.multiprocessing uses to pass CUDA tensors between processes)."""
+    The exchange buffers are torch symmetric memory (torch.distributed._symmetric_memory): every rank allocates
+    one, the rendezvous maps all of them into every process with access for the local GPU, and the kernel gets
+    their addresses.  NVLink multicast is not used and is switched off for the mapping."""
 
     def __init__(self, max_numel, group=None, device=None, timeout_s=10.0):
-        from torch.multiprocessing.reductions import reduce_tensor
-
         from . import _lib
 
         self._lib = _lib
@@ -74,22 +73,29 @@ class GradPushAllReduce:
         nbytes = self.lib.kdw_allreduce_buffer_bytes(self.max_numel, self.world)
         if nbytes <= 0:
             raise ValueError(f'GradPushAllReduce: max_numel={max_numel}, world={self.world} not supported')
-        # an allocation of its own (not a slice of a cached block), zero = "no flag raised yet"
-        self.buffer = torch.zeros(max(nbytes, 2 << 20) // 4, dtype=torch.float32, device=self.device)
-        self.peers = [self.buffer]
-        if self.world > 1:
-            torch.cuda.synchronize(self.device)
-            handles = [None] * self.world
-            dist.all_gather_object(handles, reduce_tensor(self.buffer), group=group)
-            self.peers = []
-            for r, (rebuild, rebuild_args) in enumerate(handles):
-                self.peers.append(self.buffer if r == self.rank else rebuild(*rebuild_args))
+        if self.world == 1:
+            self.buffer = torch.zeros(nbytes // 4, dtype=torch.float32, device=self.device)
+            ptrs = [self.buffer.data_ptr()]
+        else:
+            import os
+
+            os.environ.setdefault('TORCH_SYMM_MEM_DISABLE_MULTICAST', '1')
+            import torch.distributed._symmetric_memory as symm_mem
+
+            pg = group if group is not None else dist.group.WORLD
             with torch.cuda.device(self.device):
-                for t in self.peers:
-                    if t.device != self.device:
-                        _lib.check(self.lib.kdw_enable_peer_access(t.device.index))
+                self.buffer = symm_mem.empty(nbytes // 4, dtype=torch.float32, device=self.device)
+                self.buffer.zero_()  # zero = "no flag raised yet"
+                torch.cuda.synchronize(self.device)
+                try:
+                    self.handle = symm_mem.rendezvous(self.buffer, pg)
+                except TypeError:
+                    self.handle = symm_mem.rendezvous(self.buffer, pg.group_name)
+            ptrs = [int(p) for p in self.handle.buffer_ptrs]
+            if len(ptrs) != self.world or ptrs[self.rank] != self.buffer.data_ptr() or not all(ptrs):
+                raise RuntimeError(f'GradPushAllReduce: unexpected peer mapping {ptrs} (own {self.buffer.data_ptr()})')
             dist.barrier(group)  # every buffer is zeroed and mapped before anybody pushes
-        self._ptrs = (ctypes.c_void_p * self.world)(*[t.data_ptr() for t in self.peers])
+        self._ptrs = (ctypes.c_void_p * self.world)(*ptrs)
         self.seq = 0
 
     def __call__(self, local, out=None):
