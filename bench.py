@@ -165,8 +165,9 @@ def cpu_step(x, grad, w, dtype):
     return y.detach().to(torch.float16), wt.grad
 
 
-def time_cpu_arm(C, steps, warmup):
-    """Seconds per step (median) of the faster of the fp32 / fp16 torch CPU paths, and its name."""
+def time_cpu_arm(C, steps, warmup, min_seconds=0.0):
+    """Seconds per step (median) of the faster of the fp32 / fp16 torch CPU paths, its name, the CPU seconds spent
+    in its timed steps and their number.  At least `steps` steps, and more until `min_seconds` of work are done."""
     import torch
 
     x, grad, w = make_cpu_inputs(C)
@@ -176,13 +177,13 @@ def time_cpu_arm(C, steps, warmup):
             for _ in range(warmup):
                 cpu_step(x, grad, w, dtype)
             ts = []
-            for _ in range(steps):
+            while len(ts) < steps or (sum(ts) < min_seconds and len(ts) < 500):
                 t0 = time.perf_counter()
                 cpu_step(x, grad, w, dtype)
                 ts.append(time.perf_counter() - t0)
             med = statistics.median(ts)
             if best is None or med < best[0]:
-                best = (med, str(dtype).replace('torch.', ''), sum(ts))
+                best = (med, str(dtype).replace('torch.', ''), sum(ts), len(ts))
         except Exception:
             continue
     if best is None:
@@ -198,7 +199,7 @@ def run_reference(args):
         return
     C = 8
     cores = torch.get_num_threads()
-    med, dtype, _ = time_cpu_arm(C, args.steps, max(1, args.warmup))
+    med, dtype, _, _ = time_cpu_arm(C, args.steps, max(1, args.warmup))
     nbytes = 2 * algorithmic_bytes(C)
     value = nbytes / med / 1e9
     sample = f'one (1,{C},350,350,128) volume per step: conv3d(groups=C) forward + weight gradient, torch CPU {dtype}'
@@ -382,11 +383,11 @@ def run_ours(args):
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cores = torch.get_num_threads()
-        med, dtype, spent = time_cpu_arm(8, steps=2, warmup=1)
+        med, dtype, spent, n_cpu = time_cpu_arm(8, steps=2, warmup=1, min_seconds=8.0)
         cpu_baseline = {
             'value': round(2 * algorithmic_bytes(8) / med / 1e9, 3), 'unit': 'GB/s', 'cores': cores, 'kind': 'port',
             'sample': f'(1,8,350,350,128) only: torch CPU conv3d(groups=8) forward + weight gradient in {dtype}, '
-                      f'median of 2 steps after 1 warm-up ({spent:.1f} s of CPU work)',
+                      f'median of {n_cpu} steps after 1 warm-up ({spent:.1f} s of CPU work)',
         }
     triton_ref = measure_triton_reference(channels, data, dev) if (args.compare_triton and rank == 0) else None
 
