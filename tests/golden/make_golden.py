@@ -36,6 +36,8 @@ CASES = [
     ('odd_n1_c16_3x2x37', 2, 1, 16, 3, 2, 37),
     ('batch_n2_c32_4x6x9', 3, 2, 32, 4, 6, 9),
     ('tiny_n1_c8_2x2x2', 4, 1, 8, 2, 2, 2),
+    ('c64_n1_3x5x20', 5, 1, 64, 3, 5, 20),
+    ('c128_n2_2x3x10', 6, 2, 128, 2, 3, 10),
 ]
 
 
@@ -87,9 +89,13 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--reference', default='/root/reference')
     ap.add_argument('--out', default=os.path.dirname(os.path.abspath(__file__)))
+    ap.add_argument('--only', default='', help='comma-separated case names (default: all)')
     args = ap.parse_args()
     DWConv, DWConvWGRAD = load_reference(args.reference)
+    only = set(filter(None, args.only.split(',')))
     for name, seed, N, C, s1, s2, s3 in CASES:
+        if only and name not in only:
+            continue
         x, grad, w_ker = make_inputs(seed, N, C, s1, s2, s3)
         y = DWConv(x, w_ker)
         dw = DWConvWGRAD(x, grad)
