@@ -336,11 +336,14 @@ def run_ours(args):
     detail = {'fprop': {}, 'wgrad': {}}
     tot = {'fprop': [0.0, 0.0], 'wgrad': [0.0, 0.0]}  # ms, bytes
     for C in channels:
-        f_ms = statistics.mean(e0.elapsed_time(e1) for (c, e0, e1, e2) in events if c == C)
-        w_ms = statistics.mean(e1.elapsed_time(e2) for (c, e0, e1, e2) in events if c == C)
-        for kind, ms in (('fprop', f_ms), ('wgrad', w_ms)):
+        f_all = [e0.elapsed_time(e1) for (c, e0, e1, e2) in events if c == C]
+        w_all = [e1.elapsed_time(e2) for (c, e0, e1, e2) in events if c == C]
+        for kind, all_ms in (('fprop', f_all), ('wgrad', w_all)):
+            ms = statistics.mean(all_ms)
             gbs = algorithmic_bytes(C) / (ms * 1e-3) / 1e9
-            detail[kind][str(C)] = {'ms': round(ms, 4), 'gbs': round(gbs, 1), 'frac': round(gbs / peak, 4)}
+            detail[kind][str(C)] = {'ms': round(ms, 4), 'ms_median': round(statistics.median(all_ms), 4),
+                                    'ms_min': round(min(all_ms), 4), 'gbs': round(gbs, 1),
+                                    'frac': round(gbs / peak, 4), 'frac_of_nominal_8000': round(gbs / 8000.0, 4)}
             tot[kind][0] += ms
             tot[kind][1] += algorithmic_bytes(C)
     # torch.clone of the same tensors, the comparator the reference's README uses
@@ -357,6 +360,8 @@ def run_ours(args):
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / 5
         clone[str(C)] = {'ms': round(ms, 4), 'gbs': round(algorithmic_bytes(C) / (ms * 1e-3) / 1e9, 1)}
+        for kind in ('fprop', 'wgrad'):
+            detail[kind][str(C)]['x_clone'] = round(detail[kind][str(C)]['ms'] / ms, 3)
     detail['clone'] = clone
 
     def roof(kind):
