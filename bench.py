@@ -83,7 +83,9 @@ class ClockSampler:
         self.samples, self.reasons, self.err = [], set(), None
         self.max_mhz = None
         self._stop = threading.Event()
+        self._recording = threading.Event()
         self._thread = None
+        self.period_s = 0.01
         try:
             import pynvml
             import torch
@@ -109,28 +111,42 @@ class ClockSampler:
         nv = self.nv
         while not self._stop.is_set():
             try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
                 try:
                     mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
                 except Exception:
                     mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
-                for bit, name in self.REASONS.items():
-                    if mask & bit:
-                        self.reasons.add(name)
+                if self._recording.is_set():
+                    self.samples.append(mhz)
+                    for bit, name in self.REASONS.items():
+                        if mask & bit:
+                            self.reasons.add(name)
             except Exception as e:
                 self.err = f'{type(e).__name__}: {e}'
                 return
-            time.sleep(0.004)
+            time.sleep(self.period_s)
 
     def start(self):
+        """Starts polling.  Call it BEFORE the warm-up: the first NVML queries of a process stall its CUDA
+        launches for milliseconds (more with several ranks on one node); samples are kept only after begin()."""
         if self.err is None:
             self._thread = threading.Thread(target=self._run, daemon=True)
             self._thread.start()
+
+    def begin(self):
+        """Marks the start of the timed region."""
+        self.samples, self.reasons = [], set()
+        self._recording.set()
 
     def stop(self):
         self._stop.set()
         if self._thread is not None:
             self._thread.join()
+        if not self.samples and self.err is None:  # timed region shorter than one polling period
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+            except Exception as e:
+                self.err = f'{type(e).__name__}: {e}'
         out = {'sm_mhz': statistics.median(self.samples) if self.samples else None, 'sm_max_mhz': self.max_mhz,
                'reasons': sorted(self.reasons), 'samples': len(self.samples)}
         if self.err:
@@ -312,11 +328,12 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize()
 
+    sampler = ClockSampler(dev)
+    sampler.start()
     for _ in range(args.warmup):
         step()
     barrier()
-    sampler = ClockSampler(dev)
-    sampler.start()
+    sampler.begin()
     events = []
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_start.record()
@@ -550,11 +567,12 @@ def run_dshard(args):
             dist.barrier()
             torch.cuda.synchronize()
 
+    sampler = ClockSampler(dev)
+    sampler.start()
     for _ in range(args.warmup):
         step()
     barrier()
-    sampler = ClockSampler(dev)
-    sampler.start()
+    sampler.begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
@@ -633,11 +651,12 @@ def run_dpstep(args):
             torch.cuda.synchronize()
 
     reducer = make_reducer(args, 27 * C, world)
+    sampler = ClockSampler(dev)
+    sampler.start()
     for _ in range(args.warmup):
         kd.sample_sharded_step(x, w, grad, reducer=reducer)
     barrier()
-    sampler = ClockSampler(dev)
-    sampler.start()
+    sampler.begin()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
