@@ -441,7 +441,7 @@ def measure_e2e(args, channels, dev, world, rank):
     import torch
     import torch.distributed as dist
 
-    from kerops_b200.host import DWConvHost, DWConvWGRADHost
+    from kerops_b200.host import DWConvHost, DWConvStepHost, DWConvWGRADHost
 
     if args.no_e2e:
         return None
@@ -459,10 +459,15 @@ def measure_e2e(args, channels, dev, world, rank):
 
     wts = {C: ((torch.rand(3, 3, 3, C) * 2 - 1) / math.sqrt(27)).to(torch.float16).pin_memory() for C in channels}
 
+    fused = args.e2e_api == 'step'
+
     def step():
         for C in channels:
-            DWConvHost(view(pool[0], C), wts[C], out=view(pool[2], C), device=dev)
-            DWConvWGRADHost(view(pool[0], C), view(pool[1], C), device=dev)
+            if fused:  # x crosses the bus once and feeds both kernels
+                DWConvStepHost(view(pool[0], C), wts[C], view(pool[1], C), out=view(pool[2], C), device=dev)
+            else:
+                DWConvHost(view(pool[0], C), wts[C], out=view(pool[2], C), device=dev)
+                DWConvWGRADHost(view(pool[0], C), view(pool[1], C), device=dev)
 
     n = max(1, min(args.steps, 3))
     step()
@@ -478,12 +483,15 @@ def measure_e2e(args, channels, dev, world, rank):
         t = torch.tensor([dt], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dt = float(t.item())
-    h2d = sum(3 * 2 * VOX * C + 54 * C for C in channels)  # x for fprop; x and grad for wgrad; weights
+    # split calls: x for fprop, x and grad for wgrad; fused step: x and grad once; plus the weights
+    h2d = sum((2 if fused else 3) * 2 * VOX * C + 54 * C for C in channels)
     d2h = sum(2 * VOX * C + 54 * C for C in channels)      # y; dw
     nbytes = sum(2 * algorithmic_bytes(C) for C in channels) * world
     return {'value': round(nbytes * n / dt / 1e9, 2), 'unit': 'GB/s', 'h2d_bytes_per_step': h2d,
             'd2h_bytes_per_step': d2h, 'steps': n, 'ms_per_step': round(dt / n * 1e3, 2),
-            'api': 'kerops_b200.host.DWConvHost / DWConvWGRADHost (pinned host buffers, slab pipeline)'}
+            'api': ('kerops_b200.host.DWConvStepHost (forward + weight gradient of one host volume per call'
+                    if fused else 'kerops_b200.host.DWConvHost then DWConvWGRADHost (two calls per volume')
+                   + '; pinned host buffers, slab pipeline)'}
 
 
 def measure_triton_reference(channels, data, dev):
@@ -711,6 +719,9 @@ def main():
                          'push/flag/sum kernel over peer memory')
     ap.add_argument('--dshard-planes', type=int, default=1400)
     ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--e2e-api', default='step', choices=['step', 'split'],
+                    help="'step': one DWConvStepHost call per volume (x is copied once); 'split': DWConvHost and "
+                         'DWConvWGRADHost as two calls')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--compare-triton', action='store_true',
                     help='also time the reference Triton kernels from baseline/_ref on this GPU')

@@ -12,6 +12,9 @@ import torch
 from .ops.conv import _launch
 
 
+__all__ = ['DWConvHost', 'DWConvWGRADHost', 'DWConvStepHost']
+
+
 def _slabs(H, planes):
     return [(h0, min(H, h0 + planes)) for h0 in range(0, H, planes)]
 
@@ -114,3 +117,62 @@ def DWConvWGRADHost(x, grad, *, device='cuda', slab_planes=None):
     g_dev.record_stream(s_in)
     result = total.to(torch.float16).cpu()
     return result
+
+
+def DWConvStepHost(x, weight, grad, out=None, *, device='cuda', slab_planes=None, ACCTYPE='float32'):
+    """Forward pass AND weight gradient of a host volume in one sweep: every slab of x crosses the bus once and
+    feeds both kernels (a training step needs y = DWConv(x, weight) and dw = DWConvWGRAD(x, grad) of the same x).
+    Returns (y, dw): y a pinned host tensor shaped like x (or `out`), dw fp16 [3, 3, 3, C] on the host."""
+    _check_host_volume(x, 'x')
+    _check_host_volume(grad, 'grad')
+    assert x.shape == grad.shape
+    N, C, H, W, D = x.shape
+    assert list(weight.shape) == [3, 3, 3, C] and weight.dtype == torch.float16
+    dev = torch.device(device)
+    if out is None:
+        out = torch.empty_like(x, pin_memory=True)
+    else:
+        _check_host_volume(out, 'out')
+        assert out.shape == x.shape
+    if x.numel() == 0:
+        return out, torch.zeros([3, 3, 3, C], dtype=torch.float16)
+    if slab_planes is None:
+        slab_planes = max(1, min(H, (64 << 20) // max(1, W * D * C * 2)))
+    w_dev = weight.to(dev, non_blocking=True).contiguous()
+    x_dev = torch.empty_like(x, device=dev)
+    g_dev = torch.empty_like(x, device=dev)
+    y_dev = torch.empty_like(x, device=dev)
+    main = torch.cuda.current_stream(dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    s_in.wait_stream(main)
+    s_out.wait_stream(main)
+    work = [(n, h0, h1) for n in range(N) for (h0, h1) in _slabs(H, slab_planes)]
+    copied = []
+    for (n, h0, h1) in work:
+        with torch.cuda.stream(s_in):
+            _phys(x_dev)[n, h0:h1].copy_(_phys(x)[n, h0:h1], non_blocking=True)
+            _phys(g_dev)[n, h0:h1].copy_(_phys(grad)[n, h0:h1], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(s_in)
+            copied.append(ev)
+    ws = _launch.wgrad_workspace(x_dev)
+    total = torch.zeros([3, 3, 3, C], dtype=torch.float32, device=dev)
+    for i, (n, h0, h1) in enumerate(work):
+        need = i + 1 if (i + 1 < len(work) and work[i + 1][0] == n) else i
+        main.wait_event(copied[need])
+        _launch.fprop(x_dev[n:n + 1], w_dev, y_dev[n:n + 1], h_begin=h0, h_end=h1, y_h0=0, acc=ACCTYPE)
+        done = torch.cuda.Event()
+        done.record(main)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(done)
+            _phys(out)[n, h0:h1].copy_(_phys(y_dev)[n, h0:h1], non_blocking=True)
+        dw32, _ = _launch.wgrad(x_dev[n:n + 1], g_dev[n:n + 1], h_begin=h0, h_end=h1, g_h0=0, want_f32=True,
+                                want_f16=False, workspace=ws)
+        total += dw32
+    main.wait_stream(s_out)
+    x_dev.record_stream(s_in)
+    g_dev.record_stream(s_in)
+    y_dev.record_stream(s_out)
+    dw = total.to(torch.float16).cpu()  # synchronises the current stream
+    main.synchronize()
+    return out, dw
