@@ -44,12 +44,12 @@ FALLBACK_HBM_GBS = 6650.0
 # 350/100 planes (traffic grows in proportion to the planes a launch processes).  Bytes per (1,C,350,350,128)
 # launch; None where no capture has been taken.
 NCU_TRAFFIC = {
-    ('fprop', 8): int((0.078771 + 0.026808) * 3.5e9),
-    ('wgrad', 8): int((0.151665 + 0.004278) * 3.5e9),
-    ('fprop', 32): int((0.290659 + 0.248993) * 3.5e9),
-    ('wgrad', 32): int((0.578764 + 0.005286) * 3.5e9),
-    ('fprop', 128): int((1.467924 + 1.127809) * 3.5e9),
-    ('wgrad', 128): int((2.405677 + 0.015345) * 3.5e9),
+    ('fprop', 8): int((0.078729 + 0.025757) * 3.5e9),
+    ('wgrad', 8): int((0.150921 + 0.003749) * 3.5e9),
+    ('fprop', 32): int((0.290699 + 0.250010) * 3.5e9),
+    ('wgrad', 32): int((0.618345 + 0.005101) * 3.5e9),
+    ('fprop', 128): int((1.472090 + 1.127703) * 3.5e9),
+    ('wgrad', 128): int((2.365841 + 0.009408) * 3.5e9),
 }
 
 
