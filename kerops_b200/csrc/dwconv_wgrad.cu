@@ -83,6 +83,54 @@ __global__ void __launch_bounds__(128) wgrad_plain_kernel(const __half* __restri
 // ------------------------------------------------------------------------------------------------
 // TMA pass 1
 // ------------------------------------------------------------------------------------------------
+// Adds the consumer threads' accumulators for channel slice c0 to the CTA's workspace row and clears them:
+// shuffle reduction over the lanes that share channels, then the warps take turns in a fixed order through
+// shared memory (no atomics, so the sum is reproducible).  Called by all consumer threads of the CTA.
+template <class Cfg>
+__device__ __forceinline__ void flush_acc(float2 (&acc)[27][Cfg::CP], float* red, float* row, int C, int c0, int tid) {
+    constexpr int CS = Cfg::CS, CP = Cfg::CP, CPG = Cfg::CPG, NCW = Cfg::NCW;
+    const int lane = tid & 31, warp = tid >> 5, cg = tid % CPG;
+#pragma unroll
+    for (int k = 0; k < 27; ++k)
+#pragma unroll
+        for (int i = 0; i < CP; ++i) {
+            float2 v = acc[k][i];
+#pragma unroll
+            for (int off = CPG; off < 32; off <<= 1) {
+                v.x += __shfl_xor_sync(0xffffffffu, v.x, off);
+                v.y += __shfl_xor_sync(0xffffffffu, v.y, off);
+            }
+            acc[k][i] = v;
+        }
+    for (int wi = 0; wi < NCW; ++wi) {
+        if (warp == wi && lane < CPG) {
+#pragma unroll
+            for (int k = 0; k < 27; ++k)
+#pragma unroll
+                for (int i = 0; i < CP; ++i) {
+                    float* dst = red + k * CS + cg * 2 * CP + 2 * i;
+                    if (wi == 0) {
+                        dst[0] = acc[k][i].x;
+                        dst[1] = acc[k][i].y;
+                    } else {
+                        dst[0] += acc[k][i].x;
+                        dst[1] += acc[k][i].y;
+                    }
+                }
+        }
+        named_barrier_sync(1, Cfg::NT);
+    }
+    for (int e = tid; e < 27 * CS; e += Cfg::NT) {
+        const int k = e / CS, c = e % CS;
+        row[k * C + c0 + c] += red[e];
+    }
+    named_barrier_sync(1, Cfg::NT);
+#pragma unroll
+    for (int k = 0; k < 27; ++k)
+#pragma unroll
+        for (int i = 0; i < CP; ++i) acc[k][i] = make_float2(0.f, 0.f);
+}
+
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
     wgrad_tma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmg,
@@ -161,6 +209,7 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
 
     uint32_t ci = 0;
     bool failed = false;
+    int cur_c0 = -1;  // channel slice the accumulators belong to
     while (it.active) {
         const uint32_t st = ci % ST;
         const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u);
@@ -176,6 +225,13 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
             for (int m = 0; m < M; ++m)
 #pragma unroll
                 for (int i = 0; i < CP; ++i) G[0][m][i] = G[1][m][i] = G[2][m][i] = __float2half2_rn(0.f);
+            // The accumulators belong to a channel slice, not to a column: they are carried from segment to
+            // segment and flushed to the workspace row only when the slice changes (in the round phase a CTA
+            // keeps its slice whenever the CTA count is a multiple of the slice count) and at the end.
+            if (it.g.c0 != cur_c0) {
+                if (cur_c0 >= 0) flush_acc<Cfg>(acc, red, row, C, cur_c0, tid);
+                cur_c0 = it.g.c0;
+            }
         }
         const bool load_g = q + 1 < it.g.he;
         const __half* xin = reinterpret_cast<const __half*>(stage_base + st * Cfg::STAGE) + th.x_off;
@@ -187,54 +243,10 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + 8 * st);  // this warp is done with the stage
-        if (q == it.g.he) {
-            // Segment finished: reduce over the consumer threads that share channels, then add the [27][CS]
-            // result to the CTA's workspace row.  Warps take turns in a fixed order (no atomics).
-            const int c0 = it.g.c0;
-#pragma unroll
-            for (int k = 0; k < 27; ++k)
-#pragma unroll
-                for (int i = 0; i < CP; ++i) {
-                    float2 v = acc[k][i];
-#pragma unroll
-                    for (int off = CPG; off < 32; off <<= 1) {
-                        v.x += __shfl_xor_sync(0xffffffffu, v.x, off);
-                        v.y += __shfl_xor_sync(0xffffffffu, v.y, off);
-                    }
-                    acc[k][i] = v;
-                }
-            for (int wi = 0; wi < NCW; ++wi) {
-                if (warp == wi && lane < CPG) {
-#pragma unroll
-                    for (int k = 0; k < 27; ++k)
-#pragma unroll
-                        for (int i = 0; i < CP; ++i) {
-                            float* dst = red + k * CS + cg * 2 * CP + 2 * i;
-                            if (wi == 0) {
-                                dst[0] = acc[k][i].x;
-                                dst[1] = acc[k][i].y;
-                            } else {
-                                dst[0] += acc[k][i].x;
-                                dst[1] += acc[k][i].y;
-                            }
-                        }
-                }
-                named_barrier_sync(1, Cfg::NT);
-            }
-            for (int e = tid; e < 27 * CS; e += Cfg::NT) {
-                const int k = e / CS, c = e % CS;
-                row[k * C + c0 + c] += red[e];
-            }
-            named_barrier_sync(1, Cfg::NT);
-#pragma unroll
-            for (int k = 0; k < 27; ++k)
-#pragma unroll
-                for (int i = 0; i < CP; ++i) acc[k][i] = make_float2(0.f, 0.f);
-        }
         it.next(s);
         ++ci;
     }
-    (void)failed;
+    if (!failed && cur_c0 >= 0) flush_acc<Cfg>(acc, red, row, C, cur_c0, tid);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -295,11 +307,13 @@ static const WgradVariant g_wgrad_variants[] = {
 static const int g_n_wgrad_variants = (int)(sizeof(g_wgrad_variants) / sizeof(g_wgrad_variants[0]));
 
 // Measured on B200 at (1,C,350,350,128): 11 consumer warps on 32-channel slices (variant 10) beat the 8-warp
-// tiles by 3-4 % for C >= 32; C <= 16 runs on 8-channel slices (11 warps help at C = 8 only).
+// tiles; 15 consumer warps (128 registers) beat those by another 4-6 % for C >= 32, best with wide-w tiles.
+// C <= 16 runs on 8-channel slices (11 warps help at C = 8 only).
 static int auto_wgrad_variant(int64_t C) {
     if (C == 8) return 11;
     if (C <= 16) return 1;
-    return 10;
+    if (C == 32) return 14;
+    return 22;
 }
 
 static int64_t ws_rows_for_device(int* rc_out) {

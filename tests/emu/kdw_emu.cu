@@ -112,9 +112,26 @@ static int emu_wgrad_cfg(const __half* x, const __half* gr, float* dw, Vol vx, V
         StepIter cons;
         cons.init(s, blk, grid);
         unsigned ci = 0;
+        int cur_c0 = -1;
+        // like the kernel: the accumulators belong to a channel slice and are flushed when it changes and at the end
+        auto flush = [&](int c0) {
+            for (int tid = 0; tid < Cfg::NT; ++tid) {
+                const WThread<Cfg> th(tid);
+                for (int k = 0; k < 27; ++k)
+                    for (int i = 0; i < CP; ++i) {
+                        row[k * vx.C + c0 + th.cg * 2 * CP + 2 * i] += ts[tid].acc[k][i].x;
+                        row[k * vx.C + c0 + th.cg * 2 * CP + 2 * i + 1] += ts[tid].acc[k][i].y;
+                        ts[tid].acc[k][i] = make_float2(0.f, 0.f);
+                    }
+            }
+        };
         while (cons.active) {
             const int q = cons.q;
             const Seg& g = cons.g;
+            if (q == g.hb - 1 && g.c0 != cur_c0) {
+                if (cur_c0 >= 0) flush(cur_c0);
+                cur_c0 = g.c0;
+            }
             emu_tma_load(xs.data(), x, vx, CS, Cfg::DT + 2, Cfg::WT + 2, g.c0, g.d0 - 1, g.w0 - 1, q, g.n);
             const bool load_g = q + 1 < g.he;
             if (load_g)
@@ -133,20 +150,10 @@ static int emu_wgrad_cfg(const __half* x, const __half* gr, float* dw, Vol vx, V
                     default: wgrad_step<Cfg, 2>(xin, gin, load_g, t.G, t.acc); break;
                 }
             }
-            if (q == g.he) {
-                for (int tid = 0; tid < Cfg::NT; ++tid) {
-                    const WThread<Cfg> th(tid);
-                    for (int k = 0; k < 27; ++k)
-                        for (int i = 0; i < CP; ++i) {
-                            row[k * vx.C + g.c0 + th.cg * 2 * CP + 2 * i] += ts[tid].acc[k][i].x;
-                            row[k * vx.C + g.c0 + th.cg * 2 * CP + 2 * i + 1] += ts[tid].acc[k][i].y;
-                            ts[tid].acc[k][i] = make_float2(0.f, 0.f);
-                        }
-                }
-            }
             cons.next(s);
             ++ci;
         }
+        if (cur_c0 >= 0) flush(cur_c0);
     }
     for (int k = 0; k < KC; ++k) {
         float a = 0.f;
