@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
     it.init(s, (int)blockIdx.x, (int)gridDim.x);
 
     __half2 wgt[27][CP];           // taps of this thread's channels
-    float2 P1[M][CP], P2[M][CP];   // carried fp32 partial sums (see fprop_step)
+    float2 P1[M][CP], P2[M][CP];   // carried fp32 partial sums (see fprop_step_f32)
     __half2 H1[M][CP], H2[M][CP];  // carried packed-half partial sums
 #pragma unroll
     for (int m = 0; m < M; ++m)
@@ -164,7 +164,15 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
         if (store && lane == 0) tma_wait_read<1>();  // the store issued two planes ago has released this tile
         __syncwarp();
         const __half* in = reinterpret_cast<const __half*>(in_base + st * Cfg::IN_STRIDE) + th.in_off;
-        fprop_step<Cfg, MODE>(in, reinterpret_cast<__half*>(ob_bytes) + th.out_off, store, wgt, P1, P2, H1, H2);
+        __half* ob = reinterpret_cast<__half*>(ob_bytes) + th.out_off;
+        if (MODE == 0) {  // the two arrays swap roles every step
+            if (ci & 1u)
+                fprop_step_f32<Cfg>(in, ob, store, wgt, P2, P1);
+            else
+                fprop_step_f32<Cfg>(in, ob, store, wgt, P1, P2);
+        } else {
+            fprop_step_f16<Cfg>(in, ob, store, wgt, H1, H2);
+        }
         if (store) fence_proxy_async_smem();  // the tile must be visible to the TMA store
         __syncwarp();
         if (lane == 0) {
@@ -254,8 +262,7 @@ static int auto_fprop_variant(int64_t C) {
     if (C == 8) return 1;
     if (C == 16) return 10;
     if (C == 32) return 11;
-    if (C == 64) return 11;
-    return 6;
+    return 12;
 }
 
 static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N, int64_t C, int64_t Hx, int64_t W,

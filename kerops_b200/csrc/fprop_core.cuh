@@ -50,19 +50,17 @@ struct FThread {
 
 // One input plane q applied to the three output planes that use it: plane q+1 gets the a=0 taps, plane q
 // the a=1 taps, plane q-1 the a=2 taps.  The thread sweeps its M+2 input columns once; an input column j
-// feeds output m = j - b through tap b.  Carried between steps, per output m:
-//   MODE 0 (KDW_ACC_F32): P1 = fp32 sum of plane q's a=0 taps, P2 = fp32 sum of plane q-1's a=0,1 taps;
-//          every tap is one mixed-precision FMA (fp16 operands, exact product, fp32 accumulator), so the
-//          only rounding to fp16 is the final one.
-//   MODE 1 (KDW_ACC_F16): the same sums as packed-half chains (H1, H2), two channels per HFMA2.
-// When `store` is set the finished plane q-1 is written to the warp's output tile `ob`.
-template <class Cfg, int MODE>
-KDW_HD void fprop_step(const __half* __restrict__ in, __half* __restrict__ ob, bool store,
-                       const __half2 (&wgt)[27][Cfg::CP], float2 (&P1)[Cfg::M][Cfg::CP], float2 (&P2)[Cfg::M][Cfg::CP],
-                       __half2 (&H1)[Cfg::M][Cfg::CP], __half2 (&H2)[Cfg::M][Cfg::CP]) {
+// feeds output m = j - b through tap b.  Two step functions follow, one per accumulate type.
+//
+// KDW_ACC_F16: the sums are packed-half chains, two channels per HFMA2.  Carried between steps, per output m:
+// H1 = plane q's a=0 sum, H2 = plane q-1's a=0,1 sum.  When `store` is set the finished plane q-1 is written to
+// the warp's output tile `ob`.
+template <class Cfg>
+KDW_HD void fprop_step_f16(const __half* __restrict__ in, __half* __restrict__ ob, bool store,
+                           const __half2 (&wgt)[27][Cfg::CP], __half2 (&H1)[Cfg::M][Cfg::CP],
+                           __half2 (&H2)[Cfg::M][Cfg::CP]) {
     constexpr int CS = Cfg::CS, DT = Cfg::DT, M = Cfg::M, CP = Cfg::CP, DPW = Cfg::DPW;
-    float2 F[3][3][CP];   // MODE 0: running fp32 sums of [a][output slot m % 3]
-    __half2 S[3][3][CP];  // MODE 1: running packed-half chains
+    __half2 S[3][3][CP];  // running chains of [a][output slot m % 3]
 #pragma unroll
     for (int j = 0; j < M + 2; ++j) {
         __half2 xv[3][CP];
@@ -79,28 +77,17 @@ KDW_HD void fprop_step(const __half* __restrict__ in, __half* __restrict__ ob, b
                     const __half2 w0 = wgt[(a * 3 + b) * 3 + 0][i];
                     const __half2 w1 = wgt[(a * 3 + b) * 3 + 1][i];
                     const __half2 w2 = wgt[(a * 3 + b) * 3 + 2][i];
-                    if (MODE == 0) {
-                        float2 f;
-                        if (b == 0)
-                            f = (a == 0) ? make_float2(0.f, 0.f) : (a == 1 ? P1[m][i] : P2[m][i]);
+                    __half2 T;
+                    if (b == 0) {
+                        if (a == 0)
+                            T = h2_mul(w0, xv[0][i]);
                         else
-                            f = F[a][m % 3][i];
-                        f = fma_h2_f2(w0, xv[0][i], f);
-                        f = fma_h2_f2(w1, xv[1][i], f);
-                        F[a][m % 3][i] = fma_h2_f2(w2, xv[2][i], f);
+                            T = h2_fma(w0, xv[0][i], a == 1 ? H1[m][i] : H2[m][i]);
                     } else {
-                        __half2 T;
-                        if (b == 0) {
-                            if (a == 0)
-                                T = h2_mul(w0, xv[0][i]);
-                            else
-                                T = h2_fma(w0, xv[0][i], a == 1 ? H1[m][i] : H2[m][i]);
-                        } else {
-                            T = h2_fma(w0, xv[0][i], S[a][m % 3][i]);
-                        }
-                        T = h2_fma(w1, xv[1][i], T);
-                        S[a][m % 3][i] = h2_fma(w2, xv[2][i], T);
+                        T = h2_fma(w0, xv[0][i], S[a][m % 3][i]);
                     }
+                    T = h2_fma(w1, xv[1][i], T);
+                    S[a][m % 3][i] = h2_fma(w2, xv[2][i], T);
                 }
             }
         }
@@ -109,18 +96,82 @@ KDW_HD void fprop_step(const __half* __restrict__ in, __half* __restrict__ ob, b
             if (store) {  // plane q-1 is finished
                 __half2 o[CP];
 #pragma unroll
-                for (int i = 0; i < CP; ++i) o[i] = (MODE == 0) ? __float22half2_rn(F[2][m % 3][i]) : S[2][m % 3][i];
+                for (int i = 0; i < CP; ++i) o[i] = S[2][m % 3][i];
                 sts_h2<CP>(ob + (m * DPW) * CS, o);
             }
 #pragma unroll
             for (int i = 0; i < CP; ++i) {
-                if (MODE == 0) {
-                    P2[m][i] = F[1][m % 3][i];
-                    P1[m][i] = F[0][m % 3][i];
-                } else {
-                    H2[m][i] = S[1][m % 3][i];
-                    H1[m][i] = S[0][m % 3][i];
-                }
+                H2[m][i] = S[1][m % 3][i];
+                H1[m][i] = S[0][m % 3][i];
+            }
+        }
+    }
+}
+
+// KDW_ACC_F32: every tap is one mixed-precision FMA (fp16 operands, exact product, fp32 accumulator), so the
+// only rounding to fp16 is the final one.  The carried fp32 sums are updated IN PLACE: A holds, per output m, the
+// sum of plane q's a=0 taps on entry and of plane q's a=0,1 taps on exit; B holds plane q-1's a=0,1 sums on
+// entry, is completed with the a=2 taps (and stored when `store` is set), and then receives plane q+1's a=0 sum.
+// So the two arrays swap roles from one step to the next - the caller passes (A, B), then (B, A), ... - and no
+// register is ever copied.
+template <class Cfg>
+KDW_HD void fprop_step_f32(const __half* __restrict__ in, __half* __restrict__ ob, bool store,
+                               const __half2 (&wgt)[27][Cfg::CP], float2 (&A)[Cfg::M][Cfg::CP],
+                               float2 (&B)[Cfg::M][Cfg::CP]) {
+    constexpr int CS = Cfg::CS, DT = Cfg::DT, M = Cfg::M, CP = Cfg::CP, DPW = Cfg::DPW;
+    float2 T[3][CP];  // running a=0 sums of the (at most three) outputs in flight
+#pragma unroll
+    for (int j = 0; j < M + 2; ++j) {
+        __half2 xv[3][CP];
+#pragma unroll
+        for (int t = 0; t < 3; ++t) lds_h2<CP>(xv[t], in + (j * (DT + 2) + t) * CS);
+        // a = 2: completes plane q-1 in B
+#pragma unroll
+        for (int b = 0; b < 3; ++b) {
+            const int m = j - b;
+            if (m < 0 || m >= M) continue;
+#pragma unroll
+            for (int i = 0; i < CP; ++i) {
+                float2 f = B[m][i];
+                f = fma_h2_f2(wgt[(6 + b) * 3 + 0][i], xv[0][i], f);
+                f = fma_h2_f2(wgt[(6 + b) * 3 + 1][i], xv[1][i], f);
+                B[m][i] = fma_h2_f2(wgt[(6 + b) * 3 + 2][i], xv[2][i], f);
+            }
+        }
+        if (j >= 2 && store) {
+            __half2 o[CP];
+#pragma unroll
+            for (int i = 0; i < CP; ++i) o[i] = __float22half2_rn(B[j - 2][i]);
+            sts_h2<CP>(ob + ((j - 2) * DPW) * CS, o);
+        }
+        // a = 1: plane q's sum grows in A
+#pragma unroll
+        for (int b = 0; b < 3; ++b) {
+            const int m = j - b;
+            if (m < 0 || m >= M) continue;
+#pragma unroll
+            for (int i = 0; i < CP; ++i) {
+                float2 f = A[m][i];
+                f = fma_h2_f2(wgt[(3 + b) * 3 + 0][i], xv[0][i], f);
+                f = fma_h2_f2(wgt[(3 + b) * 3 + 1][i], xv[1][i], f);
+                A[m][i] = fma_h2_f2(wgt[(3 + b) * 3 + 2][i], xv[2][i], f);
+            }
+        }
+        // a = 0: plane q+1 starts in T; its last tap lands in B[m], which the a = 2 pass has just released
+#pragma unroll
+        for (int b = 0; b < 3; ++b) {
+            const int m = j - b;
+            if (m < 0 || m >= M) continue;
+#pragma unroll
+            for (int i = 0; i < CP; ++i) {
+                float2 f = (b == 0) ? make_float2(0.f, 0.f) : T[m % 3][i];
+                f = fma_h2_f2(wgt[b * 3 + 0][i], xv[0][i], f);
+                f = fma_h2_f2(wgt[b * 3 + 1][i], xv[1][i], f);
+                f = fma_h2_f2(wgt[b * 3 + 2][i], xv[2][i], f);
+                if (b == 2)
+                    B[m][i] = f;
+                else
+                    T[m % 3][i] = f;
             }
         }
     }

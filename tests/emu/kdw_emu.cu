@@ -1,7 +1,7 @@
 // CPU emulation of the TMA kernels, used only by the CPU test-suite.
 //
 // It runs the SAME host scheduler (make_sched), segment decoding (decode_segment / StepIter), thread
-// mapping (FThread / WThread) and per-thread step functions (fprop_step / wgrad_step) as the CUDA
+// mapping (FThread / WThread) and per-thread step functions (fprop_step_f32 / fprop_step_f16 / wgrad_step) as the CUDA
 // kernels, one emulated thread after the other, and replaces only the hardware plumbing: a tiled TMA
 // load becomes a box copy with zero fill, a TMA store a clipped box copy, the block reduction of the
 // weight-gradient kernel a plain loop.  It lets the index arithmetic of every kernel variant be
@@ -62,6 +62,7 @@ static int emu_fprop_cfg(const __half* x, const __half* w, __half* y, Vol vx, Vo
         memset(ts.data(), 0, sizeof(TState) * ts.size());
         StepIter cons;
         cons.init(s, blk, grid);
+        unsigned ci = 0;
         while (cons.active) {
             const int q = cons.q;
             const Seg& g = cons.g;
@@ -77,7 +78,14 @@ static int emu_fprop_cfg(const __half* x, const __half* w, __half* y, Vol vx, Vo
                 }
                 const __half* in = stage.data() + th.in_off;
                 __half* ob = out.data() + (size_t)(tid / 32) * (Cfg::OUTW_BYTES / 2) + th.out_off;
-                fprop_step<Cfg, MODE>(in, ob, store, t.wgt, t.P1, t.P2, t.H1, t.H2);
+                if (MODE == 0) {  // as in the kernel: in-place sums, roles swap every step
+                    if (ci & 1u)
+                        fprop_step_f32<Cfg>(in, ob, store, t.wgt, t.P2, t.P1);
+                    else
+                        fprop_step_f32<Cfg>(in, ob, store, t.wgt, t.P1, t.P2);
+                } else {
+                    fprop_step_f16<Cfg>(in, ob, store, t.wgt, t.H1, t.H2);
+                }
             }
             if (store) {
                 for (int wp = 0; wp < Cfg::NCW; ++wp) {  // every warp stores its own box
@@ -87,6 +95,7 @@ static int emu_fprop_cfg(const __half* x, const __half* w, __half* y, Vol vx, Vo
                 }
             }
             cons.next(s);
+            ++ci;
         }
     }
     return grid;
