@@ -44,12 +44,12 @@ FALLBACK_HBM_GBS = 6650.0
 # 350/100 planes (traffic grows in proportion to the planes a launch processes).  Bytes per (1,C,350,350,128)
 # launch; None where no capture has been taken.
 NCU_TRAFFIC = {
-    ('fprop', 8): int((0.078729 + 0.025757) * 3.5e9),
-    ('wgrad', 8): int((0.150921 + 0.003749) * 3.5e9),
-    ('fprop', 32): int((0.290699 + 0.250010) * 3.5e9),
-    ('wgrad', 32): int((0.618345 + 0.005101) * 3.5e9),
-    ('fprop', 128): int((1.472090 + 1.127703) * 3.5e9),
-    ('wgrad', 128): int((2.365841 + 0.009408) * 3.5e9),
+    ('fprop', 8): int((0.078780 + 0.026234) * 3.5e9),
+    ('wgrad', 8): int((0.151026 + 0.004179) * 3.5e9),
+    ('fprop', 32): int((0.290684 + 0.249140) * 3.5e9),
+    ('wgrad', 32): int((0.581614 + 0.004245) * 3.5e9),
+    ('fprop', 128): int((1.345314 + 1.114778) * 3.5e9),
+    ('wgrad', 128): int((2.337645 + 0.006905) * 3.5e9),
 }
 
 
