@@ -308,9 +308,9 @@ static const int g_n_wgrad_variants = (int)(sizeof(g_wgrad_variants) / sizeof(g_
 
 // Measured on B200 at (1,C,350,350,128): 11 consumer warps on 32-channel slices (variant 10) beat the 8-warp
 // tiles; 15 consumer warps (128 registers) beat those by another 4-6 % for C >= 32, best with wide-w tiles.
-// C <= 16 runs on 8-channel slices (11 warps help at C = 8 only).
+// C <= 16 runs on 8-channel slices (more warps help at C = 8 only: 12 on a 32 x 24 tile).
 static int auto_wgrad_variant(int64_t C) {
-    if (C == 8) return 11;
+    if (C == 8) return 24;
     if (C <= 16) return 1;
     if (C == 32) return 14;
     return 22;
