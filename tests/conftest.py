@@ -67,4 +67,6 @@ def kdw_emu(kdw_lib):
     emu.emu_fprop.restype = ci
     emu.emu_wgrad.argtypes = [ci, vp, vp, vp] + [i64] * 6 + [ci] * 4
     emu.emu_wgrad.restype = ci
+    emu.emu_schedule.argtypes = [i64] * 4 + [ci] * 6 + [vp, ctypes.POINTER(i64), ctypes.POINTER(i64)]
+    emu.emu_schedule.restype = ci
     return emu

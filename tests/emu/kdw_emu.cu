@@ -211,4 +211,35 @@ int emu_wgrad(int variant, const void* x, const void* g, float* dw, int64_t N, i
     return -1;
 }
 
+// Walks the schedule of every CTA exactly as the kernels do (make_sched + StepIter) and counts, per output unit
+// (sample, channel slice, d tile, w tile, plane), how many segments own it; also returns the smallest and largest
+// number of steps a CTA takes.  counts has N * nCS * nDT * nWT * (h_end - h_begin) entries, zero-initialised.
+int emu_schedule(int64_t N, int64_t C, int64_t W, int64_t D, int h_begin, int h_end, int WT, int DT, int CS,
+                 int grid_target, int* counts, int64_t* min_steps, int64_t* max_steps) {
+    Sched s;
+    const int grid = make_sched(&s, N, C, W, D, h_begin, h_end, WT, DT, CS, grid_target);
+    const int Hr = h_end - h_begin;
+    int64_t lo = -1, hi = -1;
+    for (int blk = 0; blk < grid; ++blk) {
+        StepIter it;
+        it.init(s, blk, grid);
+        int64_t steps = 0;
+        while (it.active) {
+            const Seg& g = it.g;
+            if (it.q == g.hb - 1) {  // a new segment: owns planes hb .. he-1 of its column
+                if (g.hb < h_begin || g.he > h_end || g.hb >= g.he) return -2;
+                const int64_t col = (((int64_t)g.n * s.nCS + g.c0 / CS) * s.nDT + g.d0 / DT) * s.nWT + g.w0 / WT;
+                for (int p = g.hb; p < g.he; ++p) ++counts[col * Hr + (p - h_begin)];
+            }
+            ++steps;
+            it.next(s);
+        }
+        if (lo < 0 || steps < lo) lo = steps;
+        if (steps > hi) hi = steps;
+    }
+    *min_steps = lo;
+    *max_steps = hi;
+    return grid;
+}
+
 }  // extern "C"

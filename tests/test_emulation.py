@@ -97,3 +97,45 @@ def test_emulated_plane_ranges(kdw_lib, kdw_emu):
         ref = o.wgrad_exact(x, gz)
         assert np.abs(dw - ref).max() <= 2e-3 * (np.abs(ref).max() + 1.0)
     # shards add up to the full gradient
+
+
+# ---------------------------------------------------------------------------------------------------------
+# The work decomposition shared by host and device code (make_sched, decode_column, decode_remainder,
+# StepIter): every (sample, channel slice, tile, plane) unit is owned by exactly one segment, for any shape,
+# tile and grid size, and the CTAs' step counts are balanced.
+# ---------------------------------------------------------------------------------------------------------
+def _schedule(kdw_emu, N, C, W, D, h_begin, h_end, WT, DT, CS, grid_target):
+    import ctypes
+
+    nWT, nDT, nCS = -(-W // WT), -(-D // DT), C // CS
+    counts = np.zeros(N * nCS * nDT * nWT * (h_end - h_begin), dtype=np.int32)
+    lo, hi = ctypes.c_int64(), ctypes.c_int64()
+    grid = kdw_emu.emu_schedule(N, C, W, D, h_begin, h_end, WT, DT, CS, grid_target,
+                                counts.ctypes.data_as(ctypes.c_void_p), ctypes.byref(lo), ctypes.byref(hi))
+    return grid, counts, lo.value, hi.value
+
+
+def test_schedule_covers_every_unit_once_benchmark_shapes(kdw_emu):
+    for C, CS, DT, WT in [(8, 8, 64, 8), (32, 32, 32, 8), (128, 64, 8, 8), (128, 64, 3, 40), (32, 32, 10, 24)]:
+        for grid_target in (148, 296):
+            grid, counts, lo, hi = _schedule(kdw_emu, 1, C, 350, 128, 0, 350, WT, DT, CS, grid_target)
+            assert grid == grid_target
+            assert counts.min() == 1 and counts.max() == 1
+            # a CTA's steps: its planes plus one extra input plane per segment; balanced to a few per cent
+            assert hi - lo <= max(8, 0.03 * hi), (C, CS, DT, WT, grid_target, lo, hi)
+
+
+def test_schedule_covers_every_unit_once_random_shapes(kdw_emu):
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=150, deadline=None)
+    @given(N=st.integers(1, 3), nCS=st.integers(1, 4), W=st.integers(1, 70), D=st.integers(1, 70),
+           h0=st.integers(0, 5), Hr=st.integers(1, 40), WT=st.sampled_from([4, 8, 16, 24, 40]),
+           DT=st.sampled_from([3, 5, 8, 16, 22, 32, 64]), grid_target=st.integers(1, 300))
+    def check(N, nCS, W, D, h0, Hr, WT, DT, grid_target):
+        CS = 8
+        grid, counts, lo, hi = _schedule(kdw_emu, N, nCS * CS, W, D, h0, h0 + Hr, WT, DT, CS, grid_target)
+        assert 1 <= grid <= grid_target
+        assert counts.min() == 1 and counts.max() == 1
+
+    check()
