@@ -447,6 +447,17 @@ def measure_e2e(args, channels, dev, world, rank):
         return None
     Cmax = max(channels)
     H, W, D = SHAPE
+    # every rank pins three buffers of the largest volume; skip (and say so) rather than exhaust the host
+    need = 3 * VOX * Cmax * 2 * world
+    try:
+        import psutil
+
+        avail = psutil.virtual_memory().available
+    except Exception:
+        avail = None
+    if avail is not None and need * 1.3 > avail:
+        return {'value': None, 'unit': 'GB/s', 'skipped': f'pinned host buffers need {need >> 30} GiB over all ranks, '
+                                                            f'{avail >> 30} GiB of host memory available'}
     # one pinned pool, sliced per C (contents: N(0,1) generated on the device once)
     pool = [torch.empty(VOX * Cmax, dtype=torch.float16, pin_memory=True) for _ in range(3)]
     g = torch.Generator(device=dev).manual_seed(7 + rank)
