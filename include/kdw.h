@@ -64,7 +64,7 @@ int kdw_device_status(int* status);
  *   acc_type  KDW_ACC_F32: exact fp16 x fp16 products accumulated in fp32 (mixed-precision FMA), rounded once to
  *             fp16 - at least as accurate as the reference's 'float32' mode (fp16 products, fp16 sum of three,
  *             fp32 sum of nine; kerops/kernels/dw_conv.py:49-52);  KDW_ACC_F16: all 27 taps in fp16 FMA chains
- *   tune      0 = built-in choice for this C; >0 = explicit kernel variant (see kdw_fprop_variants());
+ *   tune      0 = built-in choice for this C, W and D; >0 = explicit kernel variant (see kdw_fprop_variants());
  *             takes the place of the num_warps / D_block keywords (dwconv.py:10-17)
  * C must be a power of two.  C >= 8 uses the TMA kernel (x, y 16-byte aligned, strides multiples of 8);
  * smaller C uses a plain kernel.
@@ -88,6 +88,10 @@ int kdw_fprop_f16_range(const void* x, const void* weight, void* y, int64_t N, i
  * channel-slice width of a variant (usable when C is a multiple of it).  No reference counterpart. */
 int kdw_fprop_variants(void);
 int kdw_fprop_variant_channels(int id);
+/* The variant tune = 0 selects for a (C, W, D): the fastest measured tile for this C, corrected for the padding
+ * its tile computes when it does not divide W or D.  0 if C is not a power of two >= 8 (plain kernel) or a size is
+ * not positive.  Takes the place of the reference's per-C tables (dwconv.py:10-17).  */
+int kdw_fprop_auto_variant(int64_t C, int64_t W, int64_t D);
 
 /*
  * Bytes of device workspace kdw_wgrad_f16 needs on the current device (upper bound for any tune).  Takes
@@ -143,6 +147,8 @@ int kdw_wgrad_f16_static(const void* x, const void* grad, float* dw_f32, void* d
 
 int kdw_wgrad_variants(void);
 int kdw_wgrad_variant_channels(int id);
+/* Same as kdw_fprop_auto_variant, for the weight gradient (dwconv_wgrad.py:10-22). */
+int kdw_wgrad_auto_variant(int64_t C, int64_t W, int64_t D);
 
 /*
  * Multi-GPU sum of weight gradients by peer stores (no reference counterpart: the reference is single-GPU).

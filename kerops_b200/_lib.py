@@ -25,6 +25,7 @@ SIGNATURES = {
     ),
     'kdw_fprop_variants': (_int, []),
     'kdw_fprop_variant_channels': (_int, [_int]),
+    'kdw_fprop_auto_variant': (_int, [_i64, _i64, _i64]),
     'kdw_wgrad_workspace_bytes': (_i64, [_i64] * 5),
     'kdw_wgrad_f16': (_int, [_ptr, _ptr, _ptr, _i64, _ptr, _ptr] + [_i64] * 5 + [_i64] * 6 + [_int, _ptr]),
     'kdw_wgrad_f16_range': (
@@ -34,6 +35,7 @@ SIGNATURES = {
     'kdw_wgrad_f16_static': (_int, [_ptr, _ptr, _ptr, _ptr] + [_i64] * 5 + [_i64] * 6 + [_ptr]),
     'kdw_wgrad_variants': (_int, []),
     'kdw_wgrad_variant_channels': (_int, [_int]),
+    'kdw_wgrad_auto_variant': (_int, [_i64, _i64, _i64]),
     'kdw_allreduce_buffer_bytes': (_i64, [_i64, _int]),
     'kdw_allreduce_push_f32': (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _int, _int, ctypes.c_uint32, _i64, _ptr]),
 }

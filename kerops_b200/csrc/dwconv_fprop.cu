@@ -236,11 +236,11 @@ static int launch_fprop_tma(const FpropArgs& a) {
 
 typedef int (*FpropLaunch)(const FpropArgs&);
 struct FpropVariant {
-    int cs;
+    int cs, dt, wt;
     FpropLaunch mode[2];  // indexed by KDW_ACC_*
 };
 #define KDW_VARIANT(ID, CS, DT, WT, M, CP, ST, MINB)                            \
-    {CS,                                                                        \
+    {CS, DT, WT,                                                                \
      {&launch_fprop_tma<FCfg<CS, DT, WT, M, CP, ST, MINB>, 0>,                  \
       &launch_fprop_tma<FCfg<CS, DT, WT, M, CP, ST, MINB>, 1>}},
 // index = id - 1
@@ -257,13 +257,41 @@ int launch_fprop_mma_variant(int which, const void* x, const void* w, void* y, i
                              int64_t ysH, int64_t ysW, int h_begin, int h_end, int y_h0, cudaStream_t stream);
 static int n_fprop_variants() { return g_n_table_variants + fprop_mma_variants(); }
 
-static int auto_fprop_variant(int64_t C) {
-    // fastest KDW_ACC_F32 variant measured at (1, C, 350, 350, 128) on B200 inside the benchmark's sweep (the
-    // ranking of the 32- and 64-channel tiles moves by a few per cent with the placement of x and y in memory)
-    if (C == 8) return 1;
-    if (C == 16) return 10;
-    if (C <= 64) return 11;
-    return 8;
+// Built-in choice.  Per channel count a short list of candidates with their time relative to the best one, measured
+// at (1, C, 350, 350, 128) on B200 inside the benchmark's sweep (the ranking of the 32- and 64-channel tiles moves
+// by a few per cent with the placement of x and y in memory).  A tile that does not divide W or D computes padding:
+// the candidate's time is scaled by the padded / real area and the cheapest one wins, so e.g. D = 40 does not run
+// on a 64-deep tile.
+struct FpropCand {
+    int id;
+    float rel;
+};
+static const FpropCand kFpropCand8[] = {{1, 1.00f}, {2, 1.12f}};
+static const FpropCand kFpropCand16[] = {{10, 1.00f}, {4, 1.03f}, {1, 1.75f}};
+static const FpropCand kFpropCand32[] = {{11, 1.00f}, {6, 1.02f}, {4, 1.02f}};
+static const FpropCand kFpropCand64[] = {{11, 1.00f}, {8, 1.02f}, {6, 1.03f}};
+static const FpropCand kFpropCand128[] = {{8, 1.00f}, {11, 1.01f}, {6, 1.03f}};
+
+static int auto_fprop_variant(int64_t C, int64_t W, int64_t D) {
+    const FpropCand* cand;
+    int n;
+    if (C == 8) { cand = kFpropCand8; n = 2; }
+    else if (C == 16) { cand = kFpropCand16; n = 3; }
+    else if (C == 32) { cand = kFpropCand32; n = 3; }
+    else if (C == 64) { cand = kFpropCand64; n = 3; }
+    else { cand = kFpropCand128; n = 3; }
+    int best = cand[0].id;
+    double best_cost = 0.0;
+    for (int i = 0; i < n; ++i) {
+        const FpropVariant& v = g_fprop_variants[cand[i].id - 1];
+        const double padded = (double)((W + v.wt - 1) / v.wt * v.wt) * (double)((D + v.dt - 1) / v.dt * v.dt);
+        const double cost = cand[i].rel * padded / ((double)W * (double)D);
+        if (i == 0 || cost < best_cost) {
+            best = cand[i].id;
+            best_cost = cost;
+        }
+    }
+    return best;
 }
 
 static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N, int64_t C, int64_t Hx, int64_t W,
@@ -313,7 +341,7 @@ static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N,
         KDW_CUDA(cudaGetLastError());
         return 0;
     }
-    const int id = tune ? tune : auto_fprop_variant(C);
+    const int id = tune ? tune : auto_fprop_variant(C, W, D);
     if (id > g_n_table_variants) {
         if (acc_type != KDW_ACC_F32) {
             set_error("fprop: variant %d (tensor cores) implements KDW_ACC_F32 only", id);
@@ -336,6 +364,11 @@ static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N,
 extern "C" {
 
 int kdw_fprop_variants(void) { return kdw::n_fprop_variants(); }
+
+int kdw_fprop_auto_variant(int64_t C, int64_t W, int64_t D) {
+    if (C < 8 || (C & (C - 1)) != 0 || W <= 0 || D <= 0) return 0;
+    return kdw::auto_fprop_variant(C, W, D);
+}
 
 int kdw_fprop_variant_channels(int id) {
     if (id < 1 || id > kdw::n_fprop_variants()) return KDW_ERR_TUNE;

@@ -295,10 +295,11 @@ static int launch_wgrad_tma(const WgradArgs& a, int* rows_used) {
 
 typedef int (*WgradLaunch)(const WgradArgs&, int*);
 struct WgradVariant {
-    int cs;
+    int cs, dt, wt;
     WgradLaunch f;
 };
-#define KDW_VARIANT(ID, CS, DT, WT, M, CP, ST, MINB) {CS, &launch_wgrad_tma<WCfg<CS, DT, WT, M, CP, ST, MINB>>},
+#define KDW_VARIANT(ID, CS, DT, WT, M, CP, ST, MINB) \
+    {CS, DT, WT, &launch_wgrad_tma<WCfg<CS, DT, WT, M, CP, ST, MINB>>},
 // index = id - 1
 static const WgradVariant g_wgrad_variants[] = {
 #include "wgrad_variants.inc"
@@ -306,14 +307,38 @@ static const WgradVariant g_wgrad_variants[] = {
 #undef KDW_VARIANT
 static const int g_n_wgrad_variants = (int)(sizeof(g_wgrad_variants) / sizeof(g_wgrad_variants[0]));
 
-// Measured on B200 at (1,C,350,350,128): 11 consumer warps on 32-channel slices (variant 10) beat the 8-warp
-// tiles; 15 consumer warps (128 registers) beat those by another 4-6 % for C >= 32, best with wide-w tiles.
-// C <= 16 runs on 8-channel slices (more warps help at C = 8 only: 12 on a 32 x 24 tile).
-static int auto_wgrad_variant(int64_t C) {
-    if (C == 8) return 24;
-    if (C <= 16) return 1;
-    if (C == 32) return 14;
-    return 22;
+// Built-in choice: per channel count a short list of candidates with their time relative to the best one, measured
+// on B200 at (1,C,350,350,128) (15 consumer warps on wide-w tiles win for C >= 32; C <= 16 runs on 8-channel
+// slices); each candidate's time is scaled by the padded / real area of its tiles on this W x D and the cheapest
+// one wins.
+struct WgradCand {
+    int id;
+    float rel;
+};
+static const WgradCand kWgradCand8[] = {{24, 1.00f}, {11, 1.06f}, {1, 1.09f}, {2, 1.25f}};
+static const WgradCand kWgradCand16[] = {{1, 1.00f}, {2, 1.15f}};
+static const WgradCand kWgradCand32[] = {{14, 1.00f}, {10, 1.04f}, {3, 1.10f}, {4, 1.25f}};
+static const WgradCand kWgradCand64[] = {{22, 1.00f}, {16, 1.01f}, {8, 1.03f}, {14, 1.03f}, {5, 1.12f}};
+
+static int auto_wgrad_variant(int64_t C, int64_t W, int64_t D) {
+    const WgradCand* cand;
+    int n;
+    if (C == 8) { cand = kWgradCand8; n = 4; }
+    else if (C == 16) { cand = kWgradCand16; n = 2; }
+    else if (C == 32) { cand = kWgradCand32; n = 4; }
+    else { cand = kWgradCand64; n = 5; }
+    int best = cand[0].id;
+    double best_cost = 0.0;
+    for (int i = 0; i < n; ++i) {
+        const WgradVariant& v = g_wgrad_variants[cand[i].id - 1];
+        const double padded = (double)((W + v.wt - 1) / v.wt * v.wt) * (double)((D + v.dt - 1) / v.dt * v.dt);
+        const double cost = cand[i].rel * padded / ((double)W * (double)D);
+        if (i == 0 || cost < best_cost) {
+            best = cand[i].id;
+            best_cost = cost;
+        }
+    }
+    return best;
 }
 
 static int64_t ws_rows_for_device(int* rc_out) {
@@ -386,7 +411,7 @@ static int wgrad_dispatch(const void* x, const void* grad, void* workspace, int6
         KDW_CUDA(cudaGetLastError());
         rows = (int)blocks;
     } else {
-        const int id = tune ? tune : auto_wgrad_variant(C);
+        const int id = tune ? tune : auto_wgrad_variant(C, W, D);
         const WgradVariant& v = g_wgrad_variants[id - 1];
         if (C % v.cs != 0) {
             set_error("wgrad: variant %d works on %d-channel slices, C=%lld is not a multiple", id, v.cs,
@@ -469,7 +494,7 @@ static int wgrad_static_dispatch(const void* x, const void* grad, float* dw_f32,
         KDW_CUDA(cudaGetLastError());
         rows = (int)blocks;
     } else {
-        const WgradVariant& v = g_wgrad_variants[auto_wgrad_variant(C) - 1];
+        const WgradVariant& v = g_wgrad_variants[auto_wgrad_variant(C, W, D) - 1];
         WgradArgs a{x, grad, ws, kStaticRows, N, C, H, W, D, xsN, xsH, xsW, H, gsN, gsH, gsW, 0, (int)H, 0, st};
         rc = v.f(a, &rows);  // the launcher never uses more CTAs (= rows) than a.ws_rows
         if (rc) return rc;
@@ -484,6 +509,11 @@ static int wgrad_static_dispatch(const void* x, const void* grad, float* dw_f32,
 extern "C" {
 
 int kdw_wgrad_variants(void) { return kdw::g_n_wgrad_variants; }
+
+int kdw_wgrad_auto_variant(int64_t C, int64_t W, int64_t D) {
+    if (C < 8 || (C & (C - 1)) != 0 || W <= 0 || D <= 0) return 0;
+    return kdw::auto_wgrad_variant(C, W, D);
+}
 
 int kdw_wgrad_variant_channels(int id) {
     if (id < 1 || id > kdw::g_n_wgrad_variants) return KDW_ERR_TUNE;

@@ -54,3 +54,19 @@ def test_argument_errors_without_gpu(kdw_lib):
     rc = kdw_lib.kdw_wgrad_f16(16, 16, 16, 1 << 20, None, None, 1, 8, 4, 4, 4, 512, 128, 32, 512, 128, 32, 0, None)
     assert rc == -1
     assert kdw_lib.kdw_wgrad_workspace_bytes(1, 0, 4, 4, 4) < 0
+
+
+def test_auto_variant_follows_the_shape(kdw_lib):
+    """tune = 0: the benchmark shape gets the tiles measured fastest there; a depth that a deep tile would pad
+    heavily gets a shallower tile; every choice is a variant whose channel slice divides C."""
+    lib = kdw_lib
+    assert [lib.kdw_fprop_auto_variant(C, 350, 128) for C in (8, 16, 32, 64, 128)] == [1, 10, 11, 11, 8]
+    assert [lib.kdw_wgrad_auto_variant(C, 350, 128) for C in (8, 16, 32, 64, 128)] == [24, 1, 14, 22, 22]
+    assert lib.kdw_fprop_auto_variant(32, 350, 40) != 11   # 32-deep tiles would compute 64 of 40 planes
+    assert lib.kdw_wgrad_auto_variant(128, 48, 128) != 22  # 40-wide tiles would compute 80 of 48 columns
+    for C in (8, 16, 32, 64, 128, 256):
+        for W, D in ((350, 128), (16, 8), (40, 40), (97, 61), (1, 1)):
+            f, w = lib.kdw_fprop_auto_variant(C, W, D), lib.kdw_wgrad_auto_variant(C, W, D)
+            assert 1 <= f <= lib.kdw_fprop_variants() and C % lib.kdw_fprop_variant_channels(f) == 0
+            assert 1 <= w <= lib.kdw_wgrad_variants() and C % lib.kdw_wgrad_variant_channels(w) == 0
+    assert lib.kdw_fprop_auto_variant(4, 16, 16) == 0 and lib.kdw_wgrad_auto_variant(24, 16, 16) == 0
