@@ -411,7 +411,7 @@ def run_ours(args):
             'sample': f'(1,8,350,350,128) only: torch CPU conv3d(groups=8) forward + weight gradient in {dtype}, '
                       f'median of {n_cpu} steps after 1 warm-up ({spent:.1f} s of CPU work)',
         }
-    triton_ref = measure_triton_reference(channels, data, dev) if (args.compare_triton and rank == 0) else None
+    triton_ref = measure_triton_reference(channels, data, dev) if (args.compare_triton and rank == 0 and world == 1) else None
 
     if rank == 0:
         line = {
@@ -734,8 +734,10 @@ def main():
                     help="'step': one DWConvStepHost call per volume (x is copied once); 'split': DWConvHost and "
                          'DWConvWGRADHost as two calls')
     ap.add_argument('--no-cpu-baseline', action='store_true')
-    ap.add_argument('--compare-triton', action='store_true',
-                    help='also time the reference Triton kernels from baseline/_ref on this GPU')
+    ap.add_argument('--compare-triton', dest='compare_triton', action='store_true', default=True,
+                    help='also time the reference Triton kernels from baseline/_ref on this GPU (default at 1 GPU; '
+                         'reported as reference_triton_on_this_gpu, or why it is unavailable)')
+    ap.add_argument('--no-compare-triton', dest='compare_triton', action='store_false')
     args = ap.parse_args()
     args.channels = [int(c) for c in args.channels.split(',')]
     set_planes(args.planes)
