@@ -171,6 +171,25 @@ int64_t kdw_allreduce_buffer_bytes(int64_t n, int world);
 int kdw_allreduce_push_f32(const float* local, float* out_f32, void* out_f16, void* const* buffers, int64_t n, int rank,
                            int world, uint32_t seq, int64_t timeout_ns, void* stream);
 
+/*
+ * Forward pass with a fused residual add and per-channel statistics:
+ *   out = fp16(DWConv(x, weight)) + residual   (the add in fp16, like an elementwise add of two fp16 tensors)
+ *   mean[c] = sum(out[..., c]) / (N*H*W*D),  sqmean[c] = sum(out[..., c]^2) / (N*H*W*D)   (fp32 sums of the fp16 values)
+ * i.e. what the reference computes with two operators, AddStats(DWConv(x, weight), residual)
+ * (kerops/ops/addition.py:11-49 on top of kerops/ops/conv/dwconv.py:25-63), without writing and re-reading the
+ * convolution's output.  KDW_ACC_F32 arithmetic.  C a power of two >= 8; x, residual, y are (N, C, H, W, D) fp16
+ * volumes with the layout rules of kdw_fprop_f16; mean, sqmean fp32 [C]; workspace of
+ * kdw_fprop_addstats_workspace_bytes() bytes (no initialisation needed).  The sums are reproducible (no atomics).
+ *   tune  0 = built-in choice; 1..kdw_fprop_addstats_variants() = explicit tile
+ */
+int64_t kdw_fprop_addstats_workspace_bytes(int64_t N, int64_t C, int64_t H, int64_t W, int64_t D);
+int kdw_fprop_addstats_variants(void);
+int kdw_fprop_addstats_f16(const void* x, const void* weight, const void* residual, void* y, void* workspace,
+                           int64_t workspace_bytes, float* mean, float* sqmean, int64_t N, int64_t C, int64_t H,
+                           int64_t W, int64_t D, int64_t x_strideN, int64_t x_strideH, int64_t x_strideW,
+                           int64_t r_strideN, int64_t r_strideH, int64_t r_strideW, int64_t y_strideN,
+                           int64_t y_strideH, int64_t y_strideW, int tune, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

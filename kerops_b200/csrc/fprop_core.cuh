@@ -177,4 +177,78 @@ KDW_HD void fprop_step_f32(const __half* __restrict__ in, __half* __restrict__ o
     }
 }
 
+// fprop_step_f32 with a fused epilogue: the finished plane gets a residual added in fp16 (as a separate
+// elementwise add of two fp16 tensors would) and, for the thread's `mv` valid outputs, the stored fp16 values
+// and their squares are accumulated in fp32 (S1, S2) for per-channel statistics.  `res` points at the thread's
+// first residual value in a [WT][DT][CS] tile.  The reference runs this as a second operator over the
+// convolution's output (kerops/kernels/addition.py:5-37).
+template <class Cfg>
+KDW_HD void fprop_step_f32_addstats(const __half* __restrict__ in, const __half* __restrict__ res,
+                                    __half* __restrict__ ob, bool store, int mv, const __half2 (&wgt)[27][Cfg::CP],
+                                    float2 (&A)[Cfg::M][Cfg::CP], float2 (&B)[Cfg::M][Cfg::CP],
+                                    float2 (&S1)[Cfg::CP], float2 (&S2)[Cfg::CP]) {
+    constexpr int CS = Cfg::CS, DT = Cfg::DT, M = Cfg::M, CP = Cfg::CP, DPW = Cfg::DPW;
+    float2 T[3][CP];
+#pragma unroll
+    for (int j = 0; j < M + 2; ++j) {
+        __half2 xv[3][CP];
+#pragma unroll
+        for (int t = 0; t < 3; ++t) lds_h2<CP>(xv[t], in + (j * (DT + 2) + t) * CS);
+#pragma unroll
+        for (int b = 0; b < 3; ++b) {
+            const int m = j - b;
+            if (m < 0 || m >= M) continue;
+#pragma unroll
+            for (int i = 0; i < CP; ++i) {
+                float2 f = B[m][i];
+                f = fma_h2_f2(wgt[(6 + b) * 3 + 0][i], xv[0][i], f);
+                f = fma_h2_f2(wgt[(6 + b) * 3 + 1][i], xv[1][i], f);
+                B[m][i] = fma_h2_f2(wgt[(6 + b) * 3 + 2][i], xv[2][i], f);
+            }
+        }
+        if (j >= 2 && store) {
+            const int m = j - 2;
+            __half2 o[CP], r[CP];
+            lds_h2<CP>(r, res + (m * DT) * CS);
+#pragma unroll
+            for (int i = 0; i < CP; ++i) {
+                o[i] = h2_add(__float22half2_rn(B[m][i]), r[i]);
+                if (m < mv) {
+                    S1[i] = add_h2_f2(o[i], S1[i]);
+                    S2[i] = fma_h2_f2(o[i], o[i], S2[i]);
+                }
+            }
+            sts_h2<CP>(ob + (m * DPW) * CS, o);
+        }
+#pragma unroll
+        for (int b = 0; b < 3; ++b) {
+            const int m = j - b;
+            if (m < 0 || m >= M) continue;
+#pragma unroll
+            for (int i = 0; i < CP; ++i) {
+                float2 f = A[m][i];
+                f = fma_h2_f2(wgt[(3 + b) * 3 + 0][i], xv[0][i], f);
+                f = fma_h2_f2(wgt[(3 + b) * 3 + 1][i], xv[1][i], f);
+                A[m][i] = fma_h2_f2(wgt[(3 + b) * 3 + 2][i], xv[2][i], f);
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < 3; ++b) {
+            const int m = j - b;
+            if (m < 0 || m >= M) continue;
+#pragma unroll
+            for (int i = 0; i < CP; ++i) {
+                float2 f = (b == 0) ? make_float2(0.f, 0.f) : T[m % 3][i];
+                f = fma_h2_f2(wgt[b * 3 + 0][i], xv[0][i], f);
+                f = fma_h2_f2(wgt[b * 3 + 1][i], xv[1][i], f);
+                f = fma_h2_f2(wgt[b * 3 + 2][i], xv[2][i], f);
+                if (b == 2)
+                    B[m][i] = f;
+                else
+                    T[m % 3][i] = f;
+            }
+        }
+    }
+}
+
 }  // namespace kdw

@@ -263,6 +263,14 @@ KDW_HD __half2 h2_mul(__half2 a, __half2 b) {
     return __floats2half2_rn(fa.x * fb.x, fa.y * fb.y);  // an fp16 x fp16 product is exact in fp32
 #endif
 }
+KDW_HD __half2 h2_add(__half2 a, __half2 b) {
+#ifdef __CUDA_ARCH__
+    return __hadd2(a, b);
+#else
+    const float2 fa = __half22float2(a), fb = __half22float2(b);
+    return __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);  // the fp32 sum of two fp16 values is exact
+#endif
+}
 KDW_HD __half2 h2_fma(__half2 a, __half2 b, __half2 c) {
 #ifdef __CUDA_ARCH__
     return __hfma2(a, b, c);

@@ -1,4 +1,5 @@
 from .dwconv import DWConv
+from .dwconv_addstats import DWConvAddStats
 from .dwconv_wgrad import DWConvWGRAD
 
-__all__ = ['DWConv', 'DWConvWGRAD']
+__all__ = ['DWConv', 'DWConvWGRAD', 'DWConvAddStats']

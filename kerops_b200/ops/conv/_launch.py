@@ -89,3 +89,23 @@ def wgrad(x, grad, h_begin=None, h_end=None, g_h0=0, want_f32=False, want_f16=Tr
         )
     _lib.check(rc)
     return dw32, dw16
+
+
+def fprop_addstats(x, weight, residual, y, tune=0):
+    """Enqueues y = fp16(conv(x)) + residual and returns (mean, sqmean), fp32 [C], of y per channel."""
+    lib = _lib.load()
+    N, C, H, W, D = x.shape
+    xs, rs, ys = volume_strides(x), volume_strides(residual), volume_strides(y)
+    tune = tune or _env_tune('KDW_ADDSTATS_TUNE')
+    with torch.cuda.device(x.device):
+        nbytes = lib.kdw_fprop_addstats_workspace_bytes(N, C, H, W, D)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+        mean = torch.empty(C, dtype=torch.float32, device=x.device)
+        sqmean = torch.empty(C, dtype=torch.float32, device=x.device)
+        rc = lib.kdw_fprop_addstats_f16(
+            x.data_ptr(), weight.data_ptr(), residual.data_ptr(), y.data_ptr(), ws.data_ptr(), nbytes,
+            mean.data_ptr(), sqmean.data_ptr(), N, C, H, W, D, xs[0], xs[1], xs[2], rs[0], rs[1], rs[2], ys[0], ys[1],
+            ys[2], tune, _stream_ptr(x.device),
+        )
+    _lib.check(rc)
+    return mean, sqmean

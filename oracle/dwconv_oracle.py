@@ -22,6 +22,8 @@ fprop_reference_numerics restates the arithmetic order of kerops/kernels/dw_conv
 wgrad_exact              dw[a,b,t,c] = sum_{n,h,w,d} g[n,h,w,d,c] * x[n,h+a-1,w+b-1,d+t-1,c]
                          in fp64 (kerops/kernels/dw_conv.py:224-275 computes the same sum from
                          fp16 products with fp32/fp16 partials).
+addstats_exact           out = conv_out + residual (fp16 add) with the fp64 channel mean and mean of squares
+                         of out, the arithmetic of kerops/kernels/addition.py:28-37.
 
 Pinning: tests/test_oracle_golden.py checks these functions against vectors
 produced by the reference kernels themselves (tests/golden/*.npz, made by
@@ -92,6 +94,15 @@ def wgrad_exact(x, grad, acc_dtype=np.float64):
 def dgrad_exact(grad, weight, acc_dtype=np.float32):
     """Input gradient = fprop of grad with the taps flipped on all three axes."""
     return fprop_exact(grad, weight[::-1, ::-1, ::-1].copy(), acc_dtype)
+
+
+def addstats_exact(conv_out, residual):
+    """out = conv_out + residual as an fp16 add, and the per-channel mean and mean of squares of out in fp64
+    (kerops/kernels/addition.py:28-37: output = x + y, mean = sum(output) / numel_no_channels, sqmean likewise)."""
+    assert conv_out.dtype == np.float16 and residual.dtype == np.float16 and conv_out.shape == residual.shape
+    out = (conv_out.astype(np.float32) + residual.astype(np.float32)).astype(np.float16)  # exact sum, one rounding
+    o = out.astype(np.float64).reshape(-1, out.shape[-1])
+    return out, o.mean(axis=0), (o * o).mean(axis=0)
 
 
 def rel_l2(a, b):

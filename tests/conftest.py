@@ -69,4 +69,6 @@ def kdw_emu(kdw_lib):
     emu.emu_wgrad.restype = ci
     emu.emu_schedule.argtypes = [i64] * 4 + [ci] * 6 + [vp, ctypes.POINTER(i64), ctypes.POINTER(i64)]
     emu.emu_schedule.restype = ci
+    emu.emu_fprop_addstats.argtypes = [ci, vp, vp, vp, vp, vp] + [i64] * 5 + [ci]
+    emu.emu_fprop_addstats.restype = ci
     return emu

@@ -184,6 +184,91 @@ static int emu_wgrad_cfg(const __half* x, const __half* gr, float* dw, Vol vx, V
         return emu_wgrad_cfg<WCfg<CS, DT, WT, M, CP, ST, MINB>>((const __half*)x, (const __half*)g, dw, vx, vg,  \
                                                                 h_begin, h_end, g_h0, grid);
 
+// The fused forward + residual add + statistics kernel (dwconv_fprop_addstats.cu), same walk as emu_fprop_cfg.
+// stats receives [2][C] sums (not yet divided by the voxel count).
+template <class Cfg>
+static int emu_addstats_cfg(const __half* x, const __half* w, const __half* r, __half* y, double* stats, Vol v,
+                            int grid_target) {
+    constexpr int M = Cfg::M, CP = Cfg::CP;
+    struct TState {
+        __half2 wgt[27][CP];
+        float2 P1[M][CP], P2[M][CP], S1[CP], S2[CP];
+        int mv;
+    };
+    Sched s;
+    const int grid = make_sched(&s, v.N, v.C, v.W, v.D, 0, (int)v.H, Cfg::WT, Cfg::DT, Cfg::CS, grid_target);
+    std::vector<__half> stage(Cfg::IN_BYTES / 2), rt((size_t)Cfg::WT * Cfg::DT * Cfg::CS);
+    std::vector<__half> out((size_t)Cfg::NCW * Cfg::OUTW_BYTES / 2);
+    std::vector<TState> ts(Cfg::NT);
+    for (int k = 0; k < 2 * v.C; ++k) stats[k] = 0.0;
+    for (int blk = 0; blk < grid; ++blk) {
+        memset(ts.data(), 0, sizeof(TState) * ts.size());
+        std::vector<float> row(2 * v.C, 0.f);
+        StepIter cons;
+        cons.init(s, blk, grid);
+        unsigned ci = 0;
+        int cur_c0 = -1;
+        auto flush = [&](int c0) {
+            for (int tid = 0; tid < Cfg::NT; ++tid) {
+                const FThread<Cfg> th(tid);
+                for (int i = 0; i < CP; ++i) {
+                    row[c0 + th.cg * 2 * CP + 2 * i] += ts[tid].S1[i].x;
+                    row[c0 + th.cg * 2 * CP + 2 * i + 1] += ts[tid].S1[i].y;
+                    row[v.C + c0 + th.cg * 2 * CP + 2 * i] += ts[tid].S2[i].x;
+                    row[v.C + c0 + th.cg * 2 * CP + 2 * i + 1] += ts[tid].S2[i].y;
+                    ts[tid].S1[i] = ts[tid].S2[i] = make_float2(0.f, 0.f);
+                }
+            }
+        };
+        while (cons.active) {
+            const int q = cons.q;
+            const Seg& g = cons.g;
+            if (q == g.hb - 1 && g.c0 != cur_c0) {
+                if (cur_c0 >= 0) flush(cur_c0);
+                cur_c0 = g.c0;
+            }
+            emu_tma_load(stage.data(), x, v, Cfg::CS, Cfg::DT + 2, Cfg::WT + 2, g.c0, g.d0 - 1, g.w0 - 1, q, g.n);
+            const bool store = q - 1 >= g.hb;
+            if (store)
+                emu_tma_load(rt.data(), r, v, Cfg::CS, Cfg::DT, Cfg::WT, g.c0, g.d0, g.w0, q - 1, g.n);
+            else
+                for (auto& e : rt) e = __float2half(12345.f);  // stale data must never be used
+            for (int tid = 0; tid < Cfg::NT; ++tid) {
+                TState& t = ts[tid];
+                const FThread<Cfg> th(tid);
+                if (q == g.hb - 1) {
+                    const __half* wp = w + g.c0 + th.cg * 2 * CP;
+                    for (int k = 0; k < 27; ++k)
+                        for (int i = 0; i < CP; ++i) t.wgt[k][i] = *reinterpret_cast<const __half2*>(wp + (size_t)k * v.C + 2 * i);
+                    int mv = (int)v.W - (g.w0 + th.wg * M);
+                    mv = mv < 0 ? 0 : (mv > M ? M : mv);
+                    if (g.d0 + th.d >= v.D) mv = 0;
+                    t.mv = mv;
+                }
+                const __half* in = stage.data() + th.in_off;
+                const __half* res = rt.data() + ((th.wg * M) * Cfg::DT + th.d) * Cfg::CS + th.cg * 2 * CP;
+                __half* ob = out.data() + (size_t)(tid / 32) * (Cfg::OUTW_BYTES / 2) + th.out_off;
+                if (ci & 1u)
+                    fprop_step_f32_addstats<Cfg>(in, res, ob, store, t.mv, t.wgt, t.P2, t.P1, t.S1, t.S2);
+                else
+                    fprop_step_f32_addstats<Cfg>(in, res, ob, store, t.mv, t.wgt, t.P1, t.P2, t.S1, t.S2);
+            }
+            if (store) {
+                for (int wp = 0; wp < Cfg::NCW; ++wp) {
+                    const FThread<Cfg> th(wp * 32);
+                    emu_tma_store(y, out.data() + (size_t)wp * (Cfg::OUTW_BYTES / 2), v, Cfg::CS, Cfg::DPW, Cfg::M, g.c0,
+                                  g.d0 + th.warp_d0, g.w0 + th.wg * Cfg::M, q - 1, g.n);
+                }
+            }
+            cons.next(s);
+            ++ci;
+        }
+        if (cur_c0 >= 0) flush(cur_c0);
+        for (int k = 0; k < 2 * v.C; ++k) stats[k] += row[k];
+    }
+    return grid;
+}
+
 extern "C" {
 
 // Returns the emulated grid size (> 0) or a negative error.  Volumes are dense channels-last.
@@ -240,6 +325,21 @@ int emu_schedule(int64_t N, int64_t C, int64_t W, int64_t D, int h_begin, int h_
     *min_steps = lo;
     *max_steps = hi;
     return grid;
+}
+
+// which: 1..5, the tiles of dwconv_fprop_addstats.cu in its order.
+int emu_fprop_addstats(int which, const void* x, const void* w, const void* r, void* y, double* stats, int64_t N,
+                       int64_t C, int64_t H, int64_t W, int64_t D, int grid) {
+    const Vol v{N, C, H, W, D, H * W * D * C, W * D * C, D * C};
+    const __half *xh = (const __half*)x, *wh = (const __half*)w, *rh = (const __half*)r;
+    switch (which) {
+        case 1: return emu_addstats_cfg<FCfg<8, 64, 8, 8, 1, 4, 2>>(xh, wh, rh, (__half*)y, stats, v, grid);
+        case 2: return emu_addstats_cfg<FCfg<16, 32, 8, 8, 1, 4, 2>>(xh, wh, rh, (__half*)y, stats, v, grid);
+        case 3: return emu_addstats_cfg<FCfg<32, 16, 8, 8, 1, 4, 2>>(xh, wh, rh, (__half*)y, stats, v, grid);
+        case 4: return emu_addstats_cfg<FCfg<32, 32, 8, 8, 1, 3, 1>>(xh, wh, rh, (__half*)y, stats, v, grid);
+        case 5: return emu_addstats_cfg<FCfg<64, 8, 8, 8, 1, 4, 2>>(xh, wh, rh, (__half*)y, stats, v, grid);
+    }
+    return -1;
 }
 
 }  // extern "C"

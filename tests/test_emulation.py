@@ -139,3 +139,32 @@ def test_schedule_covers_every_unit_once_random_shapes(kdw_emu):
         assert counts.min() == 1 and counts.max() == 1
 
     check()
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Fused forward + residual add + channel statistics (dwconv_fprop_addstats.cu), every tile of that kernel
+# ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize('which,shape', [(1, (1, 8, 5, 13, 70)), (2, (2, 16, 4, 9, 37)), (3, (1, 32, 6, 11, 21)),
+                                         (4, (1, 64, 3, 10, 40)), (5, (2, 64, 4, 7, 9)), (5, (1, 128, 3, 17, 12))])
+def test_emulated_fprop_addstats(kdw_emu, which, shape):
+    import ctypes
+
+    from oracle import dwconv_oracle as orc
+
+    N, C, H, W, D = shape
+    rng = np.random.default_rng(100 + which + C)
+    x = rng.standard_normal((N, H, W, D, C)).astype(np.float16)
+    r = rng.standard_normal((N, H, W, D, C)).astype(np.float16)
+    w = ((rng.random((3, 3, 3, C)) * 2 - 1) / np.sqrt(27)).astype(np.float16)
+    y = np.full_like(x, np.float16(777))
+    stats = np.zeros(2 * C, dtype=np.float64)
+    vp = ctypes.c_void_p
+    for grid in (3, 40):
+        g = kdw_emu.emu_fprop_addstats(which, x.ctypes.data_as(vp), w.ctypes.data_as(vp), r.ctypes.data_as(vp),
+                                       y.ctypes.data_as(vp), stats.ctypes.data_as(vp), N, C, H, W, D, grid)
+        assert g > 0
+        out, mean, sqmean = orc.addstats_exact(orc.fprop_exact(x, w), r)
+        assert np.array_equal(y, out)  # exact products, fp32 sums, one rounding, then an exact fp16 add
+        n = N * H * W * D
+        np.testing.assert_allclose(stats[:C] / n, mean, rtol=1e-5, atol=1e-6)
+        np.testing.assert_allclose(stats[C:] / n, sqmean, rtol=1e-5, atol=1e-6)
