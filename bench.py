@@ -712,6 +712,82 @@ def run_dpstep(args):
         dist.destroy_process_group()
 
 
+def run_fused(args):
+    """The fused neighbour: DWConvAddStats(x, weight, residual) per C of the sweep, one GPU.  Algorithmic bytes per
+    call: read x, read residual, write out = 6*V*C.  Comparators timed in the same run: our DWConv followed by a
+    torch fp16 add and channel means, and - when baseline/_ref is present - the reference's AddStats(DWConv(...))."""
+    import torch
+
+    from kerops_b200 import _lib
+    from kerops_b200.ops.conv import DWConv, DWConvAddStats
+
+    dev = torch.device('cuda', int(os.environ.get('LOCAL_RANK', '0')))
+    torch.cuda.set_device(dev)
+    _lib.load()
+    peak, peak_kind = measured_peak()
+    ref_ops = None
+    ref_root = os.path.join(ROOT, 'baseline', '_ref')
+    if os.path.isdir(os.path.join(ref_root, 'kerops')):
+        sys.path.append(ref_root)
+        try:
+            from kerops.ops.addition import AddStats as RefAddStats
+            from kerops.ops.conv import DWConv as RefDWConv
+
+            ref_ops = (RefDWConv, RefAddStats)
+        except Exception:
+            ref_ops = None
+
+    def timeit(fn, reps):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    def unfused(x, w, r):
+        out = DWConv(x, w) + r
+        o = out.float()
+        return out, o.mean(dim=(0, 2, 3, 4)), (o * o).mean(dim=(0, 2, 3, 4))
+
+    detail, tot_ms, tot_bytes = {}, 0.0, 0
+    sampler = ClockSampler(dev)
+    sampler.start()
+    sampler.begin()
+    for C in args.channels:
+        x, r, w = make_gpu_inputs(C, dev, seed=C)
+        nbytes = 6 * VOX * C
+        ms = timeit(lambda: DWConvAddStats(x, w, r), args.steps)
+        row = {'ms': round(ms, 4), 'gbs': round(nbytes / ms / 1e6, 1), 'frac': round(nbytes / ms / 1e6 / peak, 4),
+               'unfused_ms': round(timeit(lambda: unfused(x, w, r), 3), 4)}
+        if ref_ops is not None:
+            try:
+                row['reference_chain_ms'] = round(timeit(lambda: ref_ops[1](ref_ops[0](x, w), r), 3), 4)
+            except Exception as e:
+                row['reference_chain_ms'] = f'{type(e).__name__}'
+        detail[str(C)] = row
+        tot_ms += ms
+        tot_bytes += nbytes
+        del x, r, w
+    clocks = sampler.stop()
+    value = tot_bytes / tot_ms / 1e6
+    print(json.dumps({
+        'metric': 'DWConvAddStats algorithmic HBM GB/s at (1,C,%d,350,128) fp16 channels_last_3d' % SHAPE[0],
+        'value': round(value, 1), 'unit': 'GB/s', 'n_gpus': 1, 'steps': args.steps, 'warmup': 3,
+        'ms_per_step': round(tot_ms, 4), 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
+        'dtype': 'f16 products, f32 accumulation', 'data': 'synthetic',
+        'config': {'workload': 'fused forward + residual add + channel statistics, C in '
+                               + ','.join(map(str, args.channels)), 'l2': 'inputs larger than L2'},
+        'roofline': {'bound': 'hbm', 'kernel': 'fprop_addstats_kernel, all C', 'achieved': round(value, 1), 'peak': peak,
+                     'peak_kind': peak_kind, 'unit': 'GB/s', 'frac': round(value / peak, 4), 'traffic': None},
+        'clocks': clocks, 'gpu_launches': 2 * len(args.channels) * args.steps, 'detail': detail,
+        'device_status': _lib.device_status(),
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -721,9 +797,9 @@ def main():
     ap.add_argument('--channels', default=','.join(map(str, ALL_CHANNELS)))
     ap.add_argument('--planes', type=int, default=SHAPE[0],
                     help='h extent of the volume (default 350); smaller values are for profiler captures only')
-    ap.add_argument('--workload', default='sweep', choices=['sweep', 'dshard', 'dpstep'],
+    ap.add_argument('--workload', default='sweep', choices=['sweep', 'dshard', 'dpstep', 'fused'],
                     help="'sweep' (default): the headline per-C sweep, one sample per GPU; 'dshard': one large volume "
-                         "sharded along H over the GPUs; 'dpstep': a batch of (32,350,350,128) samples split by sample")
+                         "sharded along H over the GPUs; 'dpstep': a batch of (32,350,350,128) samples split by sample; 'fused': DWConvAddStats, one GPU")
     ap.add_argument('--dp-batch', type=int, default=8)
     ap.add_argument('--allreduce', default='push', choices=['nccl', 'push'],
                     help="how the fp32 weight gradients are summed over the ranks: NCCL, or the library's own "
@@ -748,6 +824,8 @@ def main():
         run_dshard(args)
     elif args.workload == 'dpstep':
         run_dpstep(args)
+    elif args.workload == 'fused':
+        run_fused(args)
     else:
         run_ours(args)
 
