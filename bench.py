@@ -713,13 +713,15 @@ def run_dpstep(args):
 
 
 def run_fused(args):
-    """The fused neighbour: DWConvAddStats(x, weight, residual) per C of the sweep, one GPU.  Algorithmic bytes per
-    call: read x, read residual, write out = 6*V*C.  Comparators timed in the same run: our DWConv followed by a
-    torch fp16 add and channel means, and - when baseline/_ref is present - the reference's AddStats(DWConv(...))."""
+    """The fused neighbours, per C of the sweep, one GPU.  Headline: DWConvAddStats(x, weight, residual), algorithmic
+    bytes per call read x + read residual + write out = 6*V*C; comparators timed in the same run: our DWConv followed
+    by a torch fp16 add and channel means, and - when baseline/_ref is present - the reference's
+    AddStats(DWConv(...)).  Also timed (detail[C]['bnrelu']): DWConvBNReLU against the reference's
+    DWConv(ApplyBNReLU(...))."""
     import torch
 
     from kerops_b200 import _lib
-    from kerops_b200.ops.conv import DWConv, DWConvAddStats
+    from kerops_b200.ops.conv import DWConv, DWConvAddStats, DWConvBNReLU
 
     dev = torch.device('cuda', int(os.environ.get('LOCAL_RANK', '0')))
     torch.cuda.set_device(dev)
@@ -731,9 +733,10 @@ def run_fused(args):
         sys.path.append(ref_root)
         try:
             from kerops.ops.addition import AddStats as RefAddStats
+            from kerops.ops.bnrelu import ApplyBNReLU as RefApplyBNReLU
             from kerops.ops.conv import DWConv as RefDWConv
 
-            ref_ops = (RefDWConv, RefAddStats)
+            ref_ops = (RefDWConv, RefAddStats, RefApplyBNReLU)
         except Exception:
             ref_ops = None
 
@@ -768,6 +771,17 @@ def run_fused(args):
                 row['reference_chain_ms'] = round(timeit(lambda: ref_ops[1](ref_ops[0](x, w), r), 3), 4)
             except Exception as e:
                 row['reference_chain_ms'] = f'{type(e).__name__}'
+        # the prologue neighbour: y = DWConv(relu(x * scale + shift)); algorithmic bytes 4*V*C like the plain conv
+        scale, shift = torch.rand(C, device=dev) + 0.5, torch.randn(C, device=dev) * 0.5
+        ms_b = timeit(lambda: DWConvBNReLU(x, scale, shift, w), args.steps)
+        row['bnrelu'] = {'ms': round(ms_b, 4), 'gbs': round(4 * VOX * C / ms_b / 1e6, 1),
+                         'frac': round(4 * VOX * C / ms_b / 1e6 / peak, 4)}
+        if ref_ops is not None:
+            try:
+                row['bnrelu']['reference_chain_ms'] = round(
+                    timeit(lambda: ref_ops[0](ref_ops[2](x, scale, shift), w), 3), 4)
+            except Exception as e:
+                row['bnrelu']['reference_chain_ms'] = f'{type(e).__name__}'
         detail[str(C)] = row
         tot_ms += ms
         tot_bytes += nbytes
@@ -783,7 +797,7 @@ def run_fused(args):
                                + ','.join(map(str, args.channels)), 'l2': 'inputs larger than L2'},
         'roofline': {'bound': 'hbm', 'kernel': 'fprop_addstats_kernel, all C', 'achieved': round(value, 1), 'peak': peak,
                      'peak_kind': peak_kind, 'unit': 'GB/s', 'frac': round(value / peak, 4), 'traffic': None},
-        'clocks': clocks, 'gpu_launches': 2 * len(args.channels) * args.steps, 'detail': detail,
+        'clocks': clocks, 'gpu_launches': 3 * len(args.channels) * args.steps, 'detail': detail,
         'device_status': _lib.device_status(),
     }), flush=True)
 

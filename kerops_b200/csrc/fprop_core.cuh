@@ -251,4 +251,33 @@ KDW_HD void fprop_step_f32_addstats(const __half* __restrict__ in, const __half*
     }
 }
 
+// Prologue for the fused BN-affine + ReLU: x' = fp16(max(fma(float(x), scale[c], shift[c]), 0)) applied IN PLACE
+// to the part of a staged input tile [(WT+2)][(DT+2)][CS] that lies inside the volume (lines [w_lo, w_hi), depth
+// positions [d_lo, d_hi) of the tile; everything else is the zero padding of the convolution and must stay
+// zero).  Thread `tid` of the NT consumer threads handles items tid, tid + NT, ...; an item is 8 channels of
+// one voxel (one 16-byte access).  `ss` = scale[CS] then shift[CS] of the CTA's channel slice.  Same arithmetic
+// as the reference's separate operator (kerops/kernels/bnrelu.py:25-31).
+template <class Cfg>
+KDW_HD void bnrelu_stage(__half* tile, const float* ss, int tid, int w_lo, int w_hi, int d_lo, int d_hi) {
+    constexpr int CS = Cfg::CS, G = CS / 8, ROW = Cfg::DT + 2, NV = (Cfg::WT + 2) * ROW;
+    static_assert(Cfg::NT % G == 0, "a thread keeps its channel group");
+    const int cg = tid % G;
+    for (int v = tid / G; v < NV; v += Cfg::NT / G) {
+        const int line = v / ROW, dd = v - line * ROW;
+        if (line < w_lo || line >= w_hi || dd < d_lo || dd >= d_hi) continue;
+        __half* p = tile + (v * CS + cg * 8);
+        __half2 h[4];
+        lds_h2<4>(h, p);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = cg * 8 + 2 * i;
+            float2 f = __half22float2(h[i]);
+            f.x = fmaxf(fmaf(f.x, ss[c], ss[CS + c]), 0.f);
+            f.y = fmaxf(fmaf(f.y, ss[c + 1], ss[CS + c + 1]), 0.f);
+            h[i] = __float22half2_rn(f);
+        }
+        sts_h2<4>(p, h);
+    }
+}
+
 }  // namespace kdw

@@ -109,3 +109,18 @@ def fprop_addstats(x, weight, residual, y, tune=0):
         )
     _lib.check(rc)
     return mean, sqmean
+
+
+def fprop_bnrelu(x, scale, shift, weight, y, tune=0):
+    """Enqueues y = conv(relu(x * scale + shift)) (scale, shift fp32 [C])."""
+    lib = _lib.load()
+    N, C, H, W, D = x.shape
+    xs, ys = volume_strides(x), volume_strides(y)
+    tune = tune or _env_tune('KDW_BNRELU_TUNE')
+    with torch.cuda.device(x.device):
+        rc = lib.kdw_fprop_bnrelu_f16(
+            x.data_ptr(), scale.data_ptr(), shift.data_ptr(), weight.data_ptr(), y.data_ptr(), N, C, H, W, D, xs[0],
+            xs[1], xs[2], ys[0], ys[1], ys[2], tune, _stream_ptr(x.device),
+        )
+    _lib.check(rc)
+    return y

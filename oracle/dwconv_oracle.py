@@ -24,6 +24,7 @@ wgrad_exact              dw[a,b,t,c] = sum_{n,h,w,d} g[n,h,w,d,c] * x[n,h+a-1,w+
                          fp16 products with fp32/fp16 partials).
 addstats_exact           out = conv_out + residual (fp16 add) with the fp64 channel mean and mean of squares
                          of out, the arithmetic of kerops/kernels/addition.py:28-37.
+bnrelu_exact             fp16(max(fma(x, scale[c], shift[c]), 0)), the arithmetic of kerops/kernels/bnrelu.py:25-31.
 
 Pinning: tests/test_oracle_golden.py checks these functions against vectors
 produced by the reference kernels themselves (tests/golden/*.npz, made by
@@ -103,6 +104,16 @@ def addstats_exact(conv_out, residual):
     out = (conv_out.astype(np.float32) + residual.astype(np.float32)).astype(np.float16)  # exact sum, one rounding
     o = out.astype(np.float64).reshape(-1, out.shape[-1])
     return out, o.mean(axis=0), (o * o).mean(axis=0)
+
+
+def bnrelu_exact(x, scale, shift):
+    """fp16(max(x * scale[c] + shift[c], 0)) with the multiply-add in fp32 as one fused operation
+    (kerops/kernels/bnrelu.py:25-31; evaluated in fp64 and rounded to fp32: an fp16 x fp32 product fits a double
+    exactly, so only the rare double rounding of the sum can differ from a hardware FMA)."""
+    assert x.dtype == np.float16
+    f = (x.astype(np.float64) * scale.astype(np.float32).astype(np.float64)
+         + shift.astype(np.float32).astype(np.float64)).astype(np.float32)
+    return np.maximum(f, np.float32(0)).astype(np.float16)
 
 
 def rel_l2(a, b):

@@ -71,4 +71,6 @@ def kdw_emu(kdw_lib):
     emu.emu_schedule.restype = ci
     emu.emu_fprop_addstats.argtypes = [ci, vp, vp, vp, vp, vp] + [i64] * 5 + [ci]
     emu.emu_fprop_addstats.restype = ci
+    emu.emu_fprop_bnrelu.argtypes = [ci, vp, vp, vp, vp, vp] + [i64] * 5 + [ci]
+    emu.emu_fprop_bnrelu.restype = ci
     return emu

@@ -269,6 +269,71 @@ static int emu_addstats_cfg(const __half* x, const __half* w, const __half* r, _
     return grid;
 }
 
+// The fused BN-affine + ReLU prologue kernel (dwconv_fprop_bnrelu.cu): the staged tile is activated in place by
+// the consumer threads (bnrelu_stage), then convolved as usual.
+template <class Cfg>
+static int emu_bnrelu_cfg(const __half* x, const float* scale, const float* shift, const __half* w, __half* y, Vol v,
+                          int grid_target) {
+    constexpr int M = Cfg::M, CP = Cfg::CP, CS = Cfg::CS;
+    struct TState {
+        __half2 wgt[27][CP];
+        float2 P1[M][CP], P2[M][CP];
+    };
+    Sched s;
+    const int grid = make_sched(&s, v.N, v.C, v.W, v.D, 0, (int)v.H, Cfg::WT, Cfg::DT, Cfg::CS, grid_target);
+    std::vector<__half> stage(Cfg::IN_BYTES / 2);
+    std::vector<__half> out((size_t)Cfg::NCW * Cfg::OUTW_BYTES / 2);
+    std::vector<TState> ts(Cfg::NT);
+    std::vector<float> ss(2 * CS);
+    for (int blk = 0; blk < grid; ++blk) {
+        memset(ts.data(), 0, sizeof(TState) * ts.size());
+        StepIter cons;
+        cons.init(s, blk, grid);
+        unsigned ci = 0;
+        while (cons.active) {
+            const int q = cons.q;
+            const Seg& g = cons.g;
+            for (int c = 0; c < CS; ++c) {
+                ss[c] = scale[g.c0 + c];
+                ss[CS + c] = shift[g.c0 + c];
+            }
+            int w_lo = g.w0 >= 1 ? 0 : 1 - g.w0, w_hi = (int)v.W - g.w0 + 1;
+            int d_lo = g.d0 >= 1 ? 0 : 1 - g.d0, d_hi = (int)v.D - g.d0 + 1;
+            w_hi = w_hi > Cfg::WT + 2 ? Cfg::WT + 2 : w_hi;
+            d_hi = d_hi > Cfg::DT + 2 ? Cfg::DT + 2 : d_hi;
+            emu_tma_load(stage.data(), x, v, CS, Cfg::DT + 2, Cfg::WT + 2, g.c0, g.d0 - 1, g.w0 - 1, q, g.n);
+            if (q >= 0 && q < v.H)
+                for (int tid = 0; tid < Cfg::NT; ++tid) bnrelu_stage<Cfg>(stage.data(), ss.data(), tid, w_lo, w_hi, d_lo, d_hi);
+            const bool store = q - 1 >= g.hb;
+            for (int tid = 0; tid < Cfg::NT; ++tid) {
+                TState& t = ts[tid];
+                const FThread<Cfg> th(tid);
+                if (q == g.hb - 1) {
+                    const __half* wp = w + g.c0 + th.cg * 2 * CP;
+                    for (int k = 0; k < 27; ++k)
+                        for (int i = 0; i < CP; ++i) t.wgt[k][i] = *reinterpret_cast<const __half2*>(wp + (size_t)k * v.C + 2 * i);
+                }
+                const __half* in = stage.data() + th.in_off;
+                __half* ob = out.data() + (size_t)(tid / 32) * (Cfg::OUTW_BYTES / 2) + th.out_off;
+                if (ci & 1u)
+                    fprop_step_f32<Cfg>(in, ob, store, t.wgt, t.P2, t.P1);
+                else
+                    fprop_step_f32<Cfg>(in, ob, store, t.wgt, t.P1, t.P2);
+            }
+            if (store) {
+                for (int wp = 0; wp < Cfg::NCW; ++wp) {
+                    const FThread<Cfg> th(wp * 32);
+                    emu_tma_store(y, out.data() + (size_t)wp * (Cfg::OUTW_BYTES / 2), v, CS, Cfg::DPW, Cfg::M, g.c0,
+                                  g.d0 + th.warp_d0, g.w0 + th.wg * Cfg::M, q - 1, g.n);
+                }
+            }
+            cons.next(s);
+            ++ci;
+        }
+    }
+    return grid;
+}
+
 extern "C" {
 
 // Returns the emulated grid size (> 0) or a negative error.  Volumes are dense channels-last.
@@ -338,6 +403,22 @@ int emu_fprop_addstats(int which, const void* x, const void* w, const void* r, v
         case 3: return emu_addstats_cfg<FCfg<32, 16, 8, 8, 1, 4, 2>>(xh, wh, rh, (__half*)y, stats, v, grid);
         case 4: return emu_addstats_cfg<FCfg<32, 32, 8, 8, 1, 3, 1>>(xh, wh, rh, (__half*)y, stats, v, grid);
         case 5: return emu_addstats_cfg<FCfg<64, 8, 8, 8, 1, 4, 2>>(xh, wh, rh, (__half*)y, stats, v, grid);
+    }
+    return -1;
+}
+
+// which: 1..6, the tiles of dwconv_fprop_bnrelu.cu in its order.
+int emu_fprop_bnrelu(int which, const void* x, const float* scale, const float* shift, const void* w, void* y,
+                     int64_t N, int64_t C, int64_t H, int64_t W, int64_t D, int grid) {
+    const Vol v{N, C, H, W, D, H * W * D * C, W * D * C, D * C};
+    const __half *xh = (const __half*)x, *wh = (const __half*)w;
+    switch (which) {
+        case 1: return emu_bnrelu_cfg<FCfg<8, 64, 8, 8, 1, 4, 2>>(xh, scale, shift, wh, (__half*)y, v, grid);
+        case 2: return emu_bnrelu_cfg<FCfg<16, 64, 8, 8, 1, 3, 1>>(xh, scale, shift, wh, (__half*)y, v, grid);
+        case 3: return emu_bnrelu_cfg<FCfg<16, 32, 8, 8, 1, 4, 2>>(xh, scale, shift, wh, (__half*)y, v, grid);
+        case 4: return emu_bnrelu_cfg<FCfg<32, 32, 8, 8, 1, 3, 1>>(xh, scale, shift, wh, (__half*)y, v, grid);
+        case 5: return emu_bnrelu_cfg<FCfg<32, 16, 8, 8, 1, 4, 2>>(xh, scale, shift, wh, (__half*)y, v, grid);
+        case 6: return emu_bnrelu_cfg<FCfg<64, 8, 8, 8, 1, 4, 2>>(xh, scale, shift, wh, (__half*)y, v, grid);
     }
     return -1;
 }

@@ -168,3 +168,31 @@ def test_emulated_fprop_addstats(kdw_emu, which, shape):
         n = N * H * W * D
         np.testing.assert_allclose(stats[:C] / n, mean, rtol=1e-5, atol=1e-6)
         np.testing.assert_allclose(stats[C:] / n, sqmean, rtol=1e-5, atol=1e-6)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Fused BN-affine + ReLU prologue (dwconv_fprop_bnrelu.cu), every tile of that kernel
+# ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize('which,shape', [(1, (1, 8, 5, 13, 70)), (2, (2, 16, 4, 9, 37)), (3, (1, 16, 3, 9, 33)),
+                                         (4, (1, 64, 3, 10, 40)), (5, (1, 32, 6, 11, 21)), (6, (2, 128, 3, 7, 9))])
+def test_emulated_fprop_bnrelu(kdw_emu, which, shape):
+    import ctypes
+
+    from oracle import dwconv_oracle as orc
+
+    N, C, H, W, D = shape
+    rng = np.random.default_rng(200 + which + C)
+    x = rng.standard_normal((N, H, W, D, C)).astype(np.float16)
+    w = ((rng.random((3, 3, 3, C)) * 2 - 1) / np.sqrt(27)).astype(np.float16)
+    scale = (0.5 + rng.random(C)).astype(np.float32)
+    shift = (rng.standard_normal(C) * 0.5 + 0.3).astype(np.float32)  # mostly positive: relu(shift) != 0 on padding
+    y = np.full_like(x, np.float16(777))
+    vp = ctypes.c_void_p
+    ref = orc.fprop_exact(orc.bnrelu_exact(x, scale, shift), w)
+    for grid in (3, 40):
+        g = kdw_emu.emu_fprop_bnrelu(which, x.ctypes.data_as(vp), scale.ctypes.data_as(vp), shift.ctypes.data_as(vp),
+                                     w.ctypes.data_as(vp), y.ctypes.data_as(vp), N, C, H, W, D, grid)
+        assert g > 0
+        # equal up to the rare double rounding inside the activation (see bnrelu_exact)
+        assert (y != ref).mean() < 1e-3
+        assert orc.allclose_two_stage(y, ref, rtol_strict=1e-4, atol_strict=1e-3, rtol_narrow=1e-3, atol_narrow=2e-3)
