@@ -774,8 +774,9 @@ def run_fused(args):
         # the prologue neighbour: y = DWConv(relu(x * scale + shift)); algorithmic bytes 4*V*C like the plain conv
         scale, shift = torch.rand(C, device=dev) + 0.5, torch.randn(C, device=dev) * 0.5
         ms_b = timeit(lambda: DWConvBNReLU(x, scale, shift, w), args.steps)
+        ms_h = timeit(lambda: DWConvBNReLU(x, scale, shift, w, PROLOGUE='float16'), args.steps)
         row['bnrelu'] = {'ms': round(ms_b, 4), 'gbs': round(4 * VOX * C / ms_b / 1e6, 1),
-                         'frac': round(4 * VOX * C / ms_b / 1e6 / peak, 4)}
+                         'frac': round(4 * VOX * C / ms_b / 1e6 / peak, 4), 'ms_packed_half_prologue': round(ms_h, 4)}
         if ref_ops is not None:
             try:
                 row['bnrelu']['reference_chain_ms'] = round(
@@ -797,7 +798,7 @@ def run_fused(args):
                                + ','.join(map(str, args.channels)), 'l2': 'inputs larger than L2'},
         'roofline': {'bound': 'hbm', 'kernel': 'fprop_addstats_kernel, all C', 'achieved': round(value, 1), 'peak': peak,
                      'peak_kind': peak_kind, 'unit': 'GB/s', 'frac': round(value / peak, 4), 'traffic': None},
-        'clocks': clocks, 'gpu_launches': 3 * len(args.channels) * args.steps, 'detail': detail,
+        'clocks': clocks, 'gpu_launches': 4 * len(args.channels) * args.steps, 'detail': detail,
         'device_status': _lib.device_status(),
     }), flush=True)
 

@@ -195,15 +195,19 @@ int kdw_fprop_addstats_f16(const void* x, const void* weight, const void* residu
  *   y = DWConv(relu(x * scale[c] + shift[c]), weight)
  * i.e. the reference's ApplyBNReLU(x, scale, shift) (kerops/ops/bnrelu.py:11-43; fp32 x*w+b, max 0, stored as fp16)
  * followed by DWConv (kerops/ops/conv/dwconv.py:25-63), without writing and re-reading the activated tensor.  The
- * zero padding of the convolution applies to the activated tensor.  KDW_ACC_F32 arithmetic.  C a power of two
- * >= 8; scale, shift fp32 [C]; x, y as for kdw_fprop_f16.  tune 0 = built-in choice,
- * 1..kdw_fprop_bnrelu_variants() = explicit tile.
+ * zero padding of the convolution applies to the activated tensor.  The convolution itself uses KDW_ACC_F32
+ * arithmetic.  C a power of two >= 8; scale, shift fp32 [C]; x, y as for kdw_fprop_f16.
+ *   prologue_type  KDW_ACC_F32: activation computed in fp32 from the fp32 scale / shift and rounded to fp16 - the
+ *                  reference operator's arithmetic;  KDW_ACC_F16: scale and shift rounded to fp16, activation one
+ *                  packed-half fused multiply-add with ReLU (single rounding) - faster, differs from the fp32 form
+ *                  only through the rounding of scale and shift
+ *   tune           0 = built-in choice, 1..kdw_fprop_bnrelu_variants() = explicit tile
  */
 int kdw_fprop_bnrelu_variants(void);
 int kdw_fprop_bnrelu_f16(const void* x, const float* scale, const float* shift, const void* weight, void* y, int64_t N,
                          int64_t C, int64_t H, int64_t W, int64_t D, int64_t x_strideN, int64_t x_strideH,
-                         int64_t x_strideW, int64_t y_strideN, int64_t y_strideH, int64_t y_strideW, int tune,
-                         void* stream);
+                         int64_t x_strideW, int64_t y_strideN, int64_t y_strideH, int64_t y_strideW,
+                         int prologue_type, int tune, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,9 +1,9 @@
 // Forward pass with a fused prologue: y = DWConv(relu(x * scale[c] + shift[c]), weight) - the reference's
 // ApplyBNReLU (kerops/ops/bnrelu.py:11-43, kerops/kernels/bnrelu.py:5-31) followed by DWConv, without writing
-// and re-reading the activated tensor.  Same pipeline as fprop_tma_kernel (dwconv_fprop.cu); after a stage has
-// landed the consumer threads first rewrite it in place (bnrelu_stage: only the part inside the volume - the
-// convolution pads the ACTIVATED tensor with zeros, so the TMA's zero fill must survive), meet at a named
-// barrier, and then run the usual step on it.
+// and re-reading the activated tensor.  Same pipeline as fprop_tma_kernel (dwconv_fprop.cu); the step activates
+// every value as it reads it from the staged tile (fprop_step_f32_bnrelu).  The convolution pads the ACTIVATED
+// tensor with zeros: x is loaded with NaN as the out-of-bounds fill and max(NaN, 0) = 0 restores the padding
+// without masks.  (A cooperative in-place pass over the tile with a barrier per step was measured 20-40 % slower.)
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -15,24 +15,21 @@ namespace kdw {
 
 template <class Cfg>
 struct BCfg {
-    static constexpr int SS_BYTES = 2 * Cfg::CS * 4;  // scale and shift of the channel slice
-    static constexpr int SMEM = Cfg::ST * Cfg::IN_STRIDE + 2 * Cfg::NCW * Cfg::OUTW_BYTES + SS_BYTES + 16 * Cfg::ST + 128;
+    static constexpr int SMEM = Cfg::ST * Cfg::IN_STRIDE + 2 * Cfg::NCW * Cfg::OUTW_BYTES + 16 * Cfg::ST + 128;
 };
 
-template <class Cfg>
+template <class Cfg, int PRO>
 __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
     fprop_bnrelu_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
                         const __half* __restrict__ weight, const float* __restrict__ scale,
-                        const float* __restrict__ shift, const Sched s, const int C, const int H, const int W,
-                        const int D, int* status) {
+                        const float* __restrict__ shift, const Sched s, const int C, int* status) {
     using B = BCfg<Cfg>;
-    constexpr int M = Cfg::M, CP = Cfg::CP, ST = Cfg::ST, NCW = Cfg::NCW, CS = Cfg::CS;
+    constexpr int M = Cfg::M, CP = Cfg::CP, ST = Cfg::ST, NCW = Cfg::NCW;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
     unsigned char* in_base = smem;
     unsigned char* out_base = smem + ST * Cfg::IN_STRIDE;
-    float* ss = reinterpret_cast<float*>(out_base + 2 * NCW * Cfg::OUTW_BYTES);
-    const uint32_t full0 = smem_u32(out_base + 2 * NCW * Cfg::OUTW_BYTES + B::SS_BYTES);
+    const uint32_t full0 = smem_u32(out_base + 2 * NCW * Cfg::OUTW_BYTES);
     const uint32_t empty0 = full0 + 8 * ST;
 
     const int tid = threadIdx.x;
@@ -87,8 +84,7 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
         for (int i = 0; i < CP; ++i) P1[m][i] = P2[m][i] = make_float2(0.f, 0.f);
 
     uint32_t ci = 0, oc = 0;
-    int cur_c0 = -1;
-    int w_lo = 0, w_hi = 0, d_lo = 0, d_hi = 0;  // part of the staged tile that lies inside the volume
+    float2 sc[CP], sh[CP];  // scale / shift of this thread's channels
     while (it.active) {
         const int q = it.q;
         if (q == it.g.hb - 1) {  // new segment
@@ -98,34 +94,20 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
 #pragma unroll
                 for (int i = 0; i < CP; ++i)
                     wgt[k][i] = *reinterpret_cast<const __half2*>(wp + (size_t)k * C + 2 * i);
-            if (it.g.c0 != cur_c0) {
-                // every consumer thread has passed the barrier of the previous step, so nobody still reads ss
-                cur_c0 = it.g.c0;
-                for (int c = tid; c < CS; c += Cfg::NT) {
-                    ss[c] = scale[cur_c0 + c];
-                    ss[CS + c] = shift[cur_c0 + c];
-                }
-                named_barrier_sync(3, Cfg::NT);
+            const int cb = it.g.c0 + th.cg * 2 * CP;
+#pragma unroll
+            for (int i = 0; i < CP; ++i) {
+                sc[i] = make_float2(scale[cb + 2 * i], scale[cb + 2 * i + 1]);
+                sh[i] = make_float2(shift[cb + 2 * i], shift[cb + 2 * i + 1]);
             }
-            w_lo = it.g.w0 >= 1 ? 0 : 1 - it.g.w0;
-            w_hi = W - it.g.w0 + 1;
-            w_hi = w_hi > Cfg::WT + 2 ? Cfg::WT + 2 : w_hi;
-            d_lo = it.g.d0 >= 1 ? 0 : 1 - it.g.d0;
-            d_hi = D - it.g.d0 + 1;
-            d_hi = d_hi > Cfg::DT + 2 ? Cfg::DT + 2 : d_hi;
         }
         const uint32_t st = ci % ST;
         const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u);
-        __half* tile = reinterpret_cast<__half*>(in_base + st * Cfg::IN_STRIDE);
-        if (ok && q >= 0 && q < H) {  // a plane outside the volume is padding and stays zero
-            bnrelu_stage<Cfg>(tile, ss, tid, w_lo, w_hi, d_lo, d_hi);
-            fence_proxy_async_smem();  // these writes are ordered before the TMA load that will reuse the stage
-        }
-        // the whole tile is activated before anybody convolves it; a timed-out wait stops all warps together
-        if (named_barrier_or(2, Cfg::NT, !ok)) {
-            if (tid == 0) atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
+        if (__any_sync(0xffffffffu, !ok)) {
+            if (lane == 0) atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
             break;
         }
+        const __half* tile = reinterpret_cast<const __half*>(in_base + st * Cfg::IN_STRIDE);
         const bool store = q - 1 >= it.g.hb;
         unsigned char* ob_bytes = my_out + (oc & 1u) * Cfg::OUTW_BYTES;
         if (store && lane == 0) tma_wait_read<1>();
@@ -133,9 +115,9 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
         const __half* in = tile + th.in_off;
         __half* ob = reinterpret_cast<__half*>(ob_bytes) + th.out_off;
         if (ci & 1u)
-            fprop_step_f32<Cfg>(in, ob, store, wgt, P2, P1);
+            fprop_step_f32_bnrelu<Cfg, PRO>(in, ob, store, wgt, sc, sh, P2, P1);
         else
-            fprop_step_f32<Cfg>(in, ob, store, wgt, P1, P2);
+            fprop_step_f32_bnrelu<Cfg, PRO>(in, ob, store, wgt, sc, sh, P1, P2);
         if (store) fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
@@ -161,12 +143,13 @@ struct BnReluArgs {
     cudaStream_t stream;
 };
 
-template <class Cfg>
+template <class Cfg, int PRO>
 static int launch_bnrelu(const BnReluArgs& a) {
     using B = BCfg<Cfg>;
     CUtensorMap tmx, tmy;
+    // out-of-bounds elements of x read as NaN: the activation turns them into the padding's zeros
     int rc = encode_volume_map(&tmx, a.x, a.N, a.C, a.H, a.W, a.D, a.xsN, a.xsH, a.xsW, Cfg::CS, Cfg::DT + 2,
-                               Cfg::WT + 2);
+                               Cfg::WT + 2, /*nan_fill=*/true);
     if (rc) return rc;
     rc = encode_volume_map(&tmy, a.y, a.N, a.C, a.H, a.W, a.D, a.ysN, a.ysH, a.ysW, Cfg::CS, Cfg::DPW, Cfg::M);
     if (rc) return rc;
@@ -174,7 +157,7 @@ static int launch_bnrelu(const BnReluArgs& a) {
         set_error("weight pointer must be 4-byte aligned");
         return KDW_ERR_ALIGN;
     }
-    auto kern = fprop_bnrelu_kernel<Cfg>;
+    auto kern = fprop_bnrelu_kernel<Cfg, PRO>;
     KDW_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, B::SMEM));
     int occ = 0, sms = 0;
     KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::NT + 32, B::SMEM));
@@ -189,8 +172,7 @@ static int launch_bnrelu(const BnReluArgs& a) {
     if (rc) return rc;
     Sched s;
     const int grid = make_sched(&s, a.N, a.C, a.W, a.D, 0, (int)a.H, Cfg::WT, Cfg::DT, Cfg::CS, sms * occ);
-    kern<<<grid, Cfg::NT + 32, B::SMEM, a.stream>>>(tmx, tmy, (const __half*)a.w, a.scale, a.shift, s, (int)a.C,
-                                                    (int)a.H, (int)a.W, (int)a.D, status);
+    kern<<<grid, Cfg::NT + 32, B::SMEM, a.stream>>>(tmx, tmy, (const __half*)a.w, a.scale, a.shift, s, (int)a.C, status);
     KDW_CUDA(cudaGetLastError());
     return 0;
 }
@@ -198,16 +180,20 @@ static int launch_bnrelu(const BnReluArgs& a) {
 typedef int (*BnReluLaunch)(const BnReluArgs&);
 struct BnReluVariant {
     int cs, dt, wt;
-    BnReluLaunch f;
+    BnReluLaunch f[2];  // indexed by the prologue arithmetic: KDW_ACC_F32 / KDW_ACC_F16
 };
+#define KDW_BNRELU_TILE(CS, DT, WT, M, CP, ST, MINB)                          \
+    {CS, DT, WT,                                                              \
+     {&launch_bnrelu<FCfg<CS, DT, WT, M, CP, ST, MINB>, 0>, &launch_bnrelu<FCfg<CS, DT, WT, M, CP, ST, MINB>, 1>}}
 static const BnReluVariant g_bnrelu_variants[] = {
-    {8, 64, 8, &launch_bnrelu<FCfg<8, 64, 8, 8, 1, 4, 2>>},    // C = 8
-    {16, 64, 8, &launch_bnrelu<FCfg<16, 64, 8, 8, 1, 3, 1>>},  // C = 16
-    {16, 32, 8, &launch_bnrelu<FCfg<16, 32, 8, 8, 1, 4, 2>>},
-    {32, 32, 8, &launch_bnrelu<FCfg<32, 32, 8, 8, 1, 3, 1>>},  // C = 32, 64
-    {32, 16, 8, &launch_bnrelu<FCfg<32, 16, 8, 8, 1, 4, 2>>},
-    {64, 8, 8, &launch_bnrelu<FCfg<64, 8, 8, 8, 1, 4, 2>>},    // C >= 128
+    KDW_BNRELU_TILE(8, 64, 8, 8, 1, 4, 2),   // C = 8
+    KDW_BNRELU_TILE(16, 64, 8, 8, 1, 3, 1),  // C = 16
+    KDW_BNRELU_TILE(16, 32, 8, 8, 1, 4, 2),
+    KDW_BNRELU_TILE(32, 32, 8, 8, 1, 3, 1),  // C = 32, 64
+    KDW_BNRELU_TILE(32, 16, 8, 8, 1, 4, 2),
+    KDW_BNRELU_TILE(64, 8, 8, 8, 1, 4, 2),   // C >= 128
 };
+#undef KDW_BNRELU_TILE
 static const int g_n_bnrelu_variants = (int)(sizeof(g_bnrelu_variants) / sizeof(g_bnrelu_variants[0]));
 
 static int auto_bnrelu_variant(int64_t C, int64_t D) {
@@ -225,8 +211,8 @@ int kdw_fprop_bnrelu_variants(void) { return kdw::g_n_bnrelu_variants; }
 
 int kdw_fprop_bnrelu_f16(const void* x, const float* scale, const float* shift, const void* weight, void* y, int64_t N,
                          int64_t C, int64_t H, int64_t W, int64_t D, int64_t x_strideN, int64_t x_strideH,
-                         int64_t x_strideW, int64_t y_strideN, int64_t y_strideH, int64_t y_strideW, int tune,
-                         void* stream) {
+                         int64_t x_strideW, int64_t y_strideN, int64_t y_strideH, int64_t y_strideW,
+                         int prologue_type, int tune, void* stream) {
     using namespace kdw;
     if (!x || !scale || !shift || !weight || !y) {
         set_error("fprop_bnrelu: null pointer");
@@ -239,6 +225,10 @@ int kdw_fprop_bnrelu_f16(const void* x, const float* scale, const float* shift, 
     }
     if (H > 0x7fffffff || W > 0x7fffffff || D > 0x7fffffff || N > 0x7fffffff || C > 0x7fffffff) {
         set_error("fprop_bnrelu: extent does not fit in 32 bits");
+        return KDW_ERR_ARG;
+    }
+    if (prologue_type != KDW_ACC_F32 && prologue_type != KDW_ACC_F16) {
+        set_error("fprop_bnrelu: prologue_type must be KDW_ACC_F32 or KDW_ACC_F16");
         return KDW_ERR_ARG;
     }
     if (tune < 0 || tune > g_n_bnrelu_variants) {
@@ -254,7 +244,7 @@ int kdw_fprop_bnrelu_f16(const void* x, const float* scale, const float* shift, 
     }
     BnReluArgs a{x, weight, scale, shift, y, N, C, H, W, D, x_strideN, x_strideH, x_strideW, y_strideN, y_strideH,
                  y_strideW, (cudaStream_t)stream};
-    return v.f(a);
+    return v.f[prologue_type](a);
 }
 
 }  // extern "C"

@@ -251,32 +251,97 @@ KDW_HD void fprop_step_f32_addstats(const __half* __restrict__ in, const __half*
     }
 }
 
-// Prologue for the fused BN-affine + ReLU: x' = fp16(max(fma(float(x), scale[c], shift[c]), 0)) applied IN PLACE
-// to the part of a staged input tile [(WT+2)][(DT+2)][CS] that lies inside the volume (lines [w_lo, w_hi), depth
-// positions [d_lo, d_hi) of the tile; everything else is the zero padding of the convolution and must stay
-// zero).  Thread `tid` of the NT consumer threads handles items tid, tid + NT, ...; an item is 8 channels of
-// one voxel (one 16-byte access).  `ss` = scale[CS] then shift[CS] of the CTA's channel slice.  Same arithmetic
-// as the reference's separate operator (kerops/kernels/bnrelu.py:25-31).
-template <class Cfg>
-KDW_HD void bnrelu_stage(__half* tile, const float* ss, int tid, int w_lo, int w_hi, int d_lo, int d_hi) {
-    constexpr int CS = Cfg::CS, G = CS / 8, ROW = Cfg::DT + 2, NV = (Cfg::WT + 2) * ROW;
-    static_assert(Cfg::NT % G == 0, "a thread keeps its channel group");
-    const int cg = tid % G;
-    for (int v = tid / G; v < NV; v += Cfg::NT / G) {
-        const int line = v / ROW, dd = v - line * ROW;
-        if (line < w_lo || line >= w_hi || dd < d_lo || dd >= d_hi) continue;
-        __half* p = tile + (v * CS + cg * 8);
-        __half2 h[4];
-        lds_h2<4>(h, p);
+// fprop_step_f32 with the BN-affine + ReLU applied to every value as it is read from the staged tile:
+// x' = fp16(max(x * sc + sh, 0)).  The convolution pads the ACTIVATED tensor with zeros, so the positions outside
+// the volume must give 0, not relu(sh): the tile is loaded with NaN as the out-of-bounds fill, NaN survives the
+// multiply-add, and the maximum with 0 returns the operand that is a number - no masks, no bounds tests.  Each
+// thread needs only the scale / shift of its own CP channel pairs.  A value is activated once per thread that
+// reads it (about twice per element), which costs less than a cooperative pass over the tile with a CTA-wide
+// barrier per step.
+//
+// PRO = 0: the multiply-add is computed in fp32 from fp32 scale / shift and rounded to fp16, like the reference's
+//          operator (kerops/kernels/bnrelu.py:25-31).
+// PRO = 1: scale and shift are rounded to fp16 and the multiply-add is ONE packed-half FMA per channel pair
+//          (a single rounding), followed by the packed-half maximum.
+template <class Cfg, int PRO>
+KDW_HD void fprop_step_f32_bnrelu(const __half* __restrict__ in, __half* __restrict__ ob, bool store,
+                                  const __half2 (&wgt)[27][Cfg::CP], const float2 (&sc)[Cfg::CP],
+                                  const float2 (&sh)[Cfg::CP], float2 (&A)[Cfg::M][Cfg::CP],
+                                  float2 (&B)[Cfg::M][Cfg::CP]) {
+    constexpr int CS = Cfg::CS, DT = Cfg::DT, M = Cfg::M, CP = Cfg::CP, DPW = Cfg::DPW;
+    float2 T[3][CP];
+    __half2 sc16[CP], sh16[CP];
+    if (PRO == 1) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int c = cg * 8 + 2 * i;
-            float2 f = __half22float2(h[i]);
-            f.x = fmaxf(fmaf(f.x, ss[c], ss[CS + c]), 0.f);
-            f.y = fmaxf(fmaf(f.y, ss[c + 1], ss[CS + c + 1]), 0.f);
-            h[i] = __float22half2_rn(f);
+        for (int i = 0; i < CP; ++i) {
+            sc16[i] = __float22half2_rn(sc[i]);
+            sh16[i] = __float22half2_rn(sh[i]);
         }
-        sts_h2<4>(p, h);
+    }
+#pragma unroll
+    for (int j = 0; j < M + 2; ++j) {
+        __half2 xv[3][CP];
+#pragma unroll
+        for (int t = 0; t < 3; ++t) {
+            lds_h2<CP>(xv[t], in + (j * (DT + 2) + t) * CS);
+#pragma unroll
+            for (int i = 0; i < CP; ++i) {
+                if (PRO == 1) {
+                    xv[t][i] = h2_relu_nan0(h2_fma(xv[t][i], sc16[i], sh16[i]));
+                } else {
+                    float2 f = __half22float2(xv[t][i]);
+                    f.x = fmaxf(fmaf(f.x, sc[i].x, sh[i].x), 0.f);  // fmaxf(NaN, 0) = 0
+                    f.y = fmaxf(fmaf(f.y, sc[i].y, sh[i].y), 0.f);
+                    xv[t][i] = __float22half2_rn(f);
+                }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < 3; ++b) {
+            const int m = j - b;
+            if (m < 0 || m >= M) continue;
+#pragma unroll
+            for (int i = 0; i < CP; ++i) {
+                float2 f = B[m][i];
+                f = fma_h2_f2(wgt[(6 + b) * 3 + 0][i], xv[0][i], f);
+                f = fma_h2_f2(wgt[(6 + b) * 3 + 1][i], xv[1][i], f);
+                B[m][i] = fma_h2_f2(wgt[(6 + b) * 3 + 2][i], xv[2][i], f);
+            }
+        }
+        if (j >= 2 && store) {
+            __half2 o[CP];
+#pragma unroll
+            for (int i = 0; i < CP; ++i) o[i] = __float22half2_rn(B[j - 2][i]);
+            sts_h2<CP>(ob + ((j - 2) * DPW) * CS, o);
+        }
+#pragma unroll
+        for (int b = 0; b < 3; ++b) {
+            const int m = j - b;
+            if (m < 0 || m >= M) continue;
+#pragma unroll
+            for (int i = 0; i < CP; ++i) {
+                float2 f = A[m][i];
+                f = fma_h2_f2(wgt[(3 + b) * 3 + 0][i], xv[0][i], f);
+                f = fma_h2_f2(wgt[(3 + b) * 3 + 1][i], xv[1][i], f);
+                A[m][i] = fma_h2_f2(wgt[(3 + b) * 3 + 2][i], xv[2][i], f);
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < 3; ++b) {
+            const int m = j - b;
+            if (m < 0 || m >= M) continue;
+#pragma unroll
+            for (int i = 0; i < CP; ++i) {
+                float2 f = (b == 0) ? make_float2(0.f, 0.f) : T[m % 3][i];
+                f = fma_h2_f2(wgt[b * 3 + 0][i], xv[0][i], f);
+                f = fma_h2_f2(wgt[b * 3 + 1][i], xv[1][i], f);
+                f = fma_h2_f2(wgt[b * 3 + 2][i], xv[2][i], f);
+                if (b == 2)
+                    B[m][i] = f;
+                else
+                    T[m % 3][i] = f;
+            }
+        }
     }
 }
 

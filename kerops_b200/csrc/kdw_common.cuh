@@ -41,7 +41,8 @@ int cuda_fail(cudaError_t e, const char* what);  // records the message, returns
 // strides (1, C, strideW, strideH, strideN), box (boxC, boxD, boxW, 1, 1), zero fill for
 // out-of-bounds elements.  Returns 0 or a negative argument error / positive driver error.
 int encode_volume_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
-                      int64_t strideN, int64_t strideH, int64_t strideW, int boxC, int boxD, int boxW);
+                      int64_t strideN, int64_t strideH, int64_t strideW, int boxC, int boxD, int boxW,
+                      bool nan_fill = false);  // nan_fill: out-of-bounds elements read as NaN instead of zero
 
 // As encode_volume_map with the D and C axes merged (see kdw_host.cu).
 int encode_merged_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
@@ -283,6 +284,15 @@ KDW_HD __half2 h2_add(__half2 a, __half2 b) {
 #else
     const float2 fa = __half22float2(a), fb = __half22float2(b);
     return __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);  // the fp32 sum of two fp16 values is exact
+#endif
+}
+// max(a, 0) per lane; a NaN lane gives 0 (the maximum returns the operand that is a number).
+KDW_HD __half2 h2_relu_nan0(__half2 a) {
+#ifdef __CUDA_ARCH__
+    return __hmax2(a, __float2half2_rn(0.f));
+#else
+    const float2 f = __half22float2(a);
+    return __floats2half2_rn(f.x > 0.f ? f.x : 0.f, f.y > 0.f ? f.y : 0.f);  // NaN > 0 is false
 #endif
 }
 KDW_HD __half2 h2_fma(__half2 a, __half2 b, __half2 c) {

@@ -61,7 +61,7 @@ static int get_encode_fn(EncodeTiledFn* out) {
 }
 
 int encode_volume_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
-                      int64_t strideN, int64_t strideH, int64_t strideW, int boxC, int boxD, int boxW) {
+                      int64_t strideN, int64_t strideH, int64_t strideW, int boxC, int boxD, int boxW, bool nan_fill) {
     EncodeTiledFn fn;
     int rc = get_encode_fn(&fn);
     if (rc) return rc;
@@ -84,7 +84,7 @@ int encode_volume_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, 
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    nan_fill ? CU_TENSOR_MAP_FLOAT_OOB_FILL_NAN_REQUEST_ZERO_FMA : CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed with CUresult %d (dims C=%lld D=%lld W=%lld H=%lld N=%lld)", (int)r,
                   (long long)C, (long long)D, (long long)W, (long long)H, (long long)N);

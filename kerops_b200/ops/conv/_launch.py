@@ -111,8 +111,8 @@ def fprop_addstats(x, weight, residual, y, tune=0):
     return mean, sqmean
 
 
-def fprop_bnrelu(x, scale, shift, weight, y, tune=0):
-    """Enqueues y = conv(relu(x * scale + shift)) (scale, shift fp32 [C])."""
+def fprop_bnrelu(x, scale, shift, weight, y, prologue='float32', tune=0):
+    """Enqueues y = conv(relu(x * scale + shift)) (scale, shift fp32 [C]; prologue arithmetic 'float32' | 'float16')."""
     lib = _lib.load()
     N, C, H, W, D = x.shape
     xs, ys = volume_strides(x), volume_strides(y)
@@ -120,7 +120,7 @@ def fprop_bnrelu(x, scale, shift, weight, y, tune=0):
     with torch.cuda.device(x.device):
         rc = lib.kdw_fprop_bnrelu_f16(
             x.data_ptr(), scale.data_ptr(), shift.data_ptr(), weight.data_ptr(), y.data_ptr(), N, C, H, W, D, xs[0],
-            xs[1], xs[2], ys[0], ys[1], ys[2], tune, _stream_ptr(x.device),
+            xs[1], xs[2], ys[0], ys[1], ys[2], ACC_TYPES[prologue], tune, _stream_ptr(x.device),
         )
     _lib.check(rc)
     return y

@@ -22,7 +22,7 @@ struct Vol {
 
 // box (CS, BD, BW) at (c0, d0, w0) of plane h of sample n; zero outside the volume
 static void emu_tma_load(__half* dst, const __half* src, const Vol& v, int CS, int BD, int BW, int c0, int d0, int w0,
-                         int h, int n) {
+                         int h, int n, bool nan_fill = false) {
     for (int wj = 0; wj < BW; ++wj)
         for (int dd = 0; dd < BD; ++dd)
             for (int c = 0; c < CS; ++c) {
@@ -30,7 +30,7 @@ static void emu_tma_load(__half* dst, const __half* src, const Vol& v, int CS, i
                 const bool in = h >= 0 && h < v.H && w >= 0 && w < v.W && d >= 0 && d < v.D && ch < v.C && n < v.N;
                 dst[(wj * BD + dd) * CS + c] =
                     in ? src[n * v.sN + (int64_t)h * v.sH + (int64_t)w * v.sW + (int64_t)d * v.C + ch]
-                       : __float2half(0.f);
+                       : (nan_fill ? __float2half(nanf("")) : __float2half(0.f));
             }
 }
 static void emu_tma_store(__half* dst, const __half* tile, const Vol& v, int CS, int BD, int BW, int c0, int d0, int w0,
@@ -269,22 +269,21 @@ static int emu_addstats_cfg(const __half* x, const __half* w, const __half* r, _
     return grid;
 }
 
-// The fused BN-affine + ReLU prologue kernel (dwconv_fprop_bnrelu.cu): the staged tile is activated in place by
-// the consumer threads (bnrelu_stage), then convolved as usual.
+// The fused BN-affine + ReLU prologue kernel (dwconv_fprop_bnrelu.cu): every thread activates the values it reads
+// (fprop_step_f32_bnrelu) with its own channels' scale / shift; the tile's out-of-bounds fill is NaN.
 template <class Cfg>
 static int emu_bnrelu_cfg(const __half* x, const float* scale, const float* shift, const __half* w, __half* y, Vol v,
                           int grid_target) {
     constexpr int M = Cfg::M, CP = Cfg::CP, CS = Cfg::CS;
     struct TState {
         __half2 wgt[27][CP];
-        float2 P1[M][CP], P2[M][CP];
+        float2 P1[M][CP], P2[M][CP], sc[CP], sh[CP];
     };
     Sched s;
     const int grid = make_sched(&s, v.N, v.C, v.W, v.D, 0, (int)v.H, Cfg::WT, Cfg::DT, Cfg::CS, grid_target);
     std::vector<__half> stage(Cfg::IN_BYTES / 2);
     std::vector<__half> out((size_t)Cfg::NCW * Cfg::OUTW_BYTES / 2);
     std::vector<TState> ts(Cfg::NT);
-    std::vector<float> ss(2 * CS);
     for (int blk = 0; blk < grid; ++blk) {
         memset(ts.data(), 0, sizeof(TState) * ts.size());
         StepIter cons;
@@ -293,17 +292,7 @@ static int emu_bnrelu_cfg(const __half* x, const float* scale, const float* shif
         while (cons.active) {
             const int q = cons.q;
             const Seg& g = cons.g;
-            for (int c = 0; c < CS; ++c) {
-                ss[c] = scale[g.c0 + c];
-                ss[CS + c] = shift[g.c0 + c];
-            }
-            int w_lo = g.w0 >= 1 ? 0 : 1 - g.w0, w_hi = (int)v.W - g.w0 + 1;
-            int d_lo = g.d0 >= 1 ? 0 : 1 - g.d0, d_hi = (int)v.D - g.d0 + 1;
-            w_hi = w_hi > Cfg::WT + 2 ? Cfg::WT + 2 : w_hi;
-            d_hi = d_hi > Cfg::DT + 2 ? Cfg::DT + 2 : d_hi;
-            emu_tma_load(stage.data(), x, v, CS, Cfg::DT + 2, Cfg::WT + 2, g.c0, g.d0 - 1, g.w0 - 1, q, g.n);
-            if (q >= 0 && q < v.H)
-                for (int tid = 0; tid < Cfg::NT; ++tid) bnrelu_stage<Cfg>(stage.data(), ss.data(), tid, w_lo, w_hi, d_lo, d_hi);
+            emu_tma_load(stage.data(), x, v, CS, Cfg::DT + 2, Cfg::WT + 2, g.c0, g.d0 - 1, g.w0 - 1, q, g.n, true);
             const bool store = q - 1 >= g.hb;
             for (int tid = 0; tid < Cfg::NT; ++tid) {
                 TState& t = ts[tid];
@@ -312,13 +301,18 @@ static int emu_bnrelu_cfg(const __half* x, const float* scale, const float* shif
                     const __half* wp = w + g.c0 + th.cg * 2 * CP;
                     for (int k = 0; k < 27; ++k)
                         for (int i = 0; i < CP; ++i) t.wgt[k][i] = *reinterpret_cast<const __half2*>(wp + (size_t)k * v.C + 2 * i);
+                    const int cb = g.c0 + th.cg * 2 * CP;
+                    for (int i = 0; i < CP; ++i) {
+                        t.sc[i] = make_float2(scale[cb + 2 * i], scale[cb + 2 * i + 1]);
+                        t.sh[i] = make_float2(shift[cb + 2 * i], shift[cb + 2 * i + 1]);
+                    }
                 }
                 const __half* in = stage.data() + th.in_off;
                 __half* ob = out.data() + (size_t)(tid / 32) * (Cfg::OUTW_BYTES / 2) + th.out_off;
                 if (ci & 1u)
-                    fprop_step_f32<Cfg>(in, ob, store, t.wgt, t.P2, t.P1);
+                    fprop_step_f32_bnrelu<Cfg, 0>(in, ob, store, t.wgt, t.sc, t.sh, t.P2, t.P1);
                 else
-                    fprop_step_f32<Cfg>(in, ob, store, t.wgt, t.P1, t.P2);
+                    fprop_step_f32_bnrelu<Cfg, 0>(in, ob, store, t.wgt, t.sc, t.sh, t.P1, t.P2);
             }
             if (store) {
                 for (int wp = 0; wp < Cfg::NCW; ++wp) {

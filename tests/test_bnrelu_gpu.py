@@ -99,3 +99,25 @@ def test_against_reference_two_operator_chain():
         y = DWConvBNReLU(x, scale, shift, w)
         assert allclose_two_stage(ref, y, rtol_strict=1e-4, atol_strict=1e-3, rtol_narrow=1e-3, atol_narrow=4e-3,
                                   debug_info='print')
+
+
+@pytest.mark.parametrize('shape', [(2, 8, 5, 13, 70), (1, 16, 7, 37, 33), (1, 32, 6, 20, 128), (1, 64, 9, 21, 40),
+                                   (1, 128, 5, 18, 17)])
+def test_packed_half_prologue(shape):
+    """PROLOGUE='float16': scale and shift rounded to fp16, activation = one fused multiply-add with ReLU rounded
+    once to fp16; equal to that arithmetic done in fp64 and, loosely, to the fp32 prologue."""
+    from kerops_b200 import _lib
+    from kerops_b200.ops.conv import DWConv, DWConvBNReLU
+
+    N, C, H, W, D = shape
+    x, scale, shift, w = _inputs(N, C, H, W, D, seed=2 * C + D)
+    y = DWConvBNReLU(x, scale, shift, w, PROLOGUE='float16')
+    s16 = scale.half().view(1, -1, 1, 1, 1).double()
+    b16 = shift.half().view(1, -1, 1, 1, 1).double()
+    act = torch.clamp_min(x.double() * s16 + b16, 0).half().contiguous(memory_format=torch.channels_last_3d)
+    ref = DWConv(act, w, num_warps=8, D_block=8)
+    assert float((y != ref).float().mean()) < 1e-4
+    torch.testing.assert_close(y.float(), ref.float(), rtol=1e-3, atol=2e-3)
+    y32 = DWConvBNReLU(x, scale, shift, w)
+    torch.testing.assert_close(y.float(), y32.float(), rtol=1e-2, atol=1e-2)  # only scale / shift rounding differs
+    assert _lib.device_status() == 0
