@@ -87,7 +87,7 @@ def make_inputs(seed, N, C, s1, s2, s3):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument('--reference', default='/root/reference')
+    ap.add_argument('--reference', required=True, help='path of a kerops checkout')
     ap.add_argument('--out', default=os.path.dirname(os.path.abspath(__file__)))
     ap.add_argument('--only', default='', help='comma-separated case names (default: all)')
     args = ap.parse_args()

@@ -1,5 +1,5 @@
 """Side by side with the reference itself on the GPU: the unmodified kerops package, installed offline under
-baseline/_ref, JIT-compiles its Triton kernels for this GPU; our operators must agree with its
+baseline/_ref (pip install --no-index --no-deps --target baseline/_ref <kerops checkout>), JIT-compiles its Triton kernels for this GPU; our operators must agree with its
 outputs within the tolerances of the reference's own tests (tests/ops/test_conv.py:28-36, 74-82), checked with
 the reference's own comparison functions (kerops/utils.py).  Skipped when the install is absent."""
 import glob
