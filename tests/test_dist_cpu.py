@@ -64,6 +64,21 @@ def _worker(rank, world, port, shape, out_dir):
         # ---- sample-sharded step: rank r takes samples r::world
         ys, dws = kd.sample_sharded_step(x[rank::world].contiguous(memory_format=torch.channels_last_3d), w,
                                          grad[rank::world].contiguous(memory_format=torch.channels_last_3d), ops=ops)
+        # ---- the same two reductions through a caller-supplied reducer (the place GradPushAllReduce plugs in)
+        calls = []
+
+        def reducer(t):
+            calls.append(t.numel())
+            dist.all_reduce(t)
+            return t
+
+        xh3 = kd.alloc_halo_volume(N, C, he - hb, W, D, 'cpu')
+        xh3[:, :, 1:-1] = x[:, :, hb:he]
+        dw_r = kd.hsharded_wgrad(xh3, gl, ops=ops, reducer=reducer)
+        _, dws_r = kd.sample_sharded_step(x[rank::world].contiguous(memory_format=torch.channels_last_3d), w,
+                                          grad[rank::world].contiguous(memory_format=torch.channels_last_3d), ops=ops,
+                                          reducer=reducer)
+        assert calls == [27 * C, 27 * C] and torch.equal(dw_r, dw) and torch.equal(dws_r, dws)
         torch.save({'hb': hb, 'he': he, 'y': y.contiguous(), 'dw': dw, 'ys': ys.contiguous(), 'dws': dws,
                     'halo_lo': xh[:, :, 0].clone(), 'halo_hi': xh[:, :, -1].clone()},
                    os.path.join(out_dir, f'rank{rank}.pt'))
