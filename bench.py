@@ -8,15 +8,22 @@ A STEP is one pass over the headline sweep: for every C in {8, 16, 32, 64, 128},
 (1, C, 350, 350, 128) fp16 channels_last_3d volume followed by DWConvWGRAD of the same volume against
 an independent gradient (seeded synthetic N(0,1) data, weights U(+-1/sqrt(27))).  With N GPUs every rank
 runs the sweep on its own sample (weak scaling) and the fp32 [27][C] weight gradients of a step are summed
-with one NCCL all-reduce - the only exchange the sample-sharded path has.
+once per step - by the library's own push/flag/sum kernel over peer memory (--allreduce push, the default) or by
+NCCL - the only exchange the sample-sharded path has.
 
 `value` = algorithmic bytes of all ranks / max-over-ranks device time; algorithmic bytes are 4*V*C per
 operator call (read x + write y, or read x + read grad; V = 350*350*128 voxels).
 The JSON line also carries: `roofline` (the kernel with the largest share of the timed region, bytes /
-CUDA-event time against the measured HBM peak), `detail` (per operator and C: ms, GB/s, fraction),
-`e2e` (the same sweep through the host-buffer operators, host<->device copies inside the timed region),
-`cpu_baseline` (torch CPU depthwise conv3d, the check the reference's tests use, on a bounded sample),
-`clocks` (SM clock and throttle reasons sampled through NVML during the timed region).
+CUDA-event time against the measured HBM peak), `detail` (per operator and C: ms mean / median / min, GB/s,
+fraction, ratio to torch.clone), `e2e` (the same sweep through the host-buffer operator DWConvStepHost,
+host<->device copies inside the timed region), `cpu_baseline` (torch CPU depthwise conv3d, the check the
+reference's tests use, on a bounded sample), `clocks` (SM clock and throttle reasons sampled through NVML during
+the timed region), and at one GPU `reference_triton_on_this_gpu` (the reference's own Triton kernels from
+baseline/_ref timed on the same tensors).
+
+Other workloads (--workload): `dshard` = one (1,128,1400,350,128) volume sharded along H over the ranks with halo
+exchange (strong scaling); `dpstep` = a batch of 8 x (32,350,350,128) samples split by sample (strong scaling);
+`fused` = DWConvAddStats and DWConvBNReLU against the unfused and the reference two-operator chains (one GPU).
 
 `--impl reference` times the CPU arm alone (rank 0 only): torch conv3d(groups=C) forward + weight
 gradient on the host cores, one (1, 8, 350, 350, 128) volume per step.
