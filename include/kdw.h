@@ -57,6 +57,15 @@ const char* kdw_last_error(void);
 int kdw_device_status(int* status);
 
 /*
+ * Test hook for the kernels' bounded waits (no reference counterpart; process-wide, not thread-safe, meant for
+ * test programs only).  limit_ns: time after which a wait on a TMA barrier inside a kernel gives up (default
+ * 2 s).  stop_after >= 0: the load warp of every TMA kernel stops after that many plane loads, so the next wait of
+ * the compute warps runs out, the kernel raises status 1 (kdw_device_status) and returns with its output
+ * incomplete - nothing faults and the context stays usable.  stop_after < 0 (default) switches the hook off.
+ */
+int kdw_test_wait_limits(int64_t limit_ns, int stop_after);
+
+/*
  * Forward pass.  Replaces the launch loop of kerops/ops/conv/dwconv.py:47-61 (one launch per sample of
  * _DWConv_cl3d_impl) by one launch over the whole batch.
  *   x, y      fp16 volumes (N, C, H, W, D), strides in elements; y may have different N/H/W strides

@@ -18,6 +18,7 @@ SIGNATURES = {
     'kdw_version': (_int, []),
     'kdw_last_error': (ctypes.c_char_p, []),
     'kdw_device_status': (_int, [ctypes.POINTER(_int)]),
+    'kdw_test_wait_limits': (_int, [_i64, _int]),
     'kdw_fprop_f16': (_int, [_ptr, _ptr, _ptr] + [_i64] * 5 + [_i64] * 6 + [_int, _int, _ptr]),
     'kdw_fprop_f16_range': (
         _int,

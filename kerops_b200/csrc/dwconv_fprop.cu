@@ -76,7 +76,8 @@ __global__ void __launch_bounds__(256) fprop_plain_kernel(const __half* __restri
 template <class Cfg, int MODE>
 __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
     fprop_tma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
-                     const __half* __restrict__ weight, const Sched s, const int C, const int y_h0, int* status) {
+                     const __half* __restrict__ weight, const Sched s, const int C, const int y_h0, int* status,
+                     const WaitTest wt) {
     constexpr int M = Cfg::M, CP = Cfg::CP, ST = Cfg::ST, NCW = Cfg::NCW;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
@@ -106,8 +107,9 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
         uint32_t pi = 0;
         bool ok = true;
         while (it.active && ok) {
+            if (wt.stop_after >= 0 && (int)pi >= wt.stop_after) return;  // test hook: the consumers' wait runs out
             const uint32_t st = pi % ST;
-            if (pi >= ST) ok = mbar_wait_bounded(empty0 + 8 * st, ((pi / ST) & 1u) ^ 1u);  // consumers released it
+            if (pi >= ST) ok = mbar_wait_bounded(empty0 + 8 * st, ((pi / ST) & 1u) ^ 1u, wt.limit_ns);  // released
             if (!ok) break;
             mbar_expect_tx(full0 + 8 * st, Cfg::IN_BYTES);
             tma_load_5d(status, smem_u32(in_base + st * Cfg::IN_STRIDE), &tmx, full0 + 8 * st, it.g.c0, it.g.d0 - 1,
@@ -119,7 +121,8 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
             atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
             // loads already issued still target this CTA's shared memory: give them a bounded chance to land
             const uint32_t first = pi > ST ? pi - ST : 0;
-            for (uint32_t k = first; k < pi; ++k) (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u);
+            for (uint32_t k = first; k < pi; ++k)
+                (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u, wt.limit_ns);
         }
         return;
     }
@@ -154,8 +157,8 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
                     wgt[k][i] = *reinterpret_cast<const __half2*>(wp + (size_t)k * C + 2 * i);
         }
         const uint32_t st = ci % ST;
-        const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u);
-        if (__any_sync(0xffffffffu, !ok)) {
+        const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u, wt.limit_ns);
+        if (__any_sync(0xffffffffu, !ok)) {  // this warp leaves; the other warps' waits are bounded too
             if (lane == 0) atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
             break;
         }
@@ -215,21 +218,17 @@ static int launch_fprop_tma(const FpropArgs& a) {
         return KDW_ERR_ALIGN;
     }
     auto kern = fprop_tma_kernel<Cfg, MODE>;
-    KDW_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+    static KernelSetup setup;  // one per kernel instantiation
     int occ = 0, sms = 0;
-    KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::NT + 32, Cfg::SMEM));
-    if (occ < 1) {
-        set_error("fprop kernel variant does not fit on this device");
-        return KDW_ERR_TUNE;
-    }
-    rc = device_sm_count(&sms);
+    rc = setup.get((const void*)kern, Cfg::NT + 32, Cfg::SMEM, &sms, &occ);
     if (rc) return rc;
     int* status = nullptr;
     rc = status_ptr(&status);
     if (rc) return rc;
     Sched s;
     const int grid = make_sched(&s, a.N, a.C, a.W, a.D, a.h_begin, a.h_end, Cfg::WT, Cfg::DT, Cfg::CS, sms * occ);
-    kern<<<grid, Cfg::NT + 32, Cfg::SMEM, a.stream>>>(tmx, tmy, (const __half*)a.w, s, (int)a.C, a.y_h0, status);
+    kern<<<grid, Cfg::NT + 32, Cfg::SMEM, a.stream>>>(tmx, tmy, (const __half*)a.w, s, (int)a.C, a.y_h0, status,
+                                                      wait_test());
     KDW_CUDA(cudaGetLastError());
     return 0;
 }
@@ -252,6 +251,7 @@ static const int g_n_table_variants = (int)(sizeof(g_fprop_variants) / sizeof(g_
 
 // tensor-core variants (dwconv_fprop_mma.cu) are numbered after the table; they implement KDW_ACC_F32 only
 int fprop_mma_variants();
+int fprop_mma_variant_channels(int which);
 int launch_fprop_mma_variant(int which, const void* x, const void* w, void* y, int64_t N, int64_t C, int64_t Hx,
                              int64_t W, int64_t D, int64_t xsN, int64_t xsH, int64_t xsW, int64_t Hy, int64_t ysN,
                              int64_t ysH, int64_t ysW, int h_begin, int h_end, int y_h0, cudaStream_t stream);
@@ -372,7 +372,7 @@ int kdw_fprop_auto_variant(int64_t C, int64_t W, int64_t D) {
 
 int kdw_fprop_variant_channels(int id) {
     if (id < 1 || id > kdw::n_fprop_variants()) return KDW_ERR_TUNE;
-    if (id > kdw::g_n_table_variants) return 8;
+    if (id > kdw::g_n_table_variants) return kdw::fprop_mma_variant_channels(id - kdw::g_n_table_variants - 1);
     return kdw::g_fprop_variants[id - 1].cs;
 }
 

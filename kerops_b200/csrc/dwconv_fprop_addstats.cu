@@ -25,10 +25,12 @@ struct ACfg {
 
 // Adds the consumer threads' statistics for channel slice c0 to the CTA's workspace row [2][C] and clears them.
 template <class Cfg>
-__device__ __forceinline__ void flush_stats(float2 (&S1)[Cfg::CP], float2 (&S2)[Cfg::CP], float* red, float* row, int C,
-                                            int c0, int tid) {
+__device__ __forceinline__ bool flush_stats(float2 (&S1)[Cfg::CP], float2 (&S2)[Cfg::CP], float* red, float* row, int C,
+                                            int c0, int tid, bool failed) {
     constexpr int CS = Cfg::CS, CP = Cfg::CP, CPG = Cfg::CPG, NCW = Cfg::NCW;
     const int lane = tid & 31, warp = tid >> 5, cg = tid % CPG;
+    // all consumer warps come here, also those whose bounded wait ran out: either all add their sums or none does
+    if (named_barrier_or(1, Cfg::NT, failed)) return true;
 #pragma unroll
     for (int i = 0; i < CP; ++i) {
 #pragma unroll
@@ -58,6 +60,7 @@ __device__ __forceinline__ void flush_stats(float2 (&S1)[Cfg::CP], float2 (&S2)[
     named_barrier_sync(1, Cfg::NT);
 #pragma unroll
     for (int i = 0; i < CP; ++i) S1[i] = S2[i] = make_float2(0.f, 0.f);
+    return false;
 }
 
 template <class Cfg>
@@ -151,7 +154,7 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
                 for (int i = 0; i < CP; ++i)
                     wgt[k][i] = *reinterpret_cast<const __half2*>(wp + (size_t)k * C + 2 * i);
             if (it.g.c0 != cur_c0) {
-                if (cur_c0 >= 0) flush_stats<Cfg>(S1, S2, red, row, C, cur_c0, tid);
+                if (cur_c0 >= 0 && flush_stats<Cfg>(S1, S2, red, row, C, cur_c0, tid, failed)) failed = true;
                 cur_c0 = it.g.c0;
             }
             mv = W - (it.g.w0 + th.wg * M);
@@ -159,39 +162,42 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
             if (it.g.d0 + th.d >= D) mv = 0;
         }
         const uint32_t st = ci % ST;
-        const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u);
-        if (__any_sync(0xffffffffu, !ok)) {
-            if (lane == 0) atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
-            failed = true;
-            break;
-        }
-        const bool store = q - 1 >= it.g.hb;
-        unsigned char* ob_bytes = my_out + (oc & 1u) * Cfg::OUTW_BYTES;
-        if (store && lane == 0) tma_wait_read<1>();
-        __syncwarp();
-        const __half* in = reinterpret_cast<const __half*>(in_base + st * A::STAGE) + th.in_off;
-        const __half* res = reinterpret_cast<const __half*>(in_base + st * A::STAGE + Cfg::IN_STRIDE) + res_off;
-        __half* ob = reinterpret_cast<__half*>(ob_bytes) + th.out_off;
-        if (ci & 1u)
-            fprop_step_f32_addstats<Cfg>(in, res, ob, store, mv, wgt, P2, P1, S1, S2);
-        else
-            fprop_step_f32_addstats<Cfg>(in, res, ob, store, mv, wgt, P1, P2, S1, S2);
-        if (store) fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-            mbar_arrive(empty0 + 8 * st);
-            if (store) {
-                tma_store_5d(status, &tmy, smem_u32(ob_bytes), it.g.c0, it.g.d0 + th.warp_d0, it.g.w0 + th.wg * M, q - 1,
-                             it.g.n);
-                tma_commit();
+        if (!failed) {
+            const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u);
+            if (__any_sync(0xffffffffu, !ok)) {
+                if (lane == 0) atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
+                failed = true;  // keeps walking the schedule (no waits, no work) to meet the others at the flushes
             }
         }
-        if (store) ++oc;
+        if (!failed) {
+            const bool store = q - 1 >= it.g.hb;
+            unsigned char* ob_bytes = my_out + (oc & 1u) * Cfg::OUTW_BYTES;
+            if (store && lane == 0) tma_wait_read<1>();
+            __syncwarp();
+            const __half* in = reinterpret_cast<const __half*>(in_base + st * A::STAGE) + th.in_off;
+            const __half* res = reinterpret_cast<const __half*>(in_base + st * A::STAGE + Cfg::IN_STRIDE) + res_off;
+            __half* ob = reinterpret_cast<__half*>(ob_bytes) + th.out_off;
+            if (ci & 1u)
+                fprop_step_f32_addstats<Cfg>(in, res, ob, store, mv, wgt, P2, P1, S1, S2);
+            else
+                fprop_step_f32_addstats<Cfg>(in, res, ob, store, mv, wgt, P1, P2, S1, S2);
+            if (store) fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(empty0 + 8 * st);
+                if (store) {
+                    tma_store_5d(status, &tmy, smem_u32(ob_bytes), it.g.c0, it.g.d0 + th.warp_d0, it.g.w0 + th.wg * M,
+                                 q - 1, it.g.n);
+                    tma_commit();
+                }
+            }
+            if (store) ++oc;
+        }
         it.next(s);
         ++ci;
     }
     if (lane == 0) tma_wait_all();
-    if (!failed && cur_c0 >= 0) flush_stats<Cfg>(S1, S2, red, row, C, cur_c0, tid);
+    if (cur_c0 >= 0) (void)flush_stats<Cfg>(S1, S2, red, row, C, cur_c0, tid, failed);
 }
 
 // One warp per output k in [0, 2C): rows added in a fixed order, scaled by 1 / (voxels per channel).

@@ -1,141 +1,188 @@
-// Depthwise 3x3x3 forward pass on the tensor cores (warp-level mma.sync), fp32 accumulation.
+// Depthwise 3x3x3 forward pass on the tensor cores (warp-level mma.sync.m16n8k16), fp32 accumulation.
 //
-// Same column march, TMA pipeline and producer warp as fprop_tma_kernel (dwconv_fprop.cu); only the arithmetic
-// differs.  Channels are processed in slices of 8, so a voxel is one 16-byte row of the shared-memory tile.
-// For 16 consecutive voxels along d and the 8 channels of the slice, one input plane contributes
-//     out_a[v, c] += sum_{taps j} x[v + j, c] * w[a, j, c]          (a = 0, 1, 2: the three output planes it feeds)
-// which is written as  D[16 x 8] += A[16 x 16] * B[16 x 8]  with
-//     A[v, (j, c')] = x[v + tap_j, c']        two taps j per k16 step: an ldmatrix.x4 whose four 8x8 matrices are
-//                                             the voxel rows of the two shifted positions - no data rearrangement,
-//     B[(j, c'), c] = w[a, tap_j, c] if c' == c else 0      (kept in registers, rebuilt once per segment).
-// Only the channel diagonal of B is non-zero, so 1/8 of the tensor-core multiply-adds are useful; the tensor pipe
-// (about 940 multiply-adds per clock per SM for mma.sync on B200) still delivers as many useful ones as the FMA
-// pipe, so the work is split: the tap pairs (t=0, t=1) go to the tensor cores, the t=2 taps stay on the FMA pipe
-// as mixed-precision FMAs on the same fp32 accumulators (see fprop_mma_step).  fp16 x fp16 products are exact
-// and sums are kept in fp32, as in KDW_ACC_F32.
+// Replaces kerops/kernels/dw_conv.py:5-142 (_DWConv_cl3d_impl), like fprop_tma_kernel (dwconv_fprop.cu), whose
+// column march, TMA input ring and plane-by-plane accumulation it shares.  Only the arithmetic differs: the 27
+// multiply-adds per output leave the FMA pipe, which caps every CUDA-core formulation of this operator at 0.84 of
+// the HBM roofline on B200, and become small matrix products.
+//
+// Patch formulation.  Outputs are grouped in BLOCKS of 2 x 2 voxels (w, d); with one input plane, the outputs of
+// a block depend on a PATCH of 4 x 4 input voxels.  For one pair of channels (c0, c1) - one 32-bit word of a
+// channels-last voxel - and one of the three output planes an input plane feeds (a = 0, 1, 2):
+//     D[block, (out, cc')] += sum_{slot, cc}  A[block, (slot, cc)] * B[(slot, cc), (out, cc')]
+//     A[block, (slot, cc)]  = x[patch voxel `slot` of the block, channel c_cc]     a raw word of the staged tile
+//     B[(slot, cc), (out, cc')] = weight[a][b][t][c_cc'] if cc == cc' and slot - out is the tap (b, t), else 0
+// i.e. M = 16 blocks, K = 16 slots x 2 channels (two k16 steps), N = 4 outputs x 2 channels.  The A fragment of a
+// thread is a word it loads itself (one 16-byte load per voxel serves four channel pairs), the B fragments depend
+// only on the weights and stay in registers, and the D fragment of a thread is (block, out, both channels) - a
+// half2 of the output voxel - so nothing is shuffled or transposed.  27 of 96 multiply-adds are useful, against 1/8
+// for a block-diagonal formulation over 8 channels; with the tensor pipe at about 1000 multiply-adds per clock per
+// SM that leaves room for the full HBM rate.  fp16 x fp16 products are exact and sums are fp32 (KDW_ACC_F32).
+//
+// A warp owns a UNIT: 16 blocks (2 along w x 8 along d, i.e. 4 x 16 voxels) x 8 channels.  Per input plane it
+// reads 6 voxel rows with 16-byte loads (shared memory is laid out with the TMA swizzle whose span is one voxel, which makes
+// the loads of a quarter-warp hit distinct banks) and issues 24 mma on two sets of fp32 accumulators that swap roles
+// from step to step (finishing plane / middle plane), as in fprop_step_f32.  Finished planes are staged in shared
+// memory and leave through ONE TMA store per CTA and plane, issued by a dedicated warp; all hand-overs are
+// mbarriers with bounded waits.
 #include "../../include/kdw.h"
 #include "kdw_common.cuh"
 
 namespace kdw {
 
-template <int DT_, int WT_, int BW_, int ST_, int MINB_, bool MG_ = false>
-struct MCfg {
-    static constexpr bool MG = MG_;     // C == 8 only: tensor maps with the D and C axes merged (long TMA rows)
-    static constexpr int CS = 8;        // channels per slice: one 16-byte row per voxel
-    static constexpr int DT = DT_;      // d extent of the CTA tile (multiple of 16)
-    static constexpr int WT = WT_;      // w extent of the CTA tile
-    static constexpr int BW = BW_;      // w positions per warp (each a 16-voxel block along d)
-    static constexpr int ST = ST_;      // input pipeline stages
-    static constexpr int MINB = MINB_;
-    static constexpr int WD = DT / 16;  // warps along d
-    static constexpr int WW = WT / BW;  // warps along w
-    static constexpr int NCW = WD * WW;  // compute warps; warp NCW is the TMA producer
+template <int CS_, int WW_, int WD_, int UPW_, int ST_>
+struct PCfg {
+    static constexpr int CS = CS_;    // channels per CTA slice (8 .. 64)
+    static constexpr int WW = WW_;    // units along w
+    static constexpr int WD = WD_;    // units along d
+    static constexpr int UPW = UPW_;  // units (along w) per warp; they share the weight fragments
+    static constexpr int ST = ST_;    // input pipeline stages
+    static constexpr int NG = CS / 8;  // channel groups of 8 (one 16-byte chunk of a voxel)
+    static constexpr int NCW = NG * (WW / UPW) * WD;  // consumer warps; warp NCW loads, warp NCW + 1 stores
     static constexpr int NT = NCW * 32;
-    static constexpr int ROW = (DT + 2) * 16;  // bytes between consecutive w lines of an input stage
-    static constexpr int IN_BYTES = (WT + 2) * ROW;
-    static constexpr int IN_STRIDE = (IN_BYTES + 127) / 128 * 128;
-    static constexpr int OUTW_BYTES = BW * 16 * 16;  // one warp's output tile [BW][16][8] halfs
-    static constexpr int SMEM = ST * IN_STRIDE + 2 * NCW * OUTW_BYTES + 16 * ST + 128;
-    static_assert(DT % 16 == 0 && WT % BW == 0, "tile shape");
-    static_assert(OUTW_BYTES % 128 == 0, "out tile alignment");
+    static constexpr int NTHREADS = NT + 64;
+    static constexpr int WT = 4 * WW;
+    static constexpr int DT = 16 * WD;
+    static constexpr int VOXB = CS * 2;  // bytes of a voxel in shared memory
+    static constexpr int SWZ = CS == 8 ? 0 : VOXB;  // TMA swizzle span: one voxel (32, 64 or 128 bytes); none for 16
+    static constexpr int IN_BYTES = (WT + 2) * (DT + 2) * VOXB;
+    static constexpr int IN_STRIDE = (IN_BYTES + 1023) / 1024 * 1024;
+    static constexpr int OUT_BYTES = WT * DT * VOXB;
+    static constexpr int OUT_STRIDE = (OUT_BYTES + 1023) / 1024 * 1024;
+    static constexpr int SMEM = ST * IN_STRIDE + 2 * OUT_STRIDE + 16 * ST + 32 + 4 * ST + 1024;
+    static_assert(CS == 8 || CS == 16 || CS == 32 || CS == 64, "a voxel must be one swizzle span (or 16 bytes)");
+    static_assert(WW % UPW == 0, "units per warp");
+    static_assert(NTHREADS <= 1024, "thread count");
     static_assert(DT + 2 <= 256 && WT + 2 <= 256, "TMA box limits");
 };
 
-__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-__device__ __forceinline__ void ldsm_x2(uint32_t addr, uint32_t (&r)[2]) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
-}
-// d = a * b + c (m16n8k16, fp16 operands, fp32 accumulate); ZERO: c = 0
-template <bool ZERO>
-__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    if (ZERO) {
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-            "{%10, %10, %10, %10};"
-            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
-    } else {
-        asm volatile(
-            "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-            "{%0, %1, %2, %3};"
-            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-            : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-    }
-}
-__device__ __forceinline__ void mma1688(float (&d)[4], const uint32_t (&a)[2], uint32_t b0) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%0, %1, %2, %3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(b0));
+// Byte offset inside a 1024-byte aligned tile written by TMA with a swizzle span of SWZ bytes: the 16-byte chunk
+// index within the span (address bits 4..) is XORed with the address bits from bit 7 up - 3 bits for 128, 2 for
+// 64, 1 for 32.  With one voxel per span, the same chunk of 8 (and more) consecutive voxels lands in distinct
+// banks, which is what makes the 16-byte loads of a quarter-warp conflict-free.
+template <int SWZ>
+KDW_HD uint32_t swz(uint32_t off) {
+    return SWZ == 0 ? off : off ^ (((off >> 7) & (uint32_t)(SWZ / 16 - 1)) << 4);
 }
 
-// One input plane against the three output planes; R = (step count) % 3 rotates the roles of the three
-// accumulator sets: set (R+2)%3 starts plane q+1 (taps a=0), set (R+1)%3 continues plane q (a=1), set R%3
-// finishes plane q-1 (a=2) and is written to the warp's output tile when `store` is set.
-//
-// The warp walks the BW+2 input lines (w positions) of its tile once.  For a line it fetches the A fragment of
-// the tap pair (t=0, t=1) with one ldmatrix.x4 and the t=2 values with two 4-byte loads, and uses them for the
-// (up to) three outputs blk = line - b that read this line through tap b: 3 planes x 3 outputs = 9 mma (k16)
-// on nine different accumulators, plus the t=2 taps as mixed-precision FMAs on the same accumulators (the mma
-// accumulator fragment of a thread is rows g, g+8 x channels 2q, 2q+1 - exactly a pair of channel pairs).
-// Splitting the taps this way keeps the tensor pipe, the FMA pipe and shared-memory bandwidth all below their
-// limits: 9 mma + 18 packed FMAs per 16x8 outputs per plane step, 9 B of shared-memory reads per output.
-template <class Cfg, int R>
-__device__ __forceinline__ void fprop_mma_step(uint32_t stage_lane_addr, const unsigned char* stage_x2, unsigned char* ob,
-                                               bool store, const uint32_t (&wbp)[3][3][2], const __half2 (&w2)[3][3],
-                                               float (&acc)[3][Cfg::BW][4], int lane) {
-    constexpr int SET[3] = {(R + 2) % 3, (R + 1) % 3, R % 3};
-    constexpr int BW = Cfg::BW;
-    const int g = lane >> 2, q = lane & 3;
-#pragma unroll
-    for (int wl = 0; wl < BW + 2; ++wl) {
-        uint32_t a[4];
-        ldsm_x4(stage_lane_addr + wl * Cfg::ROW, a);
-        const __half2 x2g = *reinterpret_cast<const __half2*>(stage_x2 + wl * Cfg::ROW);             // row g,   t = 2
-        const __half2 x2h = *reinterpret_cast<const __half2*>(stage_x2 + wl * Cfg::ROW + 8 * 16);    // row g+8, t = 2
-#pragma unroll
-        for (int b = 0; b < 3; ++b) {
-            const int blk = wl - b;  // output position that reads this line through tap b
-            if (blk < 0 || blk >= BW) continue;
-#pragma unroll
-            for (int r = 0; r < 3; ++r) {
-                float(&d)[4] = acc[SET[r]][blk];
-                if (r == 0 && b == 0)
-                    mma16816<true>(d, a, wbp[r][b][0], wbp[r][b][1]);  // first taps of a new plane
-                else
-                    mma16816<false>(d, a, wbp[r][b][0], wbp[r][b][1]);
-                float2 lo = fma_h2_f2(w2[r][b], x2g, make_float2(d[0], d[1]));
-                float2 hi = fma_h2_f2(w2[r][b], x2h, make_float2(d[2], d[3]));
-                d[0] = lo.x;
-                d[1] = lo.y;
-                d[2] = hi.x;
-                d[3] = hi.y;
-            }
-        }
-        const int blk = wl - 2;  // all nine taps of this plane are in
-        if (blk >= 0 && store) {  // plane q-1 is finished: rows g and g+8 of the 16-voxel block, channels 2q, 2q+1
-            const float(&d)[4] = acc[SET[2]][blk];
-            *reinterpret_cast<__half2*>(ob + ((blk * 16 + g) * 8 + 2 * q) * 2) = __floats2half2_rn(d[0], d[1]);
-            *reinterpret_cast<__half2*>(ob + ((blk * 16 + g + 8) * 8 + 2 * q) * 2) = __floats2half2_rn(d[2], d[3]);
-        }
+// d = a * b + c (m16n8k16, fp16 operands, fp32 accumulate); ZERO: c = 0.  The four A registers and the four
+// accumulator registers of an mma are register QUADS (consecutive registers) in the machine instruction, the two
+// B registers a pair; Quad / the arrays below are laid out accordingly.
+struct Quad {
+    uint32_t r[4];
+};
+template <bool ZERO>
+__device__ __forceinline__ void mma16816(float (&d)[4], const Quad& a, uint32_t b0, uint32_t b1) {
+    if (ZERO) {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+            "{%10, %10, %10, %10};"
+            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+            : "r"(a.r[0]), "r"(a.r[1]), "r"(a.r[2]), "r"(a.r[3]), "r"(b0), "r"(b1), "f"(0.f));
+    } else {
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+            "{%0, %1, %2, %3};"
+            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+            : "r"(a.r[0]), "r"(a.r[1]), "r"(a.r[2]), "r"(a.r[3]), "r"(b0), "r"(b1));
     }
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+// A register copy the compiler does not look through.  A 16-byte load delivers the four channel pairs of ONE voxel
+// in a register quad, an mma wants the words of FOUR voxels for one channel pair in a quad: the 4 x 4 transpose
+// between the two is 16 moves, made once per plane step - each copy below has one definition and is used, in the
+// same position of the same quad, by the three mma (a = 2, 1, 0) that read it.
+__device__ __forceinline__ uint32_t reg_copy(uint32_t x) {
+    uint32_t y;
+    asm("mov.b32 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+
+// One input plane of one unit.  X[r] = the thread's voxel of input row r (r = 0..5: rows w-1 .. w+4 of the unit),
+// four channel-pair words each.  FIN completes plane q-1 with the a=2 taps (written to the staging tile when
+// `store`), MID takes plane q's a=1 taps, then FIN restarts as plane q+1 with the a=0 taps.
+// Fragment roles (g = lane / 4, t = lane % 4): A rows g / g+8 are the blocks (bw = 0 / 1, bd = g); the k16 step ks
+// covers the patch rows pw = 2ks (k 0-7: slot t) and 2ks+1 (k 8-15), patch column pd = t, i.e. the A quad of
+// (ks, channel pair) is the word of input rows 2ks, 2ks+2, 2ks+1, 2ks+3.
+// Consecutive mma never touch the same accumulator, so they issue back to back.
+template <class Cfg>
+__device__ __forceinline__ void pg_step(const uint4 (&X)[6], const uint32_t (&Bf)[4][3][2][2], float (&FIN)[4][4],
+                                        float (&MID)[4][4], bool store, uint32_t out_addr0, uint32_t out_addr1) {
+    Quad Q[2][4];
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+        Q[ks][0].r[0] = reg_copy(X[2 * ks].x), Q[ks][0].r[1] = reg_copy(X[2 * ks + 2].x);
+        Q[ks][0].r[2] = reg_copy(X[2 * ks + 1].x), Q[ks][0].r[3] = reg_copy(X[2 * ks + 3].x);
+        Q[ks][1].r[0] = reg_copy(X[2 * ks].y), Q[ks][1].r[1] = reg_copy(X[2 * ks + 2].y);
+        Q[ks][1].r[2] = reg_copy(X[2 * ks + 1].y), Q[ks][1].r[3] = reg_copy(X[2 * ks + 3].y);
+        Q[ks][2].r[0] = reg_copy(X[2 * ks].z), Q[ks][2].r[1] = reg_copy(X[2 * ks + 2].z);
+        Q[ks][2].r[2] = reg_copy(X[2 * ks + 1].z), Q[ks][2].r[3] = reg_copy(X[2 * ks + 3].z);
+        Q[ks][3].r[0] = reg_copy(X[2 * ks].w), Q[ks][3].r[1] = reg_copy(X[2 * ks + 2].w);
+        Q[ks][3].r[2] = reg_copy(X[2 * ks + 1].w), Q[ks][3].r[3] = reg_copy(X[2 * ks + 3].w);
+    }
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+        for (int cp = 0; cp < 4; ++cp) mma16816<false>(FIN[cp], Q[ks][cp], Bf[cp][2][ks][0], Bf[cp][2][ks][1]);
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+        for (int cp = 0; cp < 4; ++cp) mma16816<false>(MID[cp], Q[ks][cp], Bf[cp][1][ks][0], Bf[cp][1][ks][1]);
+    if (store) {
+        uint4 o0, o1;  // block row g: outputs (t>>1, t&1) of block (bw=0); row g+8: the same of block (bw=1)
+        o0.x = pack_h2(FIN[0][0], FIN[0][1]);
+        o0.y = pack_h2(FIN[1][0], FIN[1][1]);
+        o0.z = pack_h2(FIN[2][0], FIN[2][1]);
+        o0.w = pack_h2(FIN[3][0], FIN[3][1]);
+        o1.x = pack_h2(FIN[0][2], FIN[0][3]);
+        o1.y = pack_h2(FIN[1][2], FIN[1][3]);
+        o1.z = pack_h2(FIN[2][2], FIN[2][3]);
+        o1.w = pack_h2(FIN[3][2], FIN[3][3]);
+        sts128(out_addr0, o0);
+        sts128(out_addr1, o1);
+    }
+#pragma unroll
+    for (int cp = 0; cp < 4; ++cp) mma16816<true>(FIN[cp], Q[0][cp], Bf[cp][0][0][0], Bf[cp][0][0][1]);
+#pragma unroll
+    for (int cp = 0; cp < 4; ++cp) mma16816<false>(FIN[cp], Q[1][cp], Bf[cp][0][1][0], Bf[cp][0][1][1]);
 }
 
 template <class Cfg>
-__global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
-    fprop_mma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
-                     const __half* __restrict__ weight, const Sched s, const int C, const int y_h0, int* status) {
-    constexpr int ST = Cfg::ST, NCW = Cfg::NCW, BW = Cfg::BW;
+__global__ void __launch_bounds__(Cfg::NTHREADS, 1)
+    fprop_pg_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
+                    const __half* __restrict__ weight, const Sched s, const int C, const int y_h0, int* status,
+                    const WaitTest wt) {
+    constexpr int ST = Cfg::ST, NCW = Cfg::NCW, UPW = Cfg::UPW;
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
-    unsigned char* in_base = smem;
-    unsigned char* out_base = smem + ST * Cfg::IN_STRIDE;
-    const uint32_t full0 = smem_u32(out_base + 2 * NCW * Cfg::OUTW_BYTES);
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
+    const uint32_t in0 = base;
+    const uint32_t out0 = base + ST * Cfg::IN_STRIDE;
+    const uint32_t full0 = out0 + 2 * Cfg::OUT_STRIDE;  // full[ST], empty[ST], staged[2], ofree[2]
     const uint32_t empty0 = full0 + 8 * ST;
+    const uint32_t staged0 = empty0 + 8 * ST;
+    const uint32_t ofree0 = staged0 + 16;
+    // desc[ST]: what the consumers need to know about the plane in a stage, written by the load warp before the
+    // copy is issued: bit 0 = this step finishes an owned plane (store it), bits 8.. = first channel of the slice;
+    // -1 = no more planes.  The consumer warps so never decode the schedule themselves.
+    const uint32_t desc0 = ofree0 + 16;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
@@ -146,192 +193,253 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
             mbar_init(full0 + 8 * k, 1);
             mbar_init(empty0 + 8 * k, NCW);
         }
+        for (int k = 0; k < 2; ++k) {
+            mbar_init(staged0 + 8 * k, NCW);
+            mbar_init(ofree0 + 8 * k, 1);
+        }
         mbar_fence_init();
     }
     __syncthreads();  // the only CTA-wide barrier
 
     if (warp == NCW) {
-        // ---------------- producer warp: one lane streams the input planes of the CTA's range ----------------
+        // ---------------- load warp: one lane streams the input planes of the CTA's range ----------------
         if (lane != 0) return;
         StepIter it;
         it.init(s, (int)blockIdx.x, (int)gridDim.x);
         uint32_t pi = 0;
         bool ok = true;
-        while (it.active) {
+        while (true) {
+            if (wt.stop_after >= 0 && (int)pi >= wt.stop_after) return;  // test hook: the consumers' wait runs out
             const uint32_t st = pi % ST;
-            if (pi >= ST) ok = mbar_wait_bounded(empty0 + 8 * st, ((pi / ST) & 1u) ^ 1u);
+            if (pi >= ST) ok = mbar_wait_bounded(empty0 + 8 * st, ((pi / ST) & 1u) ^ 1u, wt.limit_ns);
             if (!ok) break;
+            if (!it.active) {  // end marker: completes the stage's barrier without a copy
+                st_shared_u32(desc0 + 4 * st, 0xffffffffu);
+                mbar_arrive(full0 + 8 * st);
+                break;
+            }
+            st_shared_u32(desc0 + 4 * st, ((uint32_t)it.g.c0 << 8) | (it.q - 1 >= it.g.hb ? 1u : 0u));
             mbar_expect_tx(full0 + 8 * st, Cfg::IN_BYTES);
-            if (Cfg::MG)
-                tma_load_5d(status, smem_u32(in_base + st * Cfg::IN_STRIDE), &tmx, full0 + 8 * st, (it.g.d0 - 1) * 8,
-                            it.g.w0 - 1, it.q, it.g.n, 0);
-            else
-                tma_load_5d(status, smem_u32(in_base + st * Cfg::IN_STRIDE), &tmx, full0 + 8 * st, it.g.c0,
-                            it.g.d0 - 1, it.g.w0 - 1, it.q, it.g.n);
+            tma_load_5d(status, in0 + st * Cfg::IN_STRIDE, &tmx, full0 + 8 * st, it.g.c0, it.g.d0 - 1, it.g.w0 - 1, it.q,
+                        it.g.n);
             ++pi;
             it.next(s);
         }
         if (!ok) {
             atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
             const uint32_t first = pi > ST ? pi - ST : 0;
-            for (uint32_t k = first; k < pi; ++k) (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u);
+            for (uint32_t k = first; k < pi; ++k) (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u, wt.limit_ns);
         }
         return;
     }
+    if (warp == NCW + 1) {
+        // ---------------- store warp: one TMA store per finished plane of the tile ----------------
+        if (lane != 0) return;
+        StepIter it;
+        it.init(s, (int)blockIdx.x, (int)gridDim.x);
+        uint32_t oc = 0;
+        while (it.active) {
+            if (it.q - 1 >= it.g.hb) {
+                const uint32_t b = oc & 1u;
+                if (!mbar_wait_bounded(staged0 + 8 * b, (oc >> 1) & 1u, wt.limit_ns)) {
+                    atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
+                    break;
+                }
+                tma_store_5d(status, &tmy, out0 + b * Cfg::OUT_STRIDE, it.g.c0, it.g.d0, it.g.w0, it.q - 1 - y_h0, it.g.n);
+                tma_commit();
+                tma_wait_read_all();  // the store has read the tile: the consumers may overwrite it
+                mbar_arrive(ofree0 + 8 * b);
+                ++oc;
+            }
+            it.next(s);
+        }
+        tma_wait_all();
+        return;
+    }
 
-    // ---------------- compute warps ----------------
-    const int wd = warp % Cfg::WD, ww = warp / Cfg::WD;  // this warp's 16-voxel d block and group of BW w positions
-    const int g = lane >> 2, q = lane & 3;
-    // ldmatrix: lane L addresses row (L % 8) of matrix (L / 8); matrices 0,1 = voxels 0-7, 8-15 at the first tap of
-    // a pair, matrices 2,3 = the same voxels at the second tap.  Byte offset of the lane's voxel row at tap (0, 0):
-    const int vox = (lane & 7) + ((lane >> 3) & 1) * 8;
-    // input line 0 of the warp, this lane's voxel row, tap t = lane / 16 (0 or 1)
-    const uint32_t lane_off = (uint32_t)(((ww * BW) * (Cfg::DT + 2) + wd * 16 + vox + (lane >> 4)) * 16);
-    // the same line at t = 2: row g, channels 2q, 2q+1 (row g+8 is 128 bytes further)
-    const uint32_t x2_off = (uint32_t)(((ww * BW) * (Cfg::DT + 2) + wd * 16 + g + 2) * 16 + q * 4);
-    unsigned char* my_out = out_base + warp * 2 * Cfg::OUTW_BYTES;
+    // ---------------- consumer warps ----------------
+    const int ng = warp % Cfg::NG;                // channel group
+    const int uwg = (warp / Cfg::NG) % (Cfg::WW / UPW);  // group of UPW units along w
+    const int ud = warp / (Cfg::NG * (Cfg::WW / UPW));
+    const int g = lane >> 2, t = lane & 3;
+    // Shared-memory offsets of this thread's voxels.  Input row r of unit u: w index 4*(uwg*UPW+u) + r, d index
+    // 16*ud + 2g + t; output voxel k of unit u: w index 4*(uwg*UPW+u) + 2k + (t>>1), d index 16*ud + 2g + (t&1).
+    // Rows four apart (and units, and the two output rows) differ by a whole number of swizzle periods, so their
+    // offsets differ by a constant: four input offsets and one output offset are kept in registers.
+    constexpr uint32_t IN_ROW4 = 4 * (Cfg::DT + 2) * Cfg::VOXB, OUT_ROW2 = 2 * Cfg::DT * Cfg::VOXB;
+    static_assert(Cfg::SWZ == 0 || (IN_ROW4 % (8 * Cfg::SWZ) == 0 && OUT_ROW2 % (8 * Cfg::SWZ) == 0),
+                  "row steps must preserve the swizzle phase");
+    uint32_t in_off[4], out_off;
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+        in_off[r] = swz<Cfg::SWZ>(
+            (uint32_t)(((4 * uwg * UPW + r) * (Cfg::DT + 2) + 16 * ud + 2 * g + t) * Cfg::VOXB + 16 * ng));
+    out_off = swz<Cfg::SWZ>(
+        (uint32_t)(((4 * uwg * UPW + (t >> 1)) * Cfg::DT + 16 * ud + 2 * g + (t & 1)) * Cfg::VOXB + 16 * ng));
 
-    StepIter it;
-    it.init(s, (int)blockIdx.x, (int)gridDim.x);
-    // B fragments of the tap pair (t=0, t=1) for plane a and tap b: the taps of channel g on the diagonal, i.e.
-    // (w if 2q == g, w if 2q+1 == g), zeros elsewhere; w2[a][b]: the t=2 taps of channels 2q, 2q+1 for the FMAs
-    uint32_t wbp[3][3][2];
-    __half2 w2[3][3];
-    float acc[3][BW][4];
-#pragma unroll
-    for (int r = 0; r < 3; ++r)
-#pragma unroll
-        for (int b = 0; b < BW; ++b)
-#pragma unroll
-            for (int k = 0; k < 4; ++k) acc[r][b][k] = 0.f;
+    uint32_t Bf[4][3][2][2];   // weight fragments [channel pair][a][k16 step][k half]
+    float S0[UPW][4][4], S1[UPW][4][4];  // no initialisation: a plane's sum starts with an mma that ignores them
 
     uint32_t ci = 0, oc = 0;
-    while (it.active) {
-        const int qpl = it.q;
-        if (qpl == it.g.hb - 1) {  // new segment: the taps of this slice's channel g, placed on the diagonal
-            const unsigned short* wp = reinterpret_cast<const unsigned short*>(weight) + it.g.c0;
-#pragma unroll
-            for (int a = 0; a < 3; ++a)
-#pragma unroll
-                for (int b = 0; b < 3; ++b) {
-#pragma unroll
-                    for (int t = 0; t < 2; ++t) {
-                        const uint32_t v = wp[(size_t)((a * 3 + b) * 3 + t) * C + g];
-                        wbp[a][b][t] = (g == 2 * q) ? v : ((g == 2 * q + 1) ? (v << 16) : 0u);
-                    }
-                    w2[a][b] = *reinterpret_cast<const __half2*>(wp + (size_t)((a * 3 + b) * 3 + 2) * C + 2 * q);
-                }
-        }
+    int cur_c0 = -1;
+    while (true) {
         const uint32_t st = ci % ST;
-        const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u);
+        const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u, wt.limit_ns);
         if (__any_sync(0xffffffffu, !ok)) {
             if (lane == 0) atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
             break;
         }
-        const bool store = qpl - 1 >= it.g.hb;
-        unsigned char* ob = my_out + (oc & 1u) * Cfg::OUTW_BYTES;
-        if (store && lane == 0) tma_wait_read<1>();
-        __syncwarp();
-        const uint32_t stage_lane_addr = smem_u32(in_base + st * Cfg::IN_STRIDE) + lane_off;
-        const unsigned char* stage_x2 = in_base + st * Cfg::IN_STRIDE + x2_off;
-        switch (ci % 3) {
-            case 0: fprop_mma_step<Cfg, 0>(stage_lane_addr, stage_x2, ob, store, wbp, w2, acc, lane); break;
-            case 1: fprop_mma_step<Cfg, 1>(stage_lane_addr, stage_x2, ob, store, wbp, w2, acc, lane); break;
-            default: fprop_mma_step<Cfg, 2>(stage_lane_addr, stage_x2, ob, store, wbp, w2, acc, lane); break;
+        const uint32_t dsc = ld_shared_u32(desc0 + 4 * st);
+        if (dsc == 0xffffffffu) break;  // the load warp has no more planes
+        const int c0 = (int)(dsc >> 8);
+        if (c0 != cur_c0) {
+            // new channel slice: B[(slot, cc), (out, cc')] for this thread's column n = g -> out = g >> 1, cc' = g & 1
+            // and its rows k = (slot t of patch row 2ks + j, cc): the tap (b, tt) = (patch row - ow, t - od), zero
+            // outside 0..2
+            cur_c0 = c0;
+            const unsigned short* wp = reinterpret_cast<const unsigned short*>(weight) + c0 + 8 * ng + (g & 1);
+            const int ow = g >> 2, od = (g >> 1) & 1;
+            const int tt = t - od;
+#pragma unroll
+            for (int cp = 0; cp < 4; ++cp)
+#pragma unroll
+                for (int a = 0; a < 3; ++a)
+#pragma unroll
+                    for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const int b = 2 * ks + j - ow;
+                            uint32_t v = 0;
+                            if (b >= 0 && b <= 2 && tt >= 0 && tt <= 2) v = wp[(size_t)((a * 3 + b) * 3 + tt) * C + 2 * cp];
+                            Bf[cp][a][ks][j] = (g & 1) ? (v << 16) : v;
+                        }
         }
-        if (store) fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-            mbar_arrive(empty0 + 8 * st);
-            if (store) {
-                if (Cfg::MG)
-                    tma_store_5d(status, &tmy, smem_u32(ob), (it.g.d0 + wd * 16) * 8, it.g.w0 + ww * BW, qpl - 1 - y_h0,
-                                 it.g.n, 0);
-                else
-                    tma_store_5d(status, &tmy, smem_u32(ob), it.g.c0, it.g.d0 + wd * 16, it.g.w0 + ww * BW,
-                                 qpl - 1 - y_h0, it.g.n);
-                tma_commit();
+        const bool store = (dsc & 1u) != 0;  // this step finishes a plane the segment owns
+        const uint32_t stage = in0 + st * Cfg::IN_STRIDE;
+        const uint32_t ob = out0 + (oc & 1u) * Cfg::OUT_STRIDE;
+        if (store && oc >= 2) {  // the store that last read this staging tile must have finished
+            const bool free_ok = mbar_wait_bounded(ofree0 + 8 * (oc & 1u), ((oc >> 1) - 1u) & 1u, wt.limit_ns);
+            if (__any_sync(0xffffffffu, !free_ok)) {
+                if (lane == 0) atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
+                break;
             }
         }
-        if (store) ++oc;
-        it.next(s);
+#pragma unroll
+        for (int u = 0; u < UPW; ++u) {
+            uint4 X[6];
+#pragma unroll
+            for (int r = 0; r < 6; ++r) X[r] = lds128(stage + in_off[r & 3] + (uint32_t)((r >> 2) + u) * IN_ROW4);
+            if (u == UPW - 1) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty0 + 8 * st);  // the values are in registers: the stage can be refilled
+            }
+            if (ci & 1u)
+                pg_step<Cfg>(X, Bf, S1[u], S0[u], store, ob + out_off + u * 2 * OUT_ROW2,
+                             ob + out_off + (u * 2 + 1) * OUT_ROW2);
+            else
+                pg_step<Cfg>(X, Bf, S0[u], S1[u], store, ob + out_off + u * 2 * OUT_ROW2,
+                             ob + out_off + (u * 2 + 1) * OUT_ROW2);
+        }
+        if (store) {
+            fence_proxy_async_smem();  // the tile must be visible to the TMA store
+            __syncwarp();
+            if (lane == 0) mbar_arrive(staged0 + 8 * (oc & 1u));
+            ++oc;
+        }
         ++ci;
     }
-    if (lane == 0) tma_wait_all();
 }
 
 // ------------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------------
+struct PgArgs {
+    const void* x;
+    const void* w;
+    void* y;
+    int64_t N, C, Hx, W, D, xsN, xsH, xsW, Hy, ysN, ysH, ysW;
+    int h_begin, h_end, y_h0;
+    cudaStream_t stream;
+};
+
 template <class Cfg>
-static int launch_fprop_mma(const void* x, const void* w, void* y, int64_t N, int64_t C, int64_t Hx, int64_t W, int64_t D,
-                            int64_t xsN, int64_t xsH, int64_t xsW, int64_t Hy, int64_t ysN, int64_t ysH, int64_t ysW,
-                            int h_begin, int h_end, int y_h0, cudaStream_t stream) {
+static int launch_fprop_pg(const PgArgs& a) {
     CUtensorMap tmx, tmy;
-    int rc;
-    if (Cfg::MG) {
-        if (C != 8) {
-            set_error("fprop: this tensor-core variant needs C == 8");
-            return KDW_ERR_TUNE;
-        }
-        rc = encode_merged_map(&tmx, x, N, C, Hx, W, D, xsN, xsH, xsW, (Cfg::DT + 2) * 8, Cfg::WT + 2);
-        if (rc) return rc;
-        rc = encode_merged_map(&tmy, y, N, C, Hy, W, D, ysN, ysH, ysW, 16 * 8, Cfg::BW);
-    } else {
-        rc = encode_volume_map(&tmx, x, N, C, Hx, W, D, xsN, xsH, xsW, Cfg::CS, Cfg::DT + 2, Cfg::WT + 2);
-        if (rc) return rc;
-        rc = encode_volume_map(&tmy, y, N, C, Hy, W, D, ysN, ysH, ysW, Cfg::CS, 16, Cfg::BW);
-    }
+    int rc = encode_volume_map(&tmx, a.x, a.N, a.C, a.Hx, a.W, a.D, a.xsN, a.xsH, a.xsW, Cfg::CS, Cfg::DT + 2,
+                               Cfg::WT + 2, false, Cfg::SWZ);
     if (rc) return rc;
-    if (((uintptr_t)w & 1) != 0) {
+    rc = encode_volume_map(&tmy, a.y, a.N, a.C, a.Hy, a.W, a.D, a.ysN, a.ysH, a.ysW, Cfg::CS, Cfg::DT, Cfg::WT, false,
+                           Cfg::SWZ);
+    if (rc) return rc;
+    if (((uintptr_t)a.w & 1) != 0) {
         set_error("weight pointer must be 2-byte aligned");
         return KDW_ERR_ALIGN;
     }
-    auto kern = fprop_mma_kernel<Cfg>;
-    KDW_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
-    int occ = 0, sms = 0;
-    KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::NT + 32, Cfg::SMEM));
-    if (occ < 1) {
-        set_error("fprop mma kernel variant does not fit on this device");
-        return KDW_ERR_TUNE;
-    }
-    rc = device_sm_count(&sms);
+    static KernelSetup setup;  // one per kernel instantiation
+    auto kern = fprop_pg_kernel<Cfg>;
+    int sms = 0, occ = 0;
+    rc = setup.get((const void*)kern, Cfg::NTHREADS, Cfg::SMEM, &sms, &occ);
     if (rc) return rc;
     int* status = nullptr;
     rc = status_ptr(&status);
     if (rc) return rc;
     Sched s;
-    const int grid = make_sched(&s, N, C, W, D, h_begin, h_end, Cfg::WT, Cfg::DT, Cfg::CS, sms * occ);
-    kern<<<grid, Cfg::NT + 32, Cfg::SMEM, stream>>>(tmx, tmy, (const __half*)w, s, (int)C, y_h0, status);
+    const int grid = make_sched(&s, a.N, a.C, a.W, a.D, a.h_begin, a.h_end, Cfg::WT, Cfg::DT, Cfg::CS, sms * occ);
+    kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, a.stream>>>(tmx, tmy, (const __half*)a.w, s, (int)a.C, a.y_h0, status,
+                                                       wait_test());
     KDW_CUDA(cudaGetLastError());
     return 0;
 }
 
-// Tensor-core variants, numbered after the variants of fprop_variants.inc by the dispatcher in dwconv_fprop.cu.
-#define KDW_MMA_CASE(IDX, ...)                                                                                  \
-    case IDX:                                                                                                  \
-        return launch_fprop_mma<MCfg<__VA_ARGS__>>(x, w, y, N, C, Hx, W, D, xsN, xsH, xsW, Hy, ysN, ysH, ysW, h_begin, \
-                                                   h_end, y_h0, stream);
+typedef int (*PgLaunch)(const PgArgs&);
+struct PgVariant {
+    int cs, dt, wt;
+    PgLaunch f;
+};
+// PCfg<CS, WW, WD, UPW, ST>: tile 4*WW x 16*WD voxels (w, d), CS channels
+#define KDW_PG(CS, WW, WD, UPW, ST) {CS, 16 * WD, 4 * WW, &launch_fprop_pg<PCfg<CS, WW, WD, UPW, ST>>}
+static const PgVariant g_pg_variants[] = {
+    KDW_PG(64, 2, 1, 1, 4),  // 0: 16 consumer warps, tile 8 x 16
+    KDW_PG(64, 2, 1, 2, 4),  // 1: 8 consumer warps, two units each
+    KDW_PG(32, 4, 1, 1, 4),  // 2: 16 warps, tile 16 x 16
+    KDW_PG(32, 4, 1, 2, 4),  // 3: 8 warps
+    KDW_PG(16, 4, 2, 1, 4),  // 4: 16 warps, tile 16 x 32
+    KDW_PG(16, 4, 2, 2, 4),  // 5: 8 warps
+    KDW_PG(8, 4, 4, 1, 4),   // 6: 16 warps, tile 16 x 64
+    KDW_PG(8, 4, 4, 2, 4),   // 7: 8 warps
+    KDW_PG(64, 4, 1, 2, 3),  // 8: 16 warps, two units each, tile 16 x 16
+    KDW_PG(32, 4, 2, 2, 3),  // 9: 16 warps, two units each, tile 16 x 32
+};
+#undef KDW_PG
+static const int g_n_pg_variants = (int)(sizeof(g_pg_variants) / sizeof(g_pg_variants[0]));
 
-int fprop_mma_variants() { return 10; }
+int fprop_mma_variants() { return g_n_pg_variants; }
+
+int fprop_mma_variant_channels(int which) {
+    if (which < 0 || which >= g_n_pg_variants) return KDW_ERR_TUNE;
+    return g_pg_variants[which].cs;
+}
+
+void fprop_mma_variant_tile(int which, int* wt, int* dt) {
+    *wt = g_pg_variants[which].wt;
+    *dt = g_pg_variants[which].dt;
+}
 
 int launch_fprop_mma_variant(int which, const void* x, const void* w, void* y, int64_t N, int64_t C, int64_t Hx,
                              int64_t W, int64_t D, int64_t xsN, int64_t xsH, int64_t xsW, int64_t Hy, int64_t ysN,
                              int64_t ysH, int64_t ysW, int h_begin, int h_end, int y_h0, cudaStream_t stream) {
-    switch (which) {  // MCfg<DT, WT, BW, ST, MINB, MG>
-        KDW_MMA_CASE(0, 64, 8, 4, 6, 1)
-        KDW_MMA_CASE(1, 64, 6, 3, 4, 2)
-        KDW_MMA_CASE(2, 64, 8, 4, 4, 2)
-        KDW_MMA_CASE(3, 128, 6, 3, 3, 1)
-        KDW_MMA_CASE(4, 64, 4, 2, 4, 2)
-        KDW_MMA_CASE(5, 16, 32, 4, 4, 1, true)
-        KDW_MMA_CASE(6, 16, 24, 3, 4, 2, true)
-        KDW_MMA_CASE(7, 64, 8, 4, 10, 1)
-        KDW_MMA_CASE(8, 64, 4, 2, 8, 2)
-        KDW_MMA_CASE(9, 16, 32, 4, 10, 1, true)
+    if (which < 0 || which >= g_n_pg_variants) {
+        set_error("fprop: no such tensor-core variant");
+        return KDW_ERR_TUNE;
     }
-    set_error("fprop: no such tensor-core variant");
-    return KDW_ERR_TUNE;
+    const PgVariant& v = g_pg_variants[which];
+    if (C % v.cs != 0) {
+        set_error("fprop: tensor-core variant %d works on %d-channel slices, C=%lld is not a multiple", which, v.cs,
+                  (long long)C);
+        return KDW_ERR_TUNE;
+    }
+    PgArgs a{x, w, y, N, C, Hx, W, D, xsN, xsH, xsW, Hy, ysN, ysH, ysW, h_begin, h_end, y_h0, stream};
+    return v.f(a);
 }
 
 }  // namespace kdw

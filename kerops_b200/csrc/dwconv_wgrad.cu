@@ -85,11 +85,16 @@ __global__ void __launch_bounds__(128) wgrad_plain_kernel(const __half* __restri
 // ------------------------------------------------------------------------------------------------
 // Adds the consumer threads' accumulators for channel slice c0 to the CTA's workspace row and clears them:
 // shuffle reduction over the lanes that share channels, then the warps take turns in a fixed order through
-// shared memory (no atomics, so the sum is reproducible).  Called by all consumer threads of the CTA.
+// shared memory (no atomics, so the sum is reproducible).  Called by all consumer threads of the CTA - also by
+// warps whose bounded wait ran out (`failed`): the first barrier ORs that flag over all consumer threads, so
+// either every warp adds its sums or none does, and no warp is left waiting at a barrier the others never reach.
+// Returns true when the flush was abandoned.
 template <class Cfg>
-__device__ __forceinline__ void flush_acc(float2 (&acc)[27][Cfg::CP], float* red, float* row, int C, int c0, int tid) {
+__device__ __forceinline__ bool flush_acc(float2 (&acc)[27][Cfg::CP], float* red, float* row, int C, int c0, int tid,
+                                          bool failed) {
     constexpr int CS = Cfg::CS, CP = Cfg::CP, CPG = Cfg::CPG, NCW = Cfg::NCW;
     const int lane = tid & 31, warp = tid >> 5, cg = tid % CPG;
+    if (named_barrier_or(1, Cfg::NT, failed)) return true;
 #pragma unroll
     for (int k = 0; k < 27; ++k)
 #pragma unroll
@@ -129,12 +134,14 @@ __device__ __forceinline__ void flush_acc(float2 (&acc)[27][Cfg::CP], float* red
     for (int k = 0; k < 27; ++k)
 #pragma unroll
         for (int i = 0; i < CP; ++i) acc[k][i] = make_float2(0.f, 0.f);
+    return false;
 }
 
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
     wgrad_tma_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmg,
-                     float* __restrict__ ws, const Sched s, const int C, const int g_h0, int* status) {
+                     float* __restrict__ ws, const Sched s, const int C, const int g_h0, int* status,
+                     const WaitTest wt) {
     constexpr int CS = Cfg::CS, M = Cfg::M, CP = Cfg::CP, ST = Cfg::ST, CPG = Cfg::CPG, NCW = Cfg::NCW;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);
@@ -168,8 +175,9 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
         uint32_t pi = 0;
         bool ok = true;
         while (it.active) {
+            if (wt.stop_after >= 0 && (int)pi >= wt.stop_after) return;  // test hook: the consumers' wait runs out
             const uint32_t st = pi % ST;
-            if (pi >= ST) ok = mbar_wait_bounded(empty0 + 8 * st, ((pi / ST) & 1u) ^ 1u);
+            if (pi >= ST) ok = mbar_wait_bounded(empty0 + 8 * st, ((pi / ST) & 1u) ^ 1u, wt.limit_ns);
             if (!ok) break;
             const bool with_g = it.q + 1 < it.g.he;  // grad plane q+1 is owned by the segment
             const uint32_t bar = full0 + 8 * st;
@@ -185,7 +193,8 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
         if (!ok) {
             atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
             const uint32_t first = pi > ST ? pi - ST : 0;
-            for (uint32_t k = first; k < pi; ++k) (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u);
+            for (uint32_t k = first; k < pi; ++k)
+                (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u, wt.limit_ns);
         }
         return;
     }
@@ -208,15 +217,18 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
         for (int i = 0; i < CP; ++i) acc[k][i] = make_float2(0.f, 0.f);
 
     uint32_t ci = 0;
+    // A warp whose wait ran out keeps walking the schedule without waiting or computing, so that it still meets
+    // the other consumer warps at every flush; the flush then decides for all of them (see flush_acc).
     bool failed = false;
     int cur_c0 = -1;  // channel slice the accumulators belong to
     while (it.active) {
         const uint32_t st = ci % ST;
-        const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u);
-        if (__any_sync(0xffffffffu, !ok)) {
-            if (lane == 0) atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
-            failed = true;
-            break;
+        if (!failed) {
+            const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u, wt.limit_ns);
+            if (__any_sync(0xffffffffu, !ok)) {
+                if (lane == 0) atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
+                failed = true;
+            }
         }
         const int q = it.q;
         if (q == it.g.hb - 1) {
@@ -229,24 +241,27 @@ __global__ void __launch_bounds__(Cfg::NT + 32, Cfg::MINB)
             // segment and flushed to the workspace row only when the slice changes (in the round phase a CTA
             // keeps its slice whenever the CTA count is a multiple of the slice count) and at the end.
             if (it.g.c0 != cur_c0) {
-                if (cur_c0 >= 0) flush_acc<Cfg>(acc, red, row, C, cur_c0, tid);
+                if (cur_c0 >= 0 && flush_acc<Cfg>(acc, red, row, C, cur_c0, tid, failed)) failed = true;
                 cur_c0 = it.g.c0;
             }
         }
-        const bool load_g = q + 1 < it.g.he;
-        const __half* xin = reinterpret_cast<const __half*>(stage_base + st * Cfg::STAGE) + th.x_off;
-        const __half* gin = reinterpret_cast<const __half*>(stage_base + st * Cfg::STAGE + Cfg::X_STRIDE) + th.g_off;
-        switch (ci % 3) {
-            case 0: wgrad_step<Cfg, 0>(xin, gin, load_g, G, acc); break;
-            case 1: wgrad_step<Cfg, 1>(xin, gin, load_g, G, acc); break;
-            default: wgrad_step<Cfg, 2>(xin, gin, load_g, G, acc); break;
+        if (!failed) {
+            const bool load_g = q + 1 < it.g.he;
+            const __half* xin = reinterpret_cast<const __half*>(stage_base + st * Cfg::STAGE) + th.x_off;
+            const __half* gin =
+                reinterpret_cast<const __half*>(stage_base + st * Cfg::STAGE + Cfg::X_STRIDE) + th.g_off;
+            switch (ci % 3) {
+                case 0: wgrad_step<Cfg, 0>(xin, gin, load_g, G, acc); break;
+                case 1: wgrad_step<Cfg, 1>(xin, gin, load_g, G, acc); break;
+                default: wgrad_step<Cfg, 2>(xin, gin, load_g, G, acc); break;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * st);  // this warp is done with the stage
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(empty0 + 8 * st);  // this warp is done with the stage
         it.next(s);
         ++ci;
     }
-    if (!failed && cur_c0 >= 0) flush_acc<Cfg>(acc, red, row, C, cur_c0, tid);
+    if (cur_c0 >= 0) (void)flush_acc<Cfg>(acc, red, row, C, cur_c0, tid, failed);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -271,14 +286,9 @@ static int launch_wgrad_tma(const WgradArgs& a, int* rows_used) {
     rc = encode_volume_map(&tmg, a.g, a.N, a.C, a.Hg, a.W, a.D, a.gsN, a.gsH, a.gsW, Cfg::CS, Cfg::DT, Cfg::WT);
     if (rc) return rc;
     auto kern = wgrad_tma_kernel<Cfg>;
-    KDW_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+    static KernelSetup setup;  // one per kernel instantiation
     int occ = 0, sms = 0;
-    KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, Cfg::NT + 32, Cfg::SMEM));
-    if (occ < 1) {
-        set_error("wgrad kernel variant does not fit on this device");
-        return KDW_ERR_TUNE;
-    }
-    rc = device_sm_count(&sms);
+    rc = setup.get((const void*)kern, Cfg::NT + 32, Cfg::SMEM, &sms, &occ);
     if (rc) return rc;
     int* status = nullptr;
     rc = status_ptr(&status);
@@ -287,7 +297,7 @@ static int launch_wgrad_tma(const WgradArgs& a, int* rows_used) {
     if (target > a.ws_rows) target = a.ws_rows;
     Sched s;
     const int grid = make_sched(&s, a.N, a.C, a.W, a.D, a.h_begin, a.h_end, Cfg::WT, Cfg::DT, Cfg::CS, (int)target);
-    kern<<<grid, Cfg::NT + 32, Cfg::SMEM, a.stream>>>(tmx, tmg, a.ws, s, (int)a.C, a.g_h0, status);
+    kern<<<grid, Cfg::NT + 32, Cfg::SMEM, a.stream>>>(tmx, tmg, a.ws, s, (int)a.C, a.g_h0, status, wait_test());
     KDW_CUDA(cudaGetLastError());
     *rows_used = grid;
     return 0;

@@ -42,13 +42,37 @@ int cuda_fail(cudaError_t e, const char* what);  // records the message, returns
 // out-of-bounds elements.  Returns 0 or a negative argument error / positive driver error.
 int encode_volume_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
                       int64_t strideN, int64_t strideH, int64_t strideW, int boxC, int boxD, int boxW,
-                      bool nan_fill = false);  // nan_fill: out-of-bounds elements read as NaN instead of zero
+                      bool nan_fill = false,  // out-of-bounds elements read as NaN instead of zero
+                      int swizzle = 0);       // 0, or 32 / 64 / 128: swizzled shared-memory tile, boxC * 2 == swizzle
 
 // As encode_volume_map with the D and C axes merged (see kdw_host.cu).
 int encode_merged_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
                       int64_t strideN, int64_t strideH, int64_t strideW, int boxDC, int boxW);
 
 int device_sm_count(int* sms);
+
+// Per kernel and device: the opt-in to `smem` bytes of dynamic shared memory, the CTAs per SM the kernel reaches
+// with `threads` threads and the SM count - looked up on the first launch on a device and remembered (one
+// static instance per kernel instantiation).
+struct KernelSetup {
+    static constexpr int kMaxDevices = 64;
+    int occ[kMaxDevices];
+    int sms[kMaxDevices];
+    bool done[kMaxDevices];
+    KernelSetup() {
+        for (int i = 0; i < kMaxDevices; ++i) done[i] = false;
+    }
+    int get(const void* kernel, int threads, int smem, int* sms_out, int* occ_out);
+};
+
+// Limits of the kernels' bounded waits.  limit_ns is the time after which a wait on an mbarrier gives up (2 s by
+// default); stop_after >= 0 makes the load warp of a TMA kernel stop after that many plane loads, so that the
+// consumers' next wait runs out - the way the test-suite exercises the time-out path without any fault.
+struct WaitTest {
+    unsigned long long limit_ns;
+    int stop_after;
+};
+WaitTest wait_test();
 
 // Device address (on the current device) of the library's status word.
 int status_ptr(int** p);
@@ -203,14 +227,15 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// Bounded wait: gives up after ~2 s of wall time and returns false (the caller then raises the
-// status word and leaves the kernel instead of spinning for ever).
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+// Bounded wait: gives up after limit_ns (2 s by default) of wall time and returns false (the caller then raises
+// the status word and leaves the kernel instead of spinning for ever).
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
+                                                  unsigned long long limit_ns = 2000000000ull) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 63u) == 63u && global_ns() - t0 > 2000000000ull) return false;
+        if ((it & 63u) == 63u && global_ns() - t0 > limit_ns) return false;
     }
 }
 

@@ -4,6 +4,8 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "../../include/kdw.h"
 #include "kdw_common.cuh"
 
@@ -40,6 +42,38 @@ int device_sm_count(int* sms) {
     return 0;
 }
 
+int KernelSetup::get(const void* kernel, int threads, int smem, int* sms_out, int* occ_out) {
+    static std::mutex mu;
+    int dev = 0;
+    KDW_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) {
+        set_error("device index %d is outside the supported range 0..%d", dev, kMaxDevices - 1);
+        return KDW_ERR_ARG;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!done[dev]) {
+        KDW_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        int o = 0;
+        KDW_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o, kernel, threads, smem));
+        if (o < 1) {
+            set_error("kernel variant does not fit on this device (%d threads, %d bytes of shared memory)", threads,
+                      smem);
+            return KDW_ERR_TUNE;
+        }
+        int n = 0;
+        KDW_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+        occ[dev] = o;
+        sms[dev] = n;
+        done[dev] = true;
+    }
+    *sms_out = sms[dev];
+    *occ_out = occ[dev];
+    return 0;
+}
+
+static WaitTest g_wait_test = {2000000000ull, -1};
+WaitTest wait_test() { return g_wait_test; }
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -61,7 +95,8 @@ static int get_encode_fn(EncodeTiledFn* out) {
 }
 
 int encode_volume_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
-                      int64_t strideN, int64_t strideH, int64_t strideW, int boxC, int boxD, int boxW, bool nan_fill) {
+                      int64_t strideN, int64_t strideH, int64_t strideW, int boxC, int boxD, int boxW, bool nan_fill,
+                      int swizzle) {
     EncodeTiledFn fn;
     int rc = get_encode_fn(&fn);
     if (rc) return rc;
@@ -74,6 +109,15 @@ int encode_volume_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, 
         set_error("tensor-map box out of range");
         return KDW_ERR_ARG;
     }
+    // a swizzled tile is used only with box rows exactly one swizzle span long (rows are then packed densely)
+    if (swizzle != 0 && ((swizzle != 32 && swizzle != 64 && swizzle != 128) || boxC * 2 != swizzle)) {
+        set_error("tensor-map swizzle %d does not match the %d-byte box rows", swizzle, boxC * 2);
+        return KDW_ERR_ARG;
+    }
+    const CUtensorMapSwizzle sw = swizzle == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : swizzle == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                  : swizzle == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                                  : CU_TENSOR_MAP_SWIZZLE_NONE;
     const cuuint64_t dims[5] = {(cuuint64_t)C, (cuuint64_t)D, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
     // byte strides of dims 1..4; a dimension of extent 1 still needs a legal (multiple of 16) stride
     cuuint64_t strides[4] = {(cuuint64_t)C * 2, (cuuint64_t)strideW * 2, (cuuint64_t)strideH * 2,
@@ -83,7 +127,7 @@ int encode_volume_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, 
     const cuuint32_t box[5] = {(cuuint32_t)boxC, (cuuint32_t)boxD, (cuuint32_t)boxW, 1, 1};
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     nan_fill ? CU_TENSOR_MAP_FLOAT_OOB_FILL_NAN_REQUEST_ZERO_FMA : CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed with CUresult %d (dims C=%lld D=%lld W=%lld H=%lld N=%lld)", (int)r,
@@ -169,6 +213,16 @@ extern "C" {
 int kdw_version(void) { return 100; }
 
 const char* kdw_last_error(void) { return kdw::g_err; }
+
+int kdw_test_wait_limits(int64_t limit_ns, int stop_after) {
+    if (limit_ns <= 0) {
+        kdw::set_error("kdw_test_wait_limits: limit_ns must be positive");
+        return KDW_ERR_ARG;
+    }
+    kdw::g_wait_test.limit_ns = (unsigned long long)limit_ns;
+    kdw::g_wait_test.stop_after = stop_after < 0 ? -1 : stop_after;
+    return 0;
+}
 
 int kdw_device_status(int* status) {
     if (!status) {
