@@ -15,18 +15,22 @@ NCCL - the only exchange the sample-sharded path has.
 operator call (read x + write y, or read x + read grad; V = 350*350*128 voxels).
 The JSON line also carries: `roofline` (the kernel with the largest share of the timed region, bytes /
 CUDA-event time against the measured HBM peak), `detail` (per operator and C: ms mean / median / min, GB/s,
-fraction, ratio to torch.clone), `e2e` (the same sweep through the host-buffer operator DWConvStepHost,
-host<->device copies inside the timed region), `cpu_baseline` (torch CPU depthwise conv3d, the check the
-reference's tests use, on a bounded sample), `clocks` (SM clock and throttle reasons sampled through NVML during
-the timed region), and at one GPU `reference_triton_on_this_gpu` (the reference's own Triton kernels from
-baseline/_ref timed on the same tensors).
+fraction, ratio to torch.clone, the packed-half accumulate mode, two small-shape latencies), `e2e` (the same sweep
+through the host-buffer operator DWConvStepHost, host<->device copies inside the timed region), `cpu_baseline`
+(torch CPU depthwise conv3d, the check the reference's tests use, on a bounded sample), `clocks` (SM clock and
+throttle reasons sampled through NVML during the timed region), at one GPU `reference_triton_on_this_gpu` (the
+reference's own Triton kernels from baseline/_ref timed on the same tensors) with `vs_reference_triton` (the
+speed-ups), and - at every N - the two strong-scaling workloads as sub-records:
+`dshard` = one (1,128,1400,350,128) volume sharded along H over the ranks with halo exchange (BASELINE configs[3]) and
+`dpstep` = a batch of 8 x (32,350,350,128) samples split by sample (configs[4]), each with its per-rank breakdown,
+so that strong-scaling efficiency can be computed from the lines of a 1/2/4/8-GPU series alone.
 
-Other workloads (--workload): `dshard` = one (1,128,1400,350,128) volume sharded along H over the ranks with halo
-exchange (strong scaling); `dpstep` = a batch of 8 x (32,350,350,128) samples split by sample (strong scaling);
-`fused` = DWConvAddStats and DWConvBNReLU against the unfused and the reference two-operator chains (one GPU).
+--workload dshard | dpstep | fused run one of the other workloads alone (`fused` = DWConvAddStats and DWConvBNReLU
+against the unfused and the reference two-operator chains, one GPU).
 
-`--impl reference` times the CPU arm alone (rank 0 only): torch conv3d(groups=C) forward + weight
-gradient on the host cores, one (1, 8, 350, 350, 128) volume per step.
+`--impl reference` times the CPU arm alone (rank 0 only, all host cores): torch conv3d(groups=C) forward + weight
+gradient over the same five-C sweep, every volume cut to a slab of h-planes so that a step stays near a second; the
+slab times are scaled to the full volumes by plane count (conv3d's cost is proportional to it).
 """
 import argparse
 import json
@@ -164,13 +168,27 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------------------
 # CPU arm: torch depthwise conv3d on the host cores (the reference tests' own check, test_conv.py:25,60-72)
 # ----------------------------------------------------------------------------------------------------
-def make_cpu_inputs(C, seed=0):
+def cpu_threads():
+    """Host cores this process may use (torch.distributed.run exports OMP_NUM_THREADS=1; the CPU arm undoes that)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_slab_planes(C):
+    """h-planes of the CPU arm's slab for channel count C: the full 350 at C = 8, halved for every doubling of C, so
+    that every C costs about the same CPU time."""
+    return max(8, min(SHAPE[0], (SHAPE[0] * 8) // C))
+
+
+def make_cpu_inputs(C, planes, seed=0):
     import torch
 
     g = torch.Generator().manual_seed(seed)
-    H, W, D = SHAPE
-    x = torch.randn(1, H, W, D, C, generator=g, dtype=torch.float32).to(torch.float16).permute(0, 4, 1, 2, 3)
-    grad = torch.randn(1, H, W, D, C, generator=g, dtype=torch.float32).to(torch.float16).permute(0, 4, 1, 2, 3)
+    _, W, D = SHAPE
+    x = torch.randn(1, planes, W, D, C, generator=g, dtype=torch.float32).to(torch.float16).permute(0, 4, 1, 2, 3)
+    grad = torch.randn(1, planes, W, D, C, generator=g, dtype=torch.float32).to(torch.float16).permute(0, 4, 1, 2, 3)
     w = ((torch.rand(3, 3, 3, C, generator=g) * 2 - 1) / math.sqrt(27)).to(torch.float16)
     return x, grad, w
 
@@ -188,52 +206,85 @@ def cpu_step(x, grad, w, dtype):
     return y.detach().to(torch.float16), wt.grad
 
 
-def time_cpu_arm(C, steps, warmup, min_seconds=0.0):
-    """Seconds per step (median) of the faster of the fp32 / fp16 torch CPU paths, its name, the CPU seconds spent
-    in its timed steps and their number.  At least `steps` steps, and more until `min_seconds` of work are done."""
+def time_cpu_arm(channels, steps, warmup, min_seconds=0.0):
+    """The five-C sweep on the host cores, on slabs.  Returns a dict: seconds per FULL sweep step (median over the
+    steps of the sum over C of slab time x 350 / slab planes), the dtype used (the faster of fp32 / fp16 at the first
+    C), per-C slab planes and seconds, CPU seconds spent in timed steps and their number."""
     import torch
 
-    x, grad, w = make_cpu_inputs(C)
+    torch.set_num_threads(cpu_threads())
+    data = {C: make_cpu_inputs(C, cpu_slab_planes(C)) for C in channels}
+    C0 = channels[0]
     best = None
     for dtype in (torch.float32, torch.float16):
         try:
-            for _ in range(warmup):
-                cpu_step(x, grad, w, dtype)
-            ts = []
-            while len(ts) < steps or (sum(ts) < min_seconds and len(ts) < 500):
-                t0 = time.perf_counter()
-                cpu_step(x, grad, w, dtype)
-                ts.append(time.perf_counter() - t0)
-            med = statistics.median(ts)
-            if best is None or med < best[0]:
-                best = (med, str(dtype).replace('torch.', ''), sum(ts), len(ts))
+            cpu_step(*data[C0], dtype)
+            t0 = time.perf_counter()
+            cpu_step(*data[C0], dtype)
+            dt = time.perf_counter() - t0
+            if best is None or dt < best[0]:
+                best = (dt, dtype)
         except Exception:
             continue
     if best is None:
         raise RuntimeError('torch CPU conv3d failed in both fp32 and fp16')
-    return best
+    dtype = best[1]
+    for _ in range(warmup):
+        for C in channels:
+            cpu_step(*data[C], dtype)
+    totals, per_c, spent = [], {C: [] for C in channels}, 0.0
+    while len(totals) < steps or (spent < min_seconds and len(totals) < 200):
+        tot = 0.0
+        for C in channels:
+            t0 = time.perf_counter()
+            cpu_step(*data[C], dtype)
+            dt = time.perf_counter() - t0
+            spent += dt
+            per_c[C].append(dt)
+            tot += dt * SHAPE[0] / cpu_slab_planes(C)
+        totals.append(tot)
+    return {'sec_per_step': statistics.median(totals), 'dtype': str(dtype).replace('torch.', ''), 'spent': spent,
+            'n': len(totals), 'cores': torch.get_num_threads(),
+            'per_c': {str(C): {'planes': cpu_slab_planes(C), 'slab_s': round(statistics.median(per_c[C]), 4)}
+                      for C in channels}}
+
+
+def sweep_workload(channels, world):
+    return (f'configs[1]+[2]: DWConv then DWConvWGRAD on (1,C,{SHAPE[0]},350,128) fp16 channels_last_3d for C in '
+            + ','.join(map(str, channels)) + '; one sample per GPU')
+
+
+def sweep_config(channels, world):
+    """The `config` object both arms print (identical for the same flags)."""
+    return {'workload': sweep_workload(channels, world),
+            'l2': 'inputs larger than L2 (smallest tensor 251 MB; 31 GB touched per step)',
+            'parallelism': f'dp{world}' if world > 1 else 'single'}
+
+
+def cpu_sample_text(r, channels):
+    return ('the same five-C sweep on slabs of the volumes (h-planes per C: '
+            + ', '.join(f"{C}: {r['per_c'][str(C)]['planes']}" for C in channels)
+            + f"), torch CPU conv3d(groups=C) forward + weight gradient in {r['dtype']}; slab times scaled to 350 planes; "
+              f"median of {r['n']} steps ({r['spent']:.1f} s of CPU work)")
 
 
 def run_reference(args):
-    import torch
-
     rank = int(os.environ.get('RANK', '0'))
     if rank != 0:
         return
-    C = 8
-    cores = torch.get_num_threads()
-    med, dtype, _, _ = time_cpu_arm(C, args.steps, max(1, args.warmup))
-    nbytes = 2 * algorithmic_bytes(C)
-    value = nbytes / med / 1e9
-    sample = f'one (1,{C},350,350,128) volume per step: conv3d(groups=C) forward + weight gradient, torch CPU {dtype}'
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    r = time_cpu_arm(args.channels, args.steps, max(1, args.warmup))
+    nbytes = sum(2 * algorithmic_bytes(C) for C in args.channels)
+    value = nbytes / r['sec_per_step'] / 1e9
     line = {
-        'impl': 'reference', 'metric': METRIC, 'value': value, 'unit': 'GB/s', 'n_gpus': args.gpus,
-        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': med * 1e3, 'higher_is_better': True,
-        'scaling': 'weak', 'vs_baseline': None, 'dtype': dtype, 'data': 'synthetic',
-        'config': {'workload': f'DWConv + DWConvWGRAD on (1,{C},350,350,128) fp16 channels_last_3d, host cores'},
-        'cpu_baseline': {'value': value, 'unit': 'GB/s', 'cores': cores, 'kind': 'port', 'sample': sample},
-        'e2e': {'value': value, 'unit': 'GB/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
-        'gpu_launches': 0,
+        'impl': 'reference', 'metric': METRIC, 'value': round(value, 3), 'unit': 'GB/s', 'n_gpus': args.gpus,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': round(r['sec_per_step'] * 1e3, 2),
+        'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': r['dtype'], 'data': 'synthetic',
+        'config': sweep_config(args.channels, world),
+        'cpu_baseline': {'value': round(value, 3), 'unit': 'GB/s', 'cores': r['cores'], 'kind': 'port',
+                         'sample': cpu_sample_text(r, args.channels)},
+        'e2e': {'value': round(value, 3), 'unit': 'GB/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0, 'detail': r['per_c'],
     }
     print(json.dumps(line), flush=True)
 
@@ -277,26 +328,122 @@ def make_gpu_inputs(C, device, seed):
     return x, grad, w
 
 
-def run_ours(args):
+class Ctx:
+    """One rank of the benchmark: device, process group."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+
+        from kerops_b200 import _lib
+
+        self.world = int(os.environ.get('WORLD_SIZE', '1'))
+        self.rank = int(os.environ.get('RANK', '0'))
+        self.local = int(os.environ.get('LOCAL_RANK', '0'))
+        if self.world != args.gpus and self.world > 1:
+            raise SystemExit(f'--gpus {args.gpus} but WORLD_SIZE={self.world}')
+        if not torch.cuda.is_available():
+            raise SystemExit('bench.py needs a CUDA device: kerops_b200 has no CPU path')
+        self.dev = torch.device('cuda', self.local)
+        torch.cuda.set_device(self.dev)
+        _lib.load()
+        if self.world > 1:
+            dist.init_process_group('nccl', device_id=self.dev)
+
+    def barrier(self):
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(self, ms):
+        import torch
+        import torch.distributed as dist
+
+        if self.world == 1:
+            return ms
+        t = torch.tensor([ms], device=self.dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def gather_rows(self, row):
+        """One list of floats per rank -> list of rows (rank order) on every rank."""
+        import torch
+        import torch.distributed as dist
+
+        if self.world == 1:
+            return [list(row)]
+        t = torch.tensor(row, device=self.dev, dtype=torch.float64)
+        out = [torch.empty_like(t) for _ in range(self.world)]
+        dist.all_gather(out, t)
+        return [[float(v) for v in o.tolist()] for o in out]
+
+    def close(self):
+        import torch.distributed as dist
+
+        if self.world > 1:
+            dist.destroy_process_group()
+
+
+def reducer_name(reducer, world):
+    return ('push kernel over peer memory' if reducer is not None else 'nccl') if world > 1 else None
+
+
+def breakdown(ctx, names, events):
+    """events: one tuple of len(names)+1 CUDA events per timed step.  Per phase: the mean over the steps of every
+    rank, ms, in rank order."""
+    n = len(names)
+    means = [statistics.mean(ev[i].elapsed_time(ev[i + 1]) for ev in events) for i in range(n)]
+    rows = ctx.gather_rows(means)
+    return {name: [round(r[i], 4) for r in rows] for i, name in enumerate(names)}
+
+
+def small_shape_latency(dev, triton_ops):
+    """Microseconds per call on two small shapes of the reference's test lattice, where a call is launch-bound:
+    200 back-to-back calls between two events."""
+    import torch
+
+    from kerops_b200.ops.conv import DWConv, DWConvWGRAD
+
+    out = {}
+    for (N, C, H, W, D) in [(1, 8, 16, 16, 8), (2, 32, 13, 32, 7)]:
+        g = torch.Generator(device=dev).manual_seed(5)
+        x = torch.randn(N, H, W, D, C, generator=g, device=dev, dtype=torch.float16).permute(0, 4, 1, 2, 3)
+        gr = torch.randn(N, H, W, D, C, generator=g, device=dev, dtype=torch.float16).permute(0, 4, 1, 2, 3)
+        w = ((torch.rand(3, 3, 3, C, generator=g, device=dev) * 2 - 1) / math.sqrt(27)).to(torch.float16)
+        row = {}
+        fns = [('fprop_us', lambda: DWConv(x, w)), ('wgrad_us', lambda: DWConvWGRAD(x, gr))]
+        if triton_ops is not None:
+            fns += [('reference_fprop_us', lambda: triton_ops[0](x, w)), ('reference_wgrad_us', lambda: triton_ops[1](x, gr))]
+        for name, fn in fns:
+            try:
+                for _ in range(10):
+                    fn()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(200):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                row[name] = round(e0.elapsed_time(e1) / 200 * 1e3, 2)
+            except Exception as e:
+                row[name] = f'{type(e).__name__}'
+        out[f'({N},{C},{H},{W},{D})'] = row
+    return out
+
+
+def sweep_record(args, ctx):
+    """The headline sweep; returns the JSON line as a dict (rank 0) or None."""
     import torch
     import torch.distributed as dist
 
     from kerops_b200 import _lib
     from kerops_b200.ops.conv import DWConv, _launch
 
-    world = int(os.environ.get('WORLD_SIZE', '1'))
-    rank = int(os.environ.get('RANK', '0'))
-    local = int(os.environ.get('LOCAL_RANK', '0'))
-    if world != args.gpus and world > 1:
-        raise SystemExit(f'--gpus {args.gpus} but WORLD_SIZE={world}')
-    if not torch.cuda.is_available():
-        raise SystemExit('bench.py needs a CUDA device: kerops_b200 has no CPU path')
-    dev = torch.device('cuda', local)
-    torch.cuda.set_device(dev)
-    _lib.load()
-    if world > 1:
-        dist.init_process_group('nccl', device_id=dev)
-
+    world, rank, dev = ctx.world, ctx.rank, ctx.dev
     channels = args.channels
     data = {C: make_gpu_inputs(C, dev, seed=1000 * rank + C) for C in channels}
     ws = {C: _launch.wgrad_workspace(data[C][0]) for C in channels}
@@ -329,17 +476,11 @@ def run_ours(args):
             else:
                 dist.all_reduce(bucket)
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
     sampler = ClockSampler(dev)
     sampler.start()
     for _ in range(args.warmup):
         step()
-    barrier()
+    ctx.barrier()
     sampler.begin()
     events = []
     t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -347,13 +488,9 @@ def run_ours(args):
     for _ in range(args.steps):
         step(events)
     t_end.record()
-    barrier()
+    ctx.barrier()
     clocks = sampler.stop()
-    total_ms = t_start.elapsed_time(t_end)
-    if world > 1:
-        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
+    total_ms = ctx.max_over_ranks(t_start.elapsed_time(t_end))
     status = _lib.device_status()
 
     peak, peak_kind = measured_peak()
@@ -370,22 +507,30 @@ def run_ours(args):
                                     'frac': round(gbs / peak, 4), 'frac_of_nominal_8000': round(gbs / 8000.0, 4)}
             tot[kind][0] += ms
             tot[kind][1] += algorithmic_bytes(C)
-    # torch.clone of the same tensors, the comparator the reference's README uses
-    clone = {}
-    for C in channels:
-        x = data[C][0]
+
+    def timeit(fn, reps=5):
         for _ in range(2):
-            x.clone()
+            fn()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(5):
-            x.clone()
+        for _ in range(reps):
+            fn()
         e1.record()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / 5
+        return e0.elapsed_time(e1) / reps
+
+    # torch.clone of the same tensors, the comparator the reference's README uses; and the forward pass in the
+    # packed-half accumulate mode (ACCTYPE='float16')
+    clone = {}
+    for C in channels:
+        x, _, w = data[C]
+        ms = timeit(lambda: x.clone())
         clone[str(C)] = {'ms': round(ms, 4), 'gbs': round(algorithmic_bytes(C) / (ms * 1e-3) / 1e9, 1)}
         for kind in ('fprop', 'wgrad'):
             detail[kind][str(C)]['x_clone'] = round(detail[kind][str(C)]['ms'] / ms, 3)
+        ms16 = timeit(lambda: DWConv(x, w, ACCTYPE='float16'))
+        detail['fprop'][str(C)]['acc_float16_ms'] = round(ms16, 4)
+        detail['fprop'][str(C)]['acc_float16_frac'] = round(algorithmic_bytes(C) / (ms16 * 1e-3) / 1e9 / peak, 4)
     detail['clone'] = clone
 
     def roof(kind):
@@ -401,7 +546,7 @@ def run_ours(args):
                           key=lambda kc: detail[kc[0]][str(kc[1])]['ms'])
     dom = detail[dom_kind][str(dom_C)]
     full_size = SHAPE[0] == 350
-    roofline = {'bound': 'hbm', 'kernel': f'{dom_kind}_tma_kernel at C={dom_C}', 'achieved': dom['gbs'], 'peak': peak,
+    roofline = {'bound': 'hbm', 'kernel': f'{dom_kind} pass-1 kernel at C={dom_C}', 'achieved': dom['gbs'], 'peak': peak,
                 'peak_kind': peak_kind, 'unit': 'GB/s', 'frac': dom['frac'],
                 'traffic': NCU_TRAFFIC.get((dom_kind, dom_C)) if full_size else None,
                 'algorithmic_bytes': algorithmic_bytes(dom_C), 'avg_launch_ms': dom['ms']}
@@ -411,36 +556,58 @@ def run_ours(args):
     e2e = measure_e2e(args, channels, dev, world, rank)
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cores = torch.get_num_threads()
-        med, dtype, spent, n_cpu = time_cpu_arm(8, steps=2, warmup=1, min_seconds=8.0)
-        cpu_baseline = {
-            'value': round(2 * algorithmic_bytes(8) / med / 1e9, 3), 'unit': 'GB/s', 'cores': cores, 'kind': 'port',
-            'sample': f'(1,8,350,350,128) only: torch CPU conv3d(groups=8) forward + weight gradient in {dtype}, '
-                      f'median of {n_cpu} steps after 1 warm-up ({spent:.1f} s of CPU work)',
-        }
-    triton_ref = measure_triton_reference(channels, data, dev) if (args.compare_triton and rank == 0 and world == 1) else None
+        r = time_cpu_arm(channels, steps=2, warmup=1, min_seconds=8.0)
+        cpu_baseline = {'value': round(sum(2 * algorithmic_bytes(C) for C in channels) / r['sec_per_step'] / 1e9, 3),
+                        'unit': 'GB/s', 'cores': r['cores'], 'kind': 'port', 'sample': cpu_sample_text(r, channels)}
+    triton_ref = triton_ops = None
+    if args.compare_triton and rank == 0 and world == 1:
+        triton_ref, triton_ops = measure_triton_reference(channels, data, dev)
+    if rank == 0 and world == 1 and not args.no_small:
+        detail['small_shape_latency'] = small_shape_latency(dev, triton_ops)
 
+    line = None
     if rank == 0:
         line = {
             'metric': METRIC, 'value': round(value, 1), 'unit': 'GB/s', 'n_gpus': world, 'steps': args.steps,
             'warmup': args.warmup, 'ms_per_step': round(total_ms / args.steps, 4), 'higher_is_better': True,
             'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f16 products, f32 accumulation', 'data': 'synthetic',
-            'config': {
-                'workload': f'configs[1]+[2]: DWConv then DWConvWGRAD on (1,C,{SHAPE[0]},350,128) fp16 channels_last_3d for C in '
-                            + ','.join(map(str, channels)) + '; one sample per GPU',
-                'l2': 'inputs larger than L2 (smallest tensor 251 MB; 31 GB touched per step)',
-                'parallelism': f'dp{world}' if world > 1 else 'single',
-                'allreduce': ('push kernel over peer memory' if reducer is not None else 'nccl') if world > 1 else None,
-            },
+            'config': sweep_config(channels, world), 'allreduce': reducer_name(reducer, world),
             'roofline': roofline, 'roofline_fprop': roof('fprop'), 'roofline_wgrad': roof('wgrad'),
             'cpu_baseline': cpu_baseline, 'e2e': e2e, 'clocks': clocks,
-            'gpu_launches': (3 * len(channels) + (1 if reducer is not None else 0)) * args.steps, 'detail': detail, 'device_status': status,
+            'gpu_launches': (3 * len(channels) + (1 if reducer is not None else 0)) * args.steps, 'detail': detail,
+            'device_status': status,
         }
         if triton_ref is not None:
             line['reference_triton_on_this_gpu'] = triton_ref
+            try:  # how many times faster than the reference's own kernels on this GPU, per C
+                line['vs_reference_triton'] = {
+                    kind: {str(C): round(triton_ref[kind][str(C)]['ms'] / detail[kind][str(C)]['ms'], 2) for C in channels}
+                    for kind in ('fprop', 'wgrad')}
+            except (KeyError, TypeError):
+                pass
+    return line
+
+
+def run_ours(args):
+    import gc
+
+    import torch
+
+    ctx = Ctx(args)
+    line = sweep_record(args, ctx)
+    if not args.no_sharded and SHAPE[0] == 350:
+        for name, fn in (('dshard', dshard_record), ('dpstep', dpstep_record)):
+            gc.collect()
+            torch.cuda.empty_cache()
+            try:
+                rec = fn(args, ctx, args.sub_steps, max(3, args.sub_warmup))
+            except Exception as e:  # e.g. device memory: report it instead of losing the headline
+                rec = {'error': f'{type(e).__name__}: {e}'[:300]}
+            if line is not None:
+                line[name] = rec
+    if line is not None:
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    ctx.close()
 
 
 def measure_e2e(args, channels, dev, world, rank):
@@ -518,12 +685,12 @@ def measure_triton_reference(channels, data, dev):
 
     ref_root = os.path.join(ROOT, 'baseline', '_ref')
     if not os.path.isdir(os.path.join(ref_root, 'kerops')):
-        return {'unavailable': 'baseline/_ref/kerops not present'}
+        return {'unavailable': 'baseline/_ref/kerops not present'}, None
     sys.path.insert(0, ref_root)
     try:
         from kerops.ops.conv import DWConv as RefDWConv, DWConvWGRAD as RefDWConvWGRAD
     except Exception as e:
-        return {'unavailable': f'{type(e).__name__}: {e}'}
+        return {'unavailable': f'{type(e).__name__}: {e}'}, None
     out = {'fprop': {}, 'wgrad': {}}
     for C in channels:
         x, grad, w = data[C]
@@ -541,26 +708,19 @@ def measure_triton_reference(channels, data, dev):
                 out[name][str(C)] = {'ms': round(ms, 4), 'gbs': round(algorithmic_bytes(C) / (ms * 1e-3) / 1e9, 1)}
             except Exception as e:
                 out[name][str(C)] = {'error': f'{type(e).__name__}: {e}'[:200]}
-    return out
+    return out, (RefDWConv, RefDWConvWGRAD)
 
 
-def run_dshard(args):
+def dshard_record(args, ctx, steps, warmup):
     """configs[3]: one (1, 128, 1400, 350, 128) volume sharded along H over the ranks (1-plane halos exchanged
-    point to point, fp32 weight gradient all-reduced); strong scaling.  A step = forward + weight gradient."""
+    point to point, fp32 weight gradient all-reduced); strong scaling.  A step = forward + weight gradient.
+    Returns the record (on every rank)."""
     import torch
-    import torch.distributed as dist
 
     from kerops_b200 import _lib
     from kerops_b200 import dist as kd
 
-    world = int(os.environ.get('WORLD_SIZE', '1'))
-    rank = int(os.environ.get('RANK', '0'))
-    local = int(os.environ.get('LOCAL_RANK', '0'))
-    dev = torch.device('cuda', local)
-    torch.cuda.set_device(dev)
-    _lib.load()
-    if world > 1:
-        dist.init_process_group('nccl', device_id=dev)
+    world, rank, dev = ctx.world, ctx.rank, ctx.dev
     C, H, W, D = 128, args.dshard_planes, SHAPE[1], SHAPE[2]
     hb, he = kd.shard_planes(H, world, rank)
     Hs = he - hb
@@ -569,91 +729,60 @@ def run_dshard(args):
     xh[:, :, 1:-1].copy_(torch.randn(1, Hs, W, D, C, generator=g, device=dev, dtype=torch.float16).permute(0, 4, 1, 2, 3))
     grad = torch.randn(1, Hs, W, D, C, generator=g, device=dev, dtype=torch.float16).permute(0, 4, 1, 2, 3)
     w = ((torch.rand(3, 3, 3, C, generator=g, device=dev) * 2 - 1) / math.sqrt(27)).to(torch.float16)
-
+    y = torch.empty((1, Hs, W, D, C), dtype=torch.float16, device=dev).permute(0, 4, 1, 2, 3)
     reducer = make_reducer(args, 27 * C, world)
+    names = ['fprop_interior', 'halo_wait', 'fprop_boundary', 'wgrad', 'allreduce']
 
-    class Single:  # one rank: no neighbours, the halo planes stay zero
-        @staticmethod
-        def finish():
-            return None
-
-    def step():
-        if world > 1:
-            fin = kd.exchange_halo(xh)
-            y = kd.hsharded_fprop(xh, w, halo_ready=fin)
-            dw = kd.hsharded_wgrad(xh, grad, halo_ready=lambda: None, reducer=reducer)  # halo already in place
-        else:
-            y = kd.hsharded_fprop(xh, w, halo_ready=Single.finish)
-            dw = kd.hsharded_wgrad(xh, grad, halo_ready=Single.finish, reduce=False)
-        return y, dw
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
+    def step(events=None):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] if events is not None else None
+        kd.hsharded_step(xh, w, grad, y=y, reducer=reducer, events=ev)
+        if events is not None:
+            events.append(ev)
 
     sampler = ClockSampler(dev)
     sampler.start()
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         step()
-    barrier()
+    ctx.barrier()
     sampler.begin()
+    events = []
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        step()
+    for _ in range(steps):
+        step(events)
     e1.record()
-    barrier()
+    ctx.barrier()
     clocks = sampler.stop()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms = ctx.max_over_ranks(e0.elapsed_time(e1))
+    parts = breakdown(ctx, names, events)
     status = _lib.device_status()
     peak, peak_kind = measured_peak()
     nbytes = 2 * 4 * H * W * D * C  # forward + weight gradient over the whole volume
-    value = nbytes * args.steps / (ms * 1e-3) / 1e9
-    if rank == 0:
-        print(json.dumps({
-            'metric': 'DWConv + DWConvWGRAD algorithmic HBM GB/s on one H-sharded (1,128,%d,350,128) fp16 volume' % H,
-            'value': round(value, 1), 'unit': 'GB/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
-            'ms_per_step': round(ms / args.steps, 4), 'higher_is_better': True, 'scaling': 'strong',
-            'vs_baseline': None, 'dtype': 'f16 products, f32 accumulation', 'data': 'synthetic',
-            'config': {'workload': f'configs[3]: (1,128,{H},350,128) split along H over {world} rank(s), 1-plane halos '
-                                   'over NCCL point-to-point, fp32 [27][128] gradient all-reduced ('
-                                   + ('push kernel over peer memory' if reducer is not None else 'nccl') + ')',
-                       'l2': 'inputs larger than L2', 'parallelism': f'hshard{world}'},
-            'roofline': {'bound': 'hbm', 'kernel': 'fprop + wgrad, whole step', 'achieved': round(value / world, 1),
-                         'peak': peak, 'peak_kind': peak_kind, 'unit': 'GB/s', 'frac': round(value / world / peak, 4),
-                         'traffic': None},
-            'clocks': clocks, 'gpu_launches': ((9 if world > 1 else 3) + (1 if reducer is not None else 0)) * args.steps,
-            'device_status': status,
-        }), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    value = nbytes * steps / (ms * 1e-3) / 1e9
+    return {
+        'metric': 'DWConv + DWConvWGRAD algorithmic HBM GB/s on one H-sharded (1,128,%d,350,128) fp16 volume' % H,
+        'value': round(value, 1), 'unit': 'GB/s', 'n_gpus': world, 'steps': steps, 'warmup': warmup,
+        'ms_per_step': round(ms / steps, 4), 'higher_is_better': True, 'scaling': 'strong',
+        'workload': f'configs[3]: (1,128,{H},350,128) split along H over {world} rank(s), 1-plane halos over NCCL '
+                    'point-to-point overlapped with the interior planes, fp32 [27][128] gradient all-reduced',
+        'allreduce': reducer_name(reducer, world), 'per_gpu_frac_of_peak': round(value / world / peak, 4),
+        'peak': peak, 'peak_kind': peak_kind, 'breakdown_ms_per_rank': parts,
+        'gpu_launches_per_step': (5 if world > 1 else 3) + (1 if reducer is not None else 0),
+        'clocks': clocks, 'device_status': status,
+    }
 
 
-def run_dpstep(args):
+def dpstep_record(args, ctx, steps, warmup):
     """configs[4]: data-parallel slice of a training step.  A batch of 8 samples (32, 350, 350, 128) is split by
     sample over the ranks (8, 4, 2, 1 samples per rank on 1, 2, 4, 8 GPUs); a step is DWConv of the local samples,
     DWConvWGRAD against an N(0,1) gradient, and one all-reduce of the fp32 [27][32] weight gradient.  Strong
     scaling: the batch is fixed."""
     import torch
-    import torch.distributed as dist
 
     from kerops_b200 import _lib
     from kerops_b200 import dist as kd
 
-    world = int(os.environ.get('WORLD_SIZE', '1'))
-    rank = int(os.environ.get('RANK', '0'))
-    local = int(os.environ.get('LOCAL_RANK', '0'))
-    dev = torch.device('cuda', local)
-    torch.cuda.set_device(dev)
-    _lib.load()
-    if world > 1:
-        dist.init_process_group('nccl', device_id=dev)
+    world, rank, dev = ctx.world, ctx.rank, ctx.dev
     batch, C = args.dp_batch, 32
     H, W, D = SHAPE
     if batch % world:
@@ -669,54 +798,64 @@ def run_dpstep(args):
     del xs, gs
     gw = torch.Generator(device=dev).manual_seed(77)
     w = ((torch.rand(3, 3, 3, C, generator=gw, device=dev) * 2 - 1) / math.sqrt(27)).to(torch.float16)
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
+    y = torch.empty((n_local, H, W, D, C), dtype=torch.float16, device=dev).permute(0, 4, 1, 2, 3)
     reducer = make_reducer(args, 27 * C, world)
+    names = ['fprop', 'wgrad', 'allreduce']
+
+    def step(events=None):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(names) + 1)] if events is not None else None
+        kd.sample_sharded_step(x, w, grad, reducer=reducer, y=y, events=ev)
+        if events is not None:
+            events.append(ev)
+
     sampler = ClockSampler(dev)
     sampler.start()
-    for _ in range(args.warmup):
-        kd.sample_sharded_step(x, w, grad, reducer=reducer)
-    barrier()
+    for _ in range(warmup):
+        step()
+    ctx.barrier()
     sampler.begin()
+    events = []
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        kd.sample_sharded_step(x, w, grad, reducer=reducer)
+    for _ in range(steps):
+        step(events)
     e1.record()
-    barrier()
+    ctx.barrier()
     clocks = sampler.stop()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms = ctx.max_over_ranks(e0.elapsed_time(e1))
+    parts = breakdown(ctx, names, events)
     status = _lib.device_status()
     peak, peak_kind = measured_peak()
     nbytes = 2 * algorithmic_bytes(C, batch)
-    value = nbytes * args.steps / (ms * 1e-3) / 1e9
-    if rank == 0:
-        print(json.dumps({
-            'metric': 'DWConv + DWConvWGRAD algorithmic HBM GB/s, batch of %d (32,%d,350,128) fp16 samples' % (batch, H),
-            'value': round(value, 1), 'unit': 'GB/s', 'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup,
-            'ms_per_step': round(ms / args.steps, 4), 'higher_is_better': True, 'scaling': 'strong',
-            'vs_baseline': None, 'dtype': 'f16 products, f32 accumulation', 'data': 'synthetic',
-            'config': {'workload': f'configs[4]: batch {batch} x (32,{H},350,128), {n_local} sample(s) per rank; DWConv, '
-                                   'DWConvWGRAD, all-reduce of the fp32 [27][32] gradient ('
-                                   + ('push kernel over peer memory' if reducer is not None else 'nccl') + ')',
-                       'l2': 'inputs larger than L2', 'parallelism': f'dp{world}'},
-            'roofline': {'bound': 'hbm', 'kernel': 'fprop + wgrad, whole step', 'achieved': round(value / world, 1),
-                         'peak': peak, 'peak_kind': peak_kind, 'unit': 'GB/s', 'frac': round(value / world / peak, 4),
-                         'traffic': None},
-            'clocks': clocks, 'gpu_launches': (3 + (1 if reducer is not None else 0)) * args.steps,
-            'device_status': status,
-        }), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    value = nbytes * steps / (ms * 1e-3) / 1e9
+    return {
+        'metric': 'DWConv + DWConvWGRAD algorithmic HBM GB/s, batch of %d (32,%d,350,128) fp16 samples' % (batch, H),
+        'value': round(value, 1), 'unit': 'GB/s', 'n_gpus': world, 'steps': steps, 'warmup': warmup,
+        'ms_per_step': round(ms / steps, 4), 'higher_is_better': True, 'scaling': 'strong',
+        'workload': f'configs[4]: batch {batch} x (32,{H},350,128), {n_local} sample(s) per rank; DWConv, DWConvWGRAD, '
+                    'all-reduce of the fp32 [27][32] gradient',
+        'allreduce': reducer_name(reducer, world), 'per_gpu_frac_of_peak': round(value / world / peak, 4),
+        'peak': peak, 'peak_kind': peak_kind, 'breakdown_ms_per_rank': parts,
+        'gpu_launches_per_step': 3 + (1 if reducer is not None else 0),
+        'clocks': clocks, 'device_status': status,
+    }
+
+
+def run_sharded(args, fn):
+    """--workload dshard / dpstep alone: the record as the JSON line."""
+    ctx = Ctx(args)
+    rec = fn(args, ctx, args.steps, args.warmup)
+    if ctx.rank == 0:
+        rec.update({'vs_baseline': None, 'dtype': 'f16 products, f32 accumulation', 'data': 'synthetic',
+                    'config': {'workload': rec['workload'], 'l2': 'inputs larger than L2',
+                               'parallelism': ('hshard' if fn is dshard_record else 'dp') + str(ctx.world)},
+                    'roofline': {'bound': 'hbm', 'kernel': 'fprop + wgrad, whole step',
+                                 'achieved': round(rec['value'] / ctx.world, 1), 'peak': rec['peak'],
+                                 'peak_kind': rec['peak_kind'], 'unit': 'GB/s', 'frac': rec['per_gpu_frac_of_peak'],
+                                 'traffic': None},
+                    'gpu_launches': rec['gpu_launches_per_step'] * rec['steps']})
+        print(json.dumps(rec), flush=True)
+    ctx.close()
 
 
 def run_fused(args):
@@ -827,6 +966,11 @@ def main():
                     help="how the fp32 weight gradients are summed over the ranks: NCCL, or the library's own "
                          'push/flag/sum kernel over peer memory')
     ap.add_argument('--dshard-planes', type=int, default=1400)
+    ap.add_argument('--no-sharded', action='store_true',
+                    help='sweep workload: skip the dshard / dpstep sub-records')
+    ap.add_argument('--sub-steps', type=int, default=5, help='timed steps of the dshard / dpstep sub-records')
+    ap.add_argument('--sub-warmup', type=int, default=3)
+    ap.add_argument('--no-small', action='store_true', help='skip the small-shape latency measurement')
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--e2e-api', default='step', choices=['step', 'split'],
                     help="'step': one DWConvStepHost call per volume (x is copied once); 'split': DWConvHost and "
@@ -843,9 +987,9 @@ def main():
     if args.impl == 'reference':
         run_reference(args)
     elif args.workload == 'dshard':
-        run_dshard(args)
+        run_sharded(args, dshard_record)
     elif args.workload == 'dpstep':
-        run_dpstep(args)
+        run_sharded(args, dpstep_record)
     elif args.workload == 'fused':
         run_fused(args)
     else:

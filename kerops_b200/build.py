@@ -15,9 +15,9 @@ import sys
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), 'csrc')
 INCLUDE = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 'include')
 LIB = os.path.join(CSRC, 'libkdw.so')
-SOURCES = ['kdw_host.cu', 'dwconv_fprop.cu', 'dwconv_fprop_mma.cu', 'dwconv_wgrad.cu', 'grad_allreduce.cu', 'dwconv_fprop_addstats.cu', 'dwconv_fprop_bnrelu.cu']
+SOURCES = ['kdw_host.cu', 'dwconv_fprop.cu', 'dwconv_fprop_mma.cu', 'dwconv_wgrad.cu', 'dwconv_wgrad_mma.cu', 'grad_allreduce.cu', 'dwconv_fprop_addstats.cu', 'dwconv_fprop_bnrelu.cu']
 HEADERS = [os.path.join(CSRC, h) for h in (
-    'kdw_common.cuh', 'fprop_core.cuh', 'wgrad_core.cuh', 'fprop_variants.inc', 'wgrad_variants.inc')] + [os.path.join(INCLUDE, 'kdw.h')]
+    'kdw_common.cuh', 'mma_patch.cuh', 'fprop_core.cuh', 'wgrad_core.cuh', 'fprop_variants.inc', 'wgrad_variants.inc')] + [os.path.join(INCLUDE, 'kdw.h')]
 NVCC_FLAGS = [
     '-gencode', 'arch=compute_100a,code=sm_100a',
     '-std=c++17', '-O3', '-lineinfo',

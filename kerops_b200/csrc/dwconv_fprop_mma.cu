@@ -26,6 +26,7 @@
 // mbarriers with bounded waits.
 #include "../../include/kdw.h"
 #include "kdw_common.cuh"
+#include "mma_patch.cuh"
 
 namespace kdw {
 
@@ -55,67 +56,6 @@ struct PCfg {
     static_assert(DT + 2 <= 256 && WT + 2 <= 256, "TMA box limits");
 };
 
-// Byte offset inside a 1024-byte aligned tile written by TMA with a swizzle span of SWZ bytes: the 16-byte chunk
-// index within the span (address bits 4..) is XORed with the address bits from bit 7 up - 3 bits for 128, 2 for
-// 64, 1 for 32.  With one voxel per span, the same chunk of 8 (and more) consecutive voxels lands in distinct
-// banks, which is what makes the 16-byte loads of a quarter-warp conflict-free.
-template <int SWZ>
-KDW_HD uint32_t swz(uint32_t off) {
-    return SWZ == 0 ? off : off ^ (((off >> 7) & (uint32_t)(SWZ / 16 - 1)) << 4);
-}
-
-// d = a * b + c (m16n8k16, fp16 operands, fp32 accumulate); ZERO: c = 0.  The four A registers and the four
-// accumulator registers of an mma are register QUADS (consecutive registers) in the machine instruction, the two
-// B registers a pair; Quad / the arrays below are laid out accordingly.
-struct Quad {
-    uint32_t r[4];
-};
-template <bool ZERO>
-__device__ __forceinline__ void mma16816(float (&d)[4], const Quad& a, uint32_t b0, uint32_t b1) {
-    if (ZERO) {
-        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-            "{%10, %10, %10, %10};"
-            : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-            : "r"(a.r[0]), "r"(a.r[1]), "r"(a.r[2]), "r"(a.r[3]), "r"(b0), "r"(b1), "f"(0.f));
-    } else {
-        asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-            "{%0, %1, %2, %3};"
-            : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-            : "r"(a.r[0]), "r"(a.r[1]), "r"(a.r[2]), "r"(a.r[3]), "r"(b0), "r"(b1));
-    }
-}
-
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                 : "memory");
-}
-__device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
-    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
-    return v;
-}
-__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
-    __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
-// A register copy the compiler does not look through.  A 16-byte load delivers the four channel pairs of ONE voxel
-// in a register quad, an mma wants the words of FOUR voxels for one channel pair in a quad: the 4 x 4 transpose
-// between the two is 16 moves, made once per plane step - each copy below has one definition and is used, in the
-// same position of the same quad, by the three mma (a = 2, 1, 0) that read it.
-__device__ __forceinline__ uint32_t reg_copy(uint32_t x) {
-    uint32_t y;
-    asm("mov.b32 %0, %1;" : "=r"(y) : "r"(x));
-    return y;
-}
-
 // One input plane of one unit.  X[r] = the thread's voxel of input row r (r = 0..5: rows w-1 .. w+4 of the unit),
 // four channel-pair words each.  FIN completes plane q-1 with the a=2 taps (written to the staging tile when
 // `store`), MID takes plane q's a=1 taps, then FIN restarts as plane q+1 with the a=0 taps.
@@ -125,18 +65,26 @@ __device__ __forceinline__ uint32_t reg_copy(uint32_t x) {
 // Consecutive mma never touch the same accumulator, so they issue back to back.
 template <class Cfg>
 __device__ __forceinline__ void pg_step(const uint4 (&X)[6], const uint32_t (&Bf)[4][3][2][2], float (&FIN)[4][4],
-                                        float (&MID)[4][4], bool store, uint32_t out_addr0, uint32_t out_addr1) {
+                                        float (&MID)[4][4], bool store, uint32_t out_addr0, uint32_t out_addr1,
+                                        uint32_t zero) {
+#ifdef KDW_PG_PROBE_NOMATH
+    if (store) {
+        sts128(out_addr0, X[1]);
+        sts128(out_addr1, X[3]);
+    }
+    return;
+#endif
     Quad Q[2][4];
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks) {
-        Q[ks][0].r[0] = reg_copy(X[2 * ks].x), Q[ks][0].r[1] = reg_copy(X[2 * ks + 2].x);
-        Q[ks][0].r[2] = reg_copy(X[2 * ks + 1].x), Q[ks][0].r[3] = reg_copy(X[2 * ks + 3].x);
-        Q[ks][1].r[0] = reg_copy(X[2 * ks].y), Q[ks][1].r[1] = reg_copy(X[2 * ks + 2].y);
-        Q[ks][1].r[2] = reg_copy(X[2 * ks + 1].y), Q[ks][1].r[3] = reg_copy(X[2 * ks + 3].y);
-        Q[ks][2].r[0] = reg_copy(X[2 * ks].z), Q[ks][2].r[1] = reg_copy(X[2 * ks + 2].z);
-        Q[ks][2].r[2] = reg_copy(X[2 * ks + 1].z), Q[ks][2].r[3] = reg_copy(X[2 * ks + 3].z);
-        Q[ks][3].r[0] = reg_copy(X[2 * ks].w), Q[ks][3].r[1] = reg_copy(X[2 * ks + 2].w);
-        Q[ks][3].r[2] = reg_copy(X[2 * ks + 1].w), Q[ks][3].r[3] = reg_copy(X[2 * ks + 3].w);
+        Q[ks][0].r[0] = reg_copy(X[2 * ks].x, zero), Q[ks][0].r[1] = reg_copy(X[2 * ks + 2].x, zero);
+        Q[ks][0].r[2] = reg_copy(X[2 * ks + 1].x, zero), Q[ks][0].r[3] = reg_copy(X[2 * ks + 3].x, zero);
+        Q[ks][1].r[0] = reg_copy(X[2 * ks].y, zero), Q[ks][1].r[1] = reg_copy(X[2 * ks + 2].y, zero);
+        Q[ks][1].r[2] = reg_copy(X[2 * ks + 1].y, zero), Q[ks][1].r[3] = reg_copy(X[2 * ks + 3].y, zero);
+        Q[ks][2].r[0] = reg_copy(X[2 * ks].z, zero), Q[ks][2].r[1] = reg_copy(X[2 * ks + 2].z, zero);
+        Q[ks][2].r[2] = reg_copy(X[2 * ks + 1].z, zero), Q[ks][2].r[3] = reg_copy(X[2 * ks + 3].z, zero);
+        Q[ks][3].r[0] = reg_copy(X[2 * ks].w, zero), Q[ks][3].r[1] = reg_copy(X[2 * ks + 2].w, zero);
+        Q[ks][3].r[2] = reg_copy(X[2 * ks + 1].w, zero), Q[ks][3].r[3] = reg_copy(X[2 * ks + 3].w, zero);
     }
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks)
@@ -335,10 +283,10 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
             }
             if (ci & 1u)
                 pg_step<Cfg>(X, Bf, S1[u], S0[u], store, ob + out_off + u * 2 * OUT_ROW2,
-                             ob + out_off + (u * 2 + 1) * OUT_ROW2);
+                             ob + out_off + (u * 2 + 1) * OUT_ROW2, wt.zero);
             else
                 pg_step<Cfg>(X, Bf, S0[u], S1[u], store, ob + out_off + u * 2 * OUT_ROW2,
-                             ob + out_off + (u * 2 + 1) * OUT_ROW2);
+                             ob + out_off + (u * 2 + 1) * OUT_ROW2, wt.zero);
         }
         if (store) {
             fence_proxy_async_smem();  // the tile must be visible to the TMA store

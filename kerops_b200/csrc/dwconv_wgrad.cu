@@ -315,7 +315,16 @@ static const WgradVariant g_wgrad_variants[] = {
 #include "wgrad_variants.inc"
 };
 #undef KDW_VARIANT
-static const int g_n_wgrad_variants = (int)(sizeof(g_wgrad_variants) / sizeof(g_wgrad_variants[0]));
+static const int g_n_table_wgrad_variants = (int)(sizeof(g_wgrad_variants) / sizeof(g_wgrad_variants[0]));
+
+// tensor-core variants (dwconv_wgrad_mma.cu) are numbered after the table
+int wgrad_mma_variants();
+int wgrad_mma_variant_channels(int which);
+int launch_wgrad_mma_variant(int which, const void* x, const void* grad, float* ws, int64_t ws_rows, int64_t N, int64_t C,
+                             int64_t Hx, int64_t W, int64_t D, int64_t xsN, int64_t xsH, int64_t xsW, int64_t Hg,
+                             int64_t gsN, int64_t gsH, int64_t gsW, int h_begin, int h_end, int g_h0,
+                             cudaStream_t stream, int* rows_used);
+static int n_wgrad_variants() { return g_n_table_wgrad_variants + wgrad_mma_variants(); }
 
 // Built-in choice: per channel count a short list of candidates with their time relative to the best one, measured
 // on B200 at (1,C,350,350,128) (15 consumer warps on wide-w tiles win for C >= 32; C <= 16 runs on 8-channel
@@ -386,8 +395,8 @@ static int wgrad_dispatch(const void* x, const void* grad, void* workspace, int6
         set_error("wgrad: workspace must be 16-byte aligned");
         return KDW_ERR_ALIGN;
     }
-    if (tune < 0 || tune > g_n_wgrad_variants) {
-        set_error("wgrad: tune=%d names no kernel variant (1..%d)", tune, g_n_wgrad_variants);
+    if (tune < 0 || tune > n_wgrad_variants()) {
+        set_error("wgrad: tune=%d names no kernel variant (1..%d)", tune, n_wgrad_variants());
         return KDW_ERR_TUNE;
     }
     int rc = 0;
@@ -422,15 +431,20 @@ static int wgrad_dispatch(const void* x, const void* grad, void* workspace, int6
         rows = (int)blocks;
     } else {
         const int id = tune ? tune : auto_wgrad_variant(C, W, D);
-        const WgradVariant& v = g_wgrad_variants[id - 1];
-        if (C % v.cs != 0) {
-            set_error("wgrad: variant %d works on %d-channel slices, C=%lld is not a multiple", id, v.cs,
-                      (long long)C);
-            return KDW_ERR_TUNE;
+        if (id > g_n_table_wgrad_variants) {
+            rc = launch_wgrad_mma_variant(id - g_n_table_wgrad_variants - 1, x, grad, ws, rows_cap, N, C, Hx, W, D, xsN,
+                                          xsH, xsW, Hg, gsN, gsH, gsW, (int)h_begin, (int)h_end, (int)g_h0, st, &rows);
+        } else {
+            const WgradVariant& v = g_wgrad_variants[id - 1];
+            if (C % v.cs != 0) {
+                set_error("wgrad: variant %d works on %d-channel slices, C=%lld is not a multiple", id, v.cs,
+                          (long long)C);
+                return KDW_ERR_TUNE;
+            }
+            WgradArgs a{x,   grad, ws,  rows_cap, N,   C,          Hx,         W,          D,  xsN, xsH,
+                        xsW, Hg,   gsN, gsH,      gsW, (int)h_begin, (int)h_end, (int)g_h0, st};
+            rc = v.f(a, &rows);
         }
-        WgradArgs a{x,   grad, ws,  rows_cap, N,   C,          Hx,         W,          D,  xsN, xsH,
-                    xsW, Hg,   gsN, gsH,      gsW, (int)h_begin, (int)h_end, (int)g_h0, st};
-        rc = v.f(a, &rows);
         if (rc) return rc;
     }
     wgrad_reduce_kernel<<<(KC + 3) / 4, 128, 0, st>>>(ws, rows, KC, dw_f32, (__half*)dw_f16);
@@ -518,7 +532,7 @@ static int wgrad_static_dispatch(const void* x, const void* grad, float* dw_f32,
 
 extern "C" {
 
-int kdw_wgrad_variants(void) { return kdw::g_n_wgrad_variants; }
+int kdw_wgrad_variants(void) { return kdw::n_wgrad_variants(); }
 
 int kdw_wgrad_auto_variant(int64_t C, int64_t W, int64_t D) {
     if (C < 8 || (C & (C - 1)) != 0 || W <= 0 || D <= 0) return 0;
@@ -526,7 +540,8 @@ int kdw_wgrad_auto_variant(int64_t C, int64_t W, int64_t D) {
 }
 
 int kdw_wgrad_variant_channels(int id) {
-    if (id < 1 || id > kdw::g_n_wgrad_variants) return KDW_ERR_TUNE;
+    if (id < 1 || id > kdw::n_wgrad_variants()) return KDW_ERR_TUNE;
+    if (id > kdw::g_n_table_wgrad_variants) return kdw::wgrad_mma_variant_channels(id - kdw::g_n_table_wgrad_variants - 1);
     return kdw::g_wgrad_variants[id - 1].cs;
 }
 

@@ -71,7 +71,7 @@ int KernelSetup::get(const void* kernel, int threads, int smem, int* sms_out, in
     return 0;
 }
 
-static WaitTest g_wait_test = {2000000000ull, -1};
+static WaitTest g_wait_test = {2000000000ull, -1, 0u};
 WaitTest wait_test() { return g_wait_test; }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

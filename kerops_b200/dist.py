@@ -144,6 +144,8 @@ def exchange_halo(x_halo, group=None):
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     Hs = x_halo.shape[2] - 2
+    # a rank without planes would send its halo plane as if it were data: every rank must own at least one plane
+    assert Hs >= 1, f'H-sharding needs at least one owned plane per rank (this rank has {Hs}; H < world?)'
     phys = x_halo.permute(0, 2, 3, 4, 1)  # (N, Hs+2, W, D, C) contiguous view
     ops = []
     # planes are contiguous only within one sample, so a plane of every sample is sent as one strided tensor
@@ -182,6 +184,7 @@ def hsharded_fprop(x_halo, weight, group=None, ops=None, halo_ready=None):
     ops = ops or CudaOps()
     N, C, Hp, W, D = x_halo.shape
     Hs = Hp - 2
+    assert Hs >= 1, 'H-sharding needs at least one owned plane per rank'
     y = torch.empty((N, Hs, W, D, C), dtype=x_halo.dtype, device=x_halo.device).permute(0, 4, 1, 2, 3)
     finish = halo_ready if halo_ready is not None else exchange_halo(x_halo, group)
     if Hs > 2:
@@ -200,6 +203,7 @@ def hsharded_wgrad(x_halo, grad, group=None, ops=None, halo_ready=None, reduce=T
     grad: (N, C, Hs, W, D), the owned planes only.  `reducer`: a GradPushAllReduce to use instead of NCCL."""
     ops = ops or CudaOps()
     Hs = x_halo.shape[2] - 2
+    assert Hs >= 1, 'H-sharding needs at least one owned plane per rank'
     finish = halo_ready if halo_ready is not None else exchange_halo(x_halo, group)
     dw = None
     if Hs > 2:
@@ -214,14 +218,63 @@ def hsharded_wgrad(x_halo, grad, group=None, ops=None, halo_ready=None, reduce=T
     return dw
 
 
-def sample_sharded_step(x, weight, grad, group=None, ops=None, reducer=None):
+def _mark(events, i):
+    if events is not None:
+        events[i].record()
+
+
+def hsharded_step(x_halo, weight, grad, y=None, group=None, ops=None, reducer=None, events=None):
+    """Forward pass and weight gradient of the local H-shard as ONE step: the halo exchange is started first and
+    overlaps with the forward pass over the planes that do not touch the halo; the two boundary planes follow; the
+    weight gradient then needs a single launch over all owned planes, because the halo is in place by then; its
+    fp32 result is all-reduced.  x_halo: (N, C, Hs+2, W, D), grad: (N, C, Hs, W, D).  Returns (y, dw_fp32).
+    `events`: six CUDA events recorded on the current stream at the phase boundaries (start, interior forward
+    done, halo arrived, boundary forward done, weight gradient done, all-reduce done)."""
+    ops = ops or CudaOps()
+    N, C, Hp, W, D = x_halo.shape
+    Hs = Hp - 2
+    assert Hs >= 1, 'H-sharding needs at least one owned plane per rank'
+    if y is None:
+        y = torch.empty((N, Hs, W, D, C), dtype=x_halo.dtype, device=x_halo.device).permute(0, 4, 1, 2, 3)
+    sharded = dist.is_initialized() and dist.get_world_size(group) > 1
+    _mark(events, 0)
+    if sharded and Hs > 2:
+        finish = exchange_halo(x_halo, group)
+        ops.fprop_range(x_halo, weight, y, 2, Hs, 1)  # planes that do not touch the halo
+        _mark(events, 1)
+        finish()
+        _mark(events, 2)
+        ops.fprop_range(x_halo, weight, y, 1, 2, 1)
+        ops.fprop_range(x_halo, weight, y, Hs, Hs + 1, 1)
+    else:
+        _mark(events, 1)
+        if sharded:
+            exchange_halo(x_halo, group)()
+        _mark(events, 2)
+        ops.fprop_range(x_halo, weight, y, 1, Hs + 1, 1)
+    _mark(events, 3)
+    dw = ops.wgrad_range(x_halo, grad, 1, Hs + 1, 1)
+    _mark(events, 4)
+    if sharded:
+        dw = _reduce(dw, group, reducer)
+    _mark(events, 5)
+    return y, dw
+
+
+def sample_sharded_step(x, weight, grad, group=None, ops=None, reducer=None, y=None, events=None):
     """Data-parallel slice of a training step: y = DWConv(x) for the local samples and the weight gradient of
-    the global batch.  Returns (y, dw_fp32): the local output and the all-reduced fp32 [3,3,3,C] gradient."""
+    the global batch.  Returns (y, dw_fp32): the local output and the all-reduced fp32 [3,3,3,C] gradient.
+    `events`: four CUDA events recorded at the phase boundaries (start, forward, weight gradient, all-reduce)."""
     ops = ops or CudaOps()
     N, C, H, W, D = x.shape
-    y = torch.empty((N, H, W, D, C), dtype=x.dtype, device=x.device).permute(0, 4, 1, 2, 3)
+    if y is None:
+        y = torch.empty((N, H, W, D, C), dtype=x.dtype, device=x.device).permute(0, 4, 1, 2, 3)
+    _mark(events, 0)
     ops.fprop_range(x, weight, y, 0, H, 0)
+    _mark(events, 1)
     dw = ops.wgrad_range(x, grad, 0, H, 0)
+    _mark(events, 2)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dw = _reduce(dw, group, reducer)
+    _mark(events, 3)
     return y, dw

@@ -79,6 +79,11 @@ def _worker(rank, world, port, shape, out_dir):
                                           grad[rank::world].contiguous(memory_format=torch.channels_last_3d), ops=ops,
                                           reducer=reducer)
         assert calls == [27 * C, 27 * C] and torch.equal(dw_r, dw) and torch.equal(dws_r, dws)
+        # ---- forward + weight gradient as one step (halo exchange overlapped, one weight-gradient range)
+        xh4 = kd.alloc_halo_volume(N, C, he - hb, W, D, 'cpu')
+        xh4[:, :, 1:-1] = x[:, :, hb:he]
+        y_s, dw_s = kd.hsharded_step(xh4, w, gl, ops=ops)
+        assert torch.equal(y_s, y) and to.rel_l2(dw_s, dw) <= 1e-6
         torch.save({'hb': hb, 'he': he, 'y': y.contiguous(), 'dw': dw, 'ys': ys.contiguous(), 'dws': dws,
                     'halo_lo': xh[:, :, 0].clone(), 'halo_hi': xh[:, :, -1].clone()},
                    os.path.join(out_dir, f'rank{rank}.pt'))
@@ -110,6 +115,27 @@ def test_sharded_paths_match_single_device(tmp_path, shape, world):
         assert torch.equal(res['ys'], y_full[r::world])
         assert to.rel_l2(res['dws'], dw_full) <= 1e-5
     assert covered == H
+
+
+def _worker_empty_shard(rank, world, port):
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        hb, he = kd.shard_planes(1, world, rank)  # H = 1 < world: rank 1 owns no plane
+        xh = kd.alloc_halo_volume(1, 8, he - hb, 3, 4, 'cpu')
+        if he - hb == 0:
+            with pytest.raises(AssertionError, match='at least one owned plane'):
+                kd.exchange_halo(xh)
+            with pytest.raises(AssertionError, match='at least one owned plane'):
+                kd.hsharded_step(xh, torch.zeros(3, 3, 3, 8).half(), xh[:, :, 1:-1], ops=OracleOps())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_empty_shard_is_rejected():
+    """H < world would hand a rank zero planes; the helpers refuse instead of sending a halo plane as data."""
+    mp.spawn(_worker_empty_shard, args=(2, _free_port()), nprocs=2, join=True)
 
 
 def test_shard_planes_partitions_the_axis():
