@@ -528,9 +528,13 @@ def sweep_record(args, ctx):
         clone[str(C)] = {'ms': round(ms, 4), 'gbs': round(algorithmic_bytes(C) / (ms * 1e-3) / 1e9, 1)}
         for kind in ('fprop', 'wgrad'):
             detail[kind][str(C)]['x_clone'] = round(detail[kind][str(C)]['ms'] / ms, 3)
-        ms16 = timeit(lambda: DWConv(x, w, ACCTYPE='float16'))
-        detail['fprop'][str(C)]['acc_float16_ms'] = round(ms16, 4)
-        detail['fprop'][str(C)]['acc_float16_frac'] = round(algorithmic_bytes(C) / (ms16 * 1e-3) / 1e9 / peak, 4)
+        try:
+            ms16 = timeit(lambda: DWConv(x, w, ACCTYPE='float16'))
+            detail['fprop'][str(C)]['acc_float16_ms'] = round(ms16, 4)
+            detail['fprop'][str(C)]['acc_float16_frac'] = round(algorithmic_bytes(C) / (ms16 * 1e-3) / 1e9 / peak, 4)
+        except Exception as e:  # e.g. a forced kernel variant without that mode
+            detail['fprop'][str(C)]['acc_float16_ms'] = f'{type(e).__name__}'
+            _lib.load().kdw_last_error()
     detail['clone'] = clone
 
     def roof(kind):

@@ -38,9 +38,15 @@ struct PCfg {
     static constexpr int UPW = UPW_;  // units (along w) per warp; they share the weight fragments
     static constexpr int ST = ST_;    // input pipeline stages
     static constexpr int NG = CS / 8;  // channel groups of 8 (one 16-byte chunk of a voxel)
-    static constexpr int NCW = NG * (WW / UPW) * WD;  // consumer warps; warp NCW loads, warp NCW + 1 stores
+    static constexpr int NCW = NG * (WW / UPW) * WD;  // consumer warps
     static constexpr int NT = NCW * 32;
-    static constexpr int NTHREADS = NT + 64;
+    // Warps 0-3 form the helper warpgroup (warp 0 loads, warp 1 stores, 2 and 3 leave at once), the consumer warps
+    // follow.  The kernel is compiled for 168 registers per thread (12 warps); the helper warpgroup then hands
+    // registers back (setmaxnreg) and the two consumer warpgroups take them, which this kernel needs: with 168 the
+    // weight fragments and accumulators spill and every mma drags register moves along.
+    static constexpr int NHELP = 4;
+    static constexpr int NTHREADS = NT + NHELP * 32;
+    static constexpr int REGS_HELPER = 40, REGS_CONSUMER = 232;
     static constexpr int WT = 4 * WW;
     static constexpr int DT = 16 * WD;
     static constexpr int VOXB = CS * 2;  // bytes of a voxel in shared memory
@@ -49,9 +55,10 @@ struct PCfg {
     static constexpr int IN_STRIDE = (IN_BYTES + 1023) / 1024 * 1024;
     static constexpr int OUT_BYTES = WT * DT * VOXB;
     static constexpr int OUT_STRIDE = (OUT_BYTES + 1023) / 1024 * 1024;
-    static constexpr int SMEM = ST * IN_STRIDE + 2 * OUT_STRIDE + 16 * ST + 32 + 4 * ST + 1024;
+    static constexpr int SMEM = ST * IN_STRIDE + 2 * OUT_STRIDE + 16 * ST + 32 + 4 * ST + 256 + 1024;
     static_assert(CS == 8 || CS == 16 || CS == 32 || CS == 64, "a voxel must be one swizzle span (or 16 bytes)");
     static_assert(WW % UPW == 0, "units per warp");
+    static_assert(NCW == 8, "register hand-over is laid out for two consumer warpgroups");
     static_assert(NTHREADS <= 1024, "thread count");
     static_assert(DT + 2 <= 256 && WT + 2 <= 256, "TMA box limits");
 };
@@ -67,7 +74,7 @@ template <class Cfg>
 __device__ __forceinline__ void pg_step(const uint4 (&X)[6], const uint32_t (&Bf)[4][3][2][2], float (&FIN)[4][4],
                                         float (&MID)[4][4], bool store, uint32_t out_addr0, uint32_t out_addr1,
                                         uint32_t zero) {
-#ifdef KDW_PG_PROBE_NOMATH
+#if defined(KDW_PG_PROBE) && KDW_PG_PROBE == 1
     if (store) {
         sts128(out_addr0, X[1]);
         sts128(out_addr1, X[3]);
@@ -86,14 +93,23 @@ __device__ __forceinline__ void pg_step(const uint4 (&X)[6], const uint32_t (&Bf
         Q[ks][3].r[0] = reg_copy(X[2 * ks].w, zero), Q[ks][3].r[1] = reg_copy(X[2 * ks + 2].w, zero);
         Q[ks][3].r[2] = reg_copy(X[2 * ks + 1].w, zero), Q[ks][3].r[3] = reg_copy(X[2 * ks + 3].w, zero);
     }
+#if defined(KDW_PG_PROBE) && KDW_PG_PROBE == 2
+    if (store) {
+        sts128(out_addr0, make_uint4(Q[0][0].r[0] ^ Q[1][0].r[0], Q[0][1].r[1] ^ Q[1][1].r[1], Q[0][2].r[2] ^ Q[1][2].r[2], Q[0][3].r[3] ^ Q[1][3].r[3]));
+        sts128(out_addr1, make_uint4(Q[0][0].r[1] ^ Q[1][0].r[2], Q[0][1].r[2] ^ Q[1][1].r[3], Q[0][2].r[3] ^ Q[1][2].r[0], Q[0][3].r[0] ^ Q[1][3].r[1]));
+    }
+    return;
+#endif
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks)
 #pragma unroll
         for (int cp = 0; cp < 4; ++cp) mma16816<false>(FIN[cp], Q[ks][cp], Bf[cp][2][ks][0], Bf[cp][2][ks][1]);
+#if !(defined(KDW_PG_PROBE) && KDW_PG_PROBE == 3)
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks)
 #pragma unroll
         for (int cp = 0; cp < 4; ++cp) mma16816<false>(MID[cp], Q[ks][cp], Bf[cp][1][ks][0], Bf[cp][1][ks][1]);
+#endif
     if (store) {
         uint4 o0, o1;  // block row g: outputs (t>>1, t&1) of block (bw=0); row g+8: the same of block (bw=1)
         o0.x = pack_h2(FIN[0][0], FIN[0][1]);
@@ -107,10 +123,77 @@ __device__ __forceinline__ void pg_step(const uint4 (&X)[6], const uint32_t (&Bf
         sts128(out_addr0, o0);
         sts128(out_addr1, o1);
     }
+#if !(defined(KDW_PG_PROBE) && KDW_PG_PROBE == 3)
 #pragma unroll
     for (int cp = 0; cp < 4; ++cp) mma16816<true>(FIN[cp], Q[0][cp], Bf[cp][0][0][0], Bf[cp][0][0][1]);
 #pragma unroll
     for (int cp = 0; cp < 4; ++cp) mma16816<false>(FIN[cp], Q[1][cp], Bf[cp][0][1][0], Bf[cp][0][1][1]);
+#endif
+}
+
+// Schedule position of the store warp, kept in shared memory like ProdState (the helper warps run on 40 registers).
+struct StoreState {
+    StepIter it;
+    uint32_t issued, retired;
+    int done;
+};
+
+// Issues the copy of the next input plane (or the end marker) into the next stage, waiting for the stage to be
+// free.  The position in the schedule lives in shared memory (ProdState).
+template <class Cfg>
+__device__ __forceinline__ void pg_produce(ProdState* ps, const Sched& s, const CUtensorMap& tmx, uint32_t in0,
+                                           uint32_t full0, uint32_t empty0, uint32_t desc0, int* status, const WaitTest& wt) {
+    constexpr int ST = Cfg::ST;
+    const uint32_t pi = ps->pi;
+    if (wt.stop_after >= 0 && (int)pi >= wt.stop_after) {  // test hook: the consumers' wait runs out
+        ps->done = 1;
+        return;
+    }
+    const uint32_t st = pi % ST;
+    if (pi >= ST && !mbar_wait_bounded(empty0 + 8 * st, ((pi / ST) & 1u) ^ 1u, wt.limit_ns)) {
+        atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
+        const uint32_t first = pi > ST ? pi - ST : 0;  // copies in flight still target this CTA's shared memory
+        for (uint32_t k = first; k < pi; ++k) (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u, wt.limit_ns);
+        ps->done = 1;
+        return;
+    }
+    StepIter it = ps->it;
+    if (!it.active) {  // end marker: completes the stage's barrier without a copy
+        st_shared_u32(desc0 + 4 * st, 0xffffffffu);
+        mbar_arrive(full0 + 8 * st);
+        ps->done = 1;
+        return;
+    }
+    st_shared_u32(desc0 + 4 * st, ((uint32_t)it.g.c0 << 8) | (it.q - 1 >= it.g.hb ? 1u : 0u));
+    mbar_expect_tx(full0 + 8 * st, Cfg::IN_BYTES);
+    tma_load_5d(status, in0 + st * Cfg::IN_STRIDE, &tmx, full0 + 8 * st, it.g.c0, it.g.d0 - 1, it.g.w0 - 1, it.q, it.g.n);
+    it.next(s);
+    ps->it = it;
+    ps->pi = pi + 1;
+}
+
+// Stores every finished plane of the CTA's range: waits until all consumer warps have staged it, issues the TMA
+// store, and hands the staging tile back once the store has read it.
+template <class Cfg>
+__device__ __forceinline__ void pg_store(StoreState* ss, const Sched& s, const CUtensorMap& tmy, uint32_t out0,
+                                         uint32_t staged0, uint32_t ofree0, int y_h0, int* status, const WaitTest& wt) {
+    StepIter it = ss->it;
+    uint32_t oc = 0;
+    while (it.active) {
+        if (it.q - 1 >= it.g.hb) {
+            const uint32_t b = oc & 1u;
+            if (!mbar_wait_bounded(staged0 + 8 * b, (oc >> 1) & 1u, wt.limit_ns)) {
+                atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
+                break;
+            }
+            tma_store_5d(status, &tmy, out0 + b * Cfg::OUT_STRIDE, it.g.c0, it.g.d0, it.g.w0, it.q - 1 - y_h0, it.g.n);
+            tma_commit();
+            tma_wait_read_all();  // the store has read the tile: the consumers may overwrite it
+            mbar_arrive(ofree0 + 8 * b);
+            ++oc;
+        }
+        it.next(s);
+    }
 }
 
 template <class Cfg>
@@ -149,73 +232,47 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
     }
     __syncthreads();  // the only CTA-wide barrier
 
-    if (warp == NCW) {
-        // ---------------- load warp: one lane streams the input planes of the CTA's range ----------------
+    ProdState* ps = reinterpret_cast<ProdState*>(smem_raw + ((desc0 + 4 * ST + 15) / 16 * 16 - smem_u32(smem_raw)));
+    StoreState* ss = reinterpret_cast<StoreState*>(reinterpret_cast<unsigned char*>(ps) + 128);
+    if (warp == 0 && lane == 0) {
+        ps->it.init(s, (int)blockIdx.x, (int)gridDim.x);
+        ps->pi = 0;
+        ps->done = 0;
+    }
+    if (warp == 1 && lane == 0) {
+        ss->it.init(s, (int)blockIdx.x, (int)gridDim.x);
+        ss->issued = ss->retired = 0;
+        ss->done = 0;
+    }
+    __syncwarp();
+    if (warp < Cfg::NHELP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_HELPER));
         if (lane != 0) return;
-        StepIter it;
-        it.init(s, (int)blockIdx.x, (int)gridDim.x);
-        uint32_t pi = 0;
-        bool ok = true;
-        while (true) {
-            if (wt.stop_after >= 0 && (int)pi >= wt.stop_after) return;  // test hook: the consumers' wait runs out
-            const uint32_t st = pi % ST;
-            if (pi >= ST) ok = mbar_wait_bounded(empty0 + 8 * st, ((pi / ST) & 1u) ^ 1u, wt.limit_ns);
-            if (!ok) break;
-            if (!it.active) {  // end marker: completes the stage's barrier without a copy
-                st_shared_u32(desc0 + 4 * st, 0xffffffffu);
-                mbar_arrive(full0 + 8 * st);
-                break;
-            }
-            st_shared_u32(desc0 + 4 * st, ((uint32_t)it.g.c0 << 8) | (it.q - 1 >= it.g.hb ? 1u : 0u));
-            mbar_expect_tx(full0 + 8 * st, Cfg::IN_BYTES);
-            tma_load_5d(status, in0 + st * Cfg::IN_STRIDE, &tmx, full0 + 8 * st, it.g.c0, it.g.d0 - 1, it.g.w0 - 1, it.q,
-                        it.g.n);
-            ++pi;
-            it.next(s);
-        }
-        if (!ok) {
-            atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
-            const uint32_t first = pi > ST ? pi - ST : 0;
-            for (uint32_t k = first; k < pi; ++k) (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u, wt.limit_ns);
+        if (warp == 0) {
+            // ---------------- load warp: one lane streams the input planes of the CTA's range ----------------
+            while (!ps->done) pg_produce<Cfg>(ps, s, tmx, in0, full0, empty0, desc0, status, wt);
+        } else if (warp == 1) {
+            // ---------------- store warp: one TMA store per finished plane of the tile ----------------
+            pg_store<Cfg>(ss, s, tmy, out0, staged0, ofree0, y_h0, status, wt);
+            tma_wait_all();
         }
         return;
     }
-    if (warp == NCW + 1) {
-        // ---------------- store warp: one TMA store per finished plane of the tile ----------------
-        if (lane != 0) return;
-        StepIter it;
-        it.init(s, (int)blockIdx.x, (int)gridDim.x);
-        uint32_t oc = 0;
-        while (it.active) {
-            if (it.q - 1 >= it.g.hb) {
-                const uint32_t b = oc & 1u;
-                if (!mbar_wait_bounded(staged0 + 8 * b, (oc >> 1) & 1u, wt.limit_ns)) {
-                    atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
-                    break;
-                }
-                tma_store_5d(status, &tmy, out0 + b * Cfg::OUT_STRIDE, it.g.c0, it.g.d0, it.g.w0, it.q - 1 - y_h0, it.g.n);
-                tma_commit();
-                tma_wait_read_all();  // the store has read the tile: the consumers may overwrite it
-                mbar_arrive(ofree0 + 8 * b);
-                ++oc;
-            }
-            it.next(s);
-        }
-        tma_wait_all();
-        return;
-    }
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_CONSUMER));
 
     // ---------------- consumer warps ----------------
-    const int ng = warp % Cfg::NG;                // channel group
-    const int uwg = (warp / Cfg::NG) % (Cfg::WW / UPW);  // group of UPW units along w
-    const int ud = warp / (Cfg::NG * (Cfg::WW / UPW));
+    const int cw = warp - Cfg::NHELP;
+    const int ng = cw % Cfg::NG;                // channel group
+    const int uwg = (cw / Cfg::NG) % (Cfg::WW / UPW);  // group of UPW units along w
+    const int ud = cw / (Cfg::NG * (Cfg::WW / UPW));
     const int g = lane >> 2, t = lane & 3;
     // Shared-memory offsets of this thread's voxels.  Input row r of unit u: w index 4*(uwg*UPW+u) + r, d index
     // 16*ud + 2g + t; output voxel k of unit u: w index 4*(uwg*UPW+u) + 2k + (t>>1), d index 16*ud + 2g + (t&1).
     // Rows four apart (and units, and the two output rows) differ by a whole number of swizzle periods, so their
     // offsets differ by a constant: four input offsets and one output offset are kept in registers.
     constexpr uint32_t IN_ROW4 = 4 * (Cfg::DT + 2) * Cfg::VOXB, OUT_ROW2 = 2 * Cfg::DT * Cfg::VOXB;
-    static_assert(Cfg::SWZ == 0 || (IN_ROW4 % (8 * Cfg::SWZ) == 0 && OUT_ROW2 % (8 * Cfg::SWZ) == 0),
+    constexpr uint32_t SWZ_PERIOD = 8 * (Cfg::SWZ ? Cfg::SWZ : 1);
+    static_assert(Cfg::SWZ == 0 || (IN_ROW4 % SWZ_PERIOD == 0 && OUT_ROW2 % SWZ_PERIOD == 0),
                   "row steps must preserve the swizzle phase");
     uint32_t in_off[4], out_off;
 #pragma unroll
@@ -230,15 +287,18 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
 
     uint32_t ci = 0, oc = 0;
     int cur_c0 = -1;
-    while (true) {
+    // One plane step; FINS / MIDS are the two accumulator sets in the roles of this step.  Returns false when the
+    // warp is done (no more planes, or a wait ran out).  The loop below calls it with the sets swapped every other
+    // step, so the role change costs neither a branch nor a register move.
+    auto plane_step = [&](float(&FINS)[UPW][4][4], float(&MIDS)[UPW][4][4]) -> bool {
         const uint32_t st = ci % ST;
         const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u, wt.limit_ns);
         if (__any_sync(0xffffffffu, !ok)) {
             if (lane == 0) atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
-            break;
+            return false;
         }
         const uint32_t dsc = ld_shared_u32(desc0 + 4 * st);
-        if (dsc == 0xffffffffu) break;  // the load warp has no more planes
+        if (dsc == 0xffffffffu) return false;  // the load warp has no more planes
         const int c0 = (int)(dsc >> 8);
         if (c0 != cur_c0) {
             // new channel slice: B[(slot, cc), (out, cc')] for this thread's column n = g -> out = g >> 1, cc' = g & 1
@@ -269,7 +329,7 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
             const bool free_ok = mbar_wait_bounded(ofree0 + 8 * (oc & 1u), ((oc >> 1) - 1u) & 1u, wt.limit_ns);
             if (__any_sync(0xffffffffu, !free_ok)) {
                 if (lane == 0) atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
-                break;
+                return false;
             }
         }
 #pragma unroll
@@ -281,12 +341,8 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty0 + 8 * st);  // the values are in registers: the stage can be refilled
             }
-            if (ci & 1u)
-                pg_step<Cfg>(X, Bf, S1[u], S0[u], store, ob + out_off + u * 2 * OUT_ROW2,
-                             ob + out_off + (u * 2 + 1) * OUT_ROW2, wt.zero);
-            else
-                pg_step<Cfg>(X, Bf, S0[u], S1[u], store, ob + out_off + u * 2 * OUT_ROW2,
-                             ob + out_off + (u * 2 + 1) * OUT_ROW2, wt.zero);
+            pg_step<Cfg>(X, Bf, FINS[u], MIDS[u], store, ob + out_off + u * 2 * OUT_ROW2,
+                         ob + out_off + (u * 2 + 1) * OUT_ROW2, wt.zero);
         }
         if (store) {
             fence_proxy_async_smem();  // the tile must be visible to the TMA store
@@ -295,6 +351,9 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
             ++oc;
         }
         ++ci;
+        return true;
+    };
+    while (plane_step(S0, S1) && plane_step(S1, S0)) {
     }
 }
 
@@ -344,19 +403,15 @@ struct PgVariant {
     int cs, dt, wt;
     PgLaunch f;
 };
-// PCfg<CS, WW, WD, UPW, ST>: tile 4*WW x 16*WD voxels (w, d), CS channels
+// PCfg<CS, WW, WD, UPW, ST>: tile 4*WW x 16*WD voxels (w, d), CS channels; 8 consumer warps, two units each
 #define KDW_PG(CS, WW, WD, UPW, ST) {CS, 16 * WD, 4 * WW, &launch_fprop_pg<PCfg<CS, WW, WD, UPW, ST>>}
 static const PgVariant g_pg_variants[] = {
-    KDW_PG(64, 2, 1, 1, 4),  // 0: 16 consumer warps, tile 8 x 16
-    KDW_PG(64, 2, 1, 2, 4),  // 1: 8 consumer warps, two units each
-    KDW_PG(32, 4, 1, 1, 4),  // 2: 16 warps, tile 16 x 16
-    KDW_PG(32, 4, 1, 2, 4),  // 3: 8 warps
-    KDW_PG(16, 4, 2, 1, 4),  // 4: 16 warps, tile 16 x 32
-    KDW_PG(16, 4, 2, 2, 4),  // 5: 8 warps
-    KDW_PG(8, 4, 4, 1, 4),   // 6: 16 warps, tile 16 x 64
-    KDW_PG(8, 4, 4, 2, 4),   // 7: 8 warps
-    KDW_PG(64, 4, 1, 2, 3),  // 8: 16 warps, two units each, tile 16 x 16
-    KDW_PG(32, 4, 2, 2, 3),  // 9: 16 warps, two units each, tile 16 x 32
+    KDW_PG(64, 2, 1, 2, 4),  // 0: tile 8 x 16
+    KDW_PG(32, 4, 1, 2, 4),  // 1: tile 16 x 16
+    KDW_PG(16, 4, 2, 2, 4),  // 2: tile 16 x 32
+    KDW_PG(8, 4, 4, 2, 4),   // 3: tile 16 x 64
+    KDW_PG(32, 2, 2, 2, 4),  // 4: tile 8 x 32
+    KDW_PG(64, 2, 1, 2, 5),  // 5: as 0, five stages
 };
 #undef KDW_PG
 static const int g_n_pg_variants = (int)(sizeof(g_pg_variants) / sizeof(g_pg_variants[0]));

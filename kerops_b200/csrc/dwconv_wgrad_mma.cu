@@ -23,17 +23,20 @@
 
 namespace kdw {
 
-template <int CS_, int WW_, int WD_, int UPW_, int ST_, bool IP_ = false>
+template <int CS_, int WW_, int WD_, int UPW_, int ST_>
 struct WPCfg {
     static constexpr int CS = CS_, WW = WW_, WD = WD_, UPW = UPW_, ST = ST_;
-    // IP: no load warp - lane 0 of the last consumer warp issues the copies between its own steps.  With eight
-    // warps per SM (two per scheduler) a thread may use 255 registers; a ninth warp lowers that to 168.
-    static constexpr bool IP = IP_;
     static constexpr int NG = CS / 8;               // channel groups of 8
     static constexpr int SU = (WW / UPW) * WD;      // spatial warp groups: workspace rows per CTA
-    static constexpr int NCW = NG * SU;             // consumer warps; warp NCW is the TMA producer (unless IP)
+    static constexpr int NCW = NG * SU;             // consumer warps
     static constexpr int NT = NCW * 32;
-    static constexpr int NTHREADS = NT + (IP ? 0 : 32);
+    // Warps 0-3 form the helper warpgroup (warp 0 loads, the others leave at once), the consumer warps follow.  The
+    // kernel is compiled for 168 registers per thread (12 warps); the helper warpgroup then hands registers back
+    // (setmaxnreg) and the two consumer warpgroups take them: 96 accumulators, 48 grad words and the transposed
+    // patch words do not fit in 168.
+    static constexpr int NHELP = 4;
+    static constexpr int NTHREADS = NT + NHELP * 32;
+    static constexpr int REGS_HELPER = 40, REGS_CONSUMER = 232;
     static constexpr int WT = 4 * WW, DT = 16 * WD;
     static constexpr int VOXB = CS * 2;
     static constexpr int SWZ = CS == 8 ? 0 : VOXB;
@@ -45,7 +48,7 @@ struct WPCfg {
     static constexpr int SCRATCH = 32 * 16 * 4;     // per warp: 16 floats per lane (one plane a of the flush)
     static constexpr int SMEM = ST * STAGE + NCW * SCRATCH + 16 * ST + 4 * ST + 128 + 1024;
     static_assert(CS == 8 || CS == 16 || CS == 32 || CS == 64, "a voxel must be one swizzle span (or 16 bytes)");
-    static_assert(WW % UPW == 0 && NTHREADS <= 1024, "warp layout");
+    static_assert(WW % UPW == 0 && NCW == 8, "two consumer warpgroups");
     static_assert(DT + 2 <= 256 && WT + 2 <= 256, "TMA box limits");
 };
 
@@ -123,68 +126,44 @@ __device__ __forceinline__ void wg_flush(float (&acc)[2][4][3][4], float* scratc
                 for (int k = 0; k < 4; ++k) acc[ks][cp][a][k] = 0.f;
 }
 
-// State of the thread that issues the copies, kept in shared memory so that it costs the consumer warps no registers.
-struct ProdState {
-    StepIter it;
-    uint32_t pi;   // copies issued so far
-    int done;      // end marker written, test hook reached, or a wait ran out
-};
-
-// Issues plane copies into free stages.  `my_step`: the step the calling warp is about to wait for (0xffffffff for a
-// dedicated load warp).  `block`: wait for a stage to become free; a consumer warp that doubles as producer only
-// does so when nothing is in flight for its own next step, otherwise it tests without waiting and tries again
-// between its next steps.
+// Issues the copies of the next x plane and grad plane (or the end marker) into the next stage, waiting for the
+// stage to be free.  The position in the schedule lives in shared memory (ProdState).
 template <class Cfg>
-__device__ __forceinline__ void wg_produce(ProdState* ps, uint32_t my_step, bool block, const Sched& s,
-                                           const CUtensorMap& tmx, const CUtensorMap& tmg, uint32_t stage0, uint32_t full0,
-                                           uint32_t empty0, uint32_t desc0, int g_h0, int* status, const WaitTest& wt) {
+__device__ __forceinline__ void wg_produce(ProdState* ps, const Sched& s, const CUtensorMap& tmx, const CUtensorMap& tmg,
+                                           uint32_t stage0, uint32_t full0, uint32_t empty0, uint32_t desc0, int g_h0,
+                                           int* status, const WaitTest& wt) {
     constexpr int ST = Cfg::ST;
-    if (ps->done) return;
-    StepIter it = ps->it;
-    uint32_t pi = ps->pi;
-    int done = 0;
-    while (true) {
-        if (wt.stop_after >= 0 && (int)pi >= wt.stop_after) {  // test hook: the consumers' wait runs out
-            done = 1;
-            break;
-        }
-        const uint32_t st = pi % ST;
-        if (pi >= ST) {
-            const uint32_t parity = ((pi / ST) & 1u) ^ 1u;
-            if (block || pi == my_step) {
-                if (!mbar_wait_bounded(empty0 + 8 * st, parity, wt.limit_ns)) {
-                    atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
-                    const uint32_t first = pi > ST ? pi - ST : 0;  // copies in flight still target this CTA's memory
-                    for (uint32_t k = first; k < pi; ++k)
-                        (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u, wt.limit_ns);
-                    done = 1;
-                    break;
-                }
-            } else if (!mbar_test_wait(empty0 + 8 * st, parity)) {
-                break;  // not free yet
-            }
-        }
-        const uint32_t bar = full0 + 8 * st;
-        if (!it.active) {  // end marker: completes the stage's barrier without a copy
-            st_shared_u32(desc0 + 4 * st, 0xffffffffu);
-            mbar_arrive(bar);
-            done = 1;
-            break;
-        }
-        const bool with_g = it.q + 1 < it.g.he;  // grad plane q+1 is owned by the segment
-        st_shared_u32(desc0 + 4 * st, ((uint32_t)it.g.c0 << 8) | (it.q == it.g.hb - 1 ? 2u : 0u) | (with_g ? 1u : 0u));
-        mbar_expect_tx(bar, Cfg::X_BYTES + (with_g ? Cfg::G_BYTES : 0));
-        tma_load_5d(status, stage0 + st * Cfg::STAGE, &tmx, bar, it.g.c0, it.g.d0 - 1, it.g.w0 - 1, it.q, it.g.n);
-        if (with_g)
-            tma_load_5d(status, stage0 + st * Cfg::STAGE + Cfg::X_STRIDE, &tmg, bar, it.g.c0, it.g.d0, it.g.w0,
-                        it.q + 1 - g_h0, it.g.n);
-        ++pi;
-        it.next(s);
-        if (block) break;  // a dedicated load warp re-reads `done` between copies
+    const uint32_t pi = ps->pi;
+    if (wt.stop_after >= 0 && (int)pi >= wt.stop_after) {  // test hook: the consumers' wait runs out
+        ps->done = 1;
+        return;
     }
+    const uint32_t st = pi % ST;
+    if (pi >= ST && !mbar_wait_bounded(empty0 + 8 * st, ((pi / ST) & 1u) ^ 1u, wt.limit_ns)) {
+        atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
+        const uint32_t first = pi > ST ? pi - ST : 0;  // copies in flight still target this CTA's shared memory
+        for (uint32_t k = first; k < pi; ++k) (void)mbar_wait_bounded(full0 + 8 * (k % ST), (k / ST) & 1u, wt.limit_ns);
+        ps->done = 1;
+        return;
+    }
+    const uint32_t bar = full0 + 8 * st;
+    StepIter it = ps->it;
+    if (!it.active) {  // end marker: completes the stage's barrier without a copy
+        st_shared_u32(desc0 + 4 * st, 0xffffffffu);
+        mbar_arrive(bar);
+        ps->done = 1;
+        return;
+    }
+    const bool with_g = it.q + 1 < it.g.he;  // grad plane q+1 is owned by the segment
+    st_shared_u32(desc0 + 4 * st, ((uint32_t)it.g.c0 << 8) | (it.q == it.g.hb - 1 ? 2u : 0u) | (with_g ? 1u : 0u));
+    mbar_expect_tx(bar, Cfg::X_BYTES + (with_g ? Cfg::G_BYTES : 0));
+    tma_load_5d(status, stage0 + st * Cfg::STAGE, &tmx, bar, it.g.c0, it.g.d0 - 1, it.g.w0 - 1, it.q, it.g.n);
+    if (with_g)
+        tma_load_5d(status, stage0 + st * Cfg::STAGE + Cfg::X_STRIDE, &tmg, bar, it.g.c0, it.g.d0, it.g.w0,
+                    it.q + 1 - g_h0, it.g.n);
+    it.next(s);
     ps->it = it;
-    ps->pi = pi;
-    ps->done = done;
+    ps->pi = pi + 1;
 }
 
 template <class Cfg>
@@ -221,25 +200,30 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
     __syncthreads();  // the only CTA-wide barrier
 
     ProdState* ps = reinterpret_cast<ProdState*>(base_ptr + (desc0 + 4 * ST + 15 - base) / 16 * 16);
-    if (tid == Cfg::NTHREADS - 32) {  // lane 0 of the warp that issues the copies
+    if (tid == 0) {
         ps->it.init(s, (int)blockIdx.x, (int)gridDim.x);
         ps->pi = 0;
         ps->done = 0;
     }
     __syncwarp();
-    if (!Cfg::IP && warp == NCW) {
+    if (warp < Cfg::NHELP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_HELPER));
         // ---------------- load warp ----------------
-        if (lane != 0) return;
-        while (!ps->done) wg_produce<Cfg>(ps, 0xffffffffu, true, s, tmx, tmg, stage0, full0, empty0, desc0, g_h0, status, wt);
+        if (tid == 0)
+            while (!ps->done) wg_produce<Cfg>(ps, s, tmx, tmg, stage0, full0, empty0, desc0, g_h0, status, wt);
         return;
     }
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(Cfg::REGS_CONSUMER));
+
     // ---------------- consumer warps ----------------
-    const int ng = warp % Cfg::NG;
-    const int su = warp / Cfg::NG;                 // spatial warp group
+    const int cw = warp - Cfg::NHELP;
+    const int ng = cw % Cfg::NG;
+    const int su = cw / Cfg::NG;                   // spatial warp group
     const int uwg = su % (Cfg::WW / UPW), ud = su / (Cfg::WW / UPW);
     const int g = lane >> 2, t = lane & 3;
     constexpr uint32_t IN_ROW4 = 4 * (Cfg::DT + 2) * Cfg::VOXB, G_ROW2 = 2 * Cfg::DT * Cfg::VOXB;
-    static_assert(Cfg::SWZ == 0 || (IN_ROW4 % (8 * Cfg::SWZ) == 0 && G_ROW2 % (8 * Cfg::SWZ) == 0),
+    constexpr uint32_t SWZ_PERIOD = 8 * (Cfg::SWZ ? Cfg::SWZ : 1);
+    static_assert(Cfg::SWZ == 0 || (IN_ROW4 % SWZ_PERIOD == 0 && G_ROW2 % SWZ_PERIOD == 0),
                   "row steps must preserve the swizzle phase");
     uint32_t in_off[4], g_off;
 #pragma unroll
@@ -248,7 +232,7 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
             (uint32_t)(((4 * uwg * UPW + r) * (Cfg::DT + 2) + 16 * ud + 2 * g + t) * Cfg::VOXB + 16 * ng));
     g_off = Cfg::X_STRIDE + swz<Cfg::SWZ>((uint32_t)(((4 * uwg * UPW + (t >> 1)) * Cfg::DT + 16 * ud + 2 * g + (t & 1)) *
                                                          Cfg::VOXB + 16 * ng));
-    float* scratch = scratch0 + warp * (Cfg::SCRATCH / 4);
+    float* scratch = scratch0 + cw * (Cfg::SCRATCH / 4);
     float* row = ws + ((size_t)blockIdx.x * Cfg::SU + su) * KC;
 
     float acc[2][4][3][4];
@@ -266,10 +250,6 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
     int cur_c0 = -1;
     bool failed = false;
     while (true) {
-        if (Cfg::IP && warp == NCW - 1) {  // this warp also issues the copies
-            if (lane == 0) wg_produce<Cfg>(ps, ci, false, s, tmx, tmg, stage0, full0, empty0, desc0, g_h0, status, wt);
-            __syncwarp();
-        }
         const uint32_t st = ci % ST;
         const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u, wt.limit_ns);
         if (__any_sync(0xffffffffu, !ok)) {
@@ -367,15 +347,15 @@ struct WpgVariant {
     int cs, dt, wt;
     WpgLaunch f;
 };
-// WPCfg<CS, WW, WD, UPW, ST, IP>: tile 4*WW x 16*WD voxels (w, d), CS channels
-#define KDW_WPG(CS, WW, WD, UPW, ST, IP) {CS, 16 * WD, 4 * WW, &launch_wgrad_pg<WPCfg<CS, WW, WD, UPW, ST, IP>>}
+// WPCfg<CS, WW, WD, UPW, ST>: tile 4*WW x 16*WD voxels (w, d), CS channels; 8 consumer warps, two units each
+#define KDW_WPG(CS, WW, WD, UPW, ST) {CS, 16 * WD, 4 * WW, &launch_wgrad_pg<WPCfg<CS, WW, WD, UPW, ST>>}
 static const WpgVariant g_wpg_variants[] = {
-    KDW_WPG(64, 2, 1, 2, 3, false),  // 0: 8 consumer warps + load warp, two units each, tile 8 x 16
-    KDW_WPG(64, 2, 1, 2, 3, true),   // 1: 8 warps in all
-    KDW_WPG(32, 4, 1, 2, 4, true),   // 2: tile 16 x 16
-    KDW_WPG(16, 4, 2, 2, 4, true),   // 3: tile 16 x 32
-    KDW_WPG(8, 4, 4, 2, 4, true),    // 4: tile 16 x 64
-    KDW_WPG(64, 2, 1, 2, 4, true),   // 5: as 1, four stages
+    KDW_WPG(64, 2, 1, 2, 3),  // 0: tile 8 x 16
+    KDW_WPG(32, 4, 1, 2, 4),  // 1: tile 16 x 16
+    KDW_WPG(16, 4, 2, 2, 4),  // 2: tile 16 x 32
+    KDW_WPG(8, 4, 4, 2, 4),   // 3: tile 16 x 64
+    KDW_WPG(64, 2, 1, 2, 4),  // 4: as 0, four stages
+    KDW_WPG(32, 2, 2, 2, 4),  // 5: tile 8 x 32
 };
 #undef KDW_WPG
 static const int g_n_wpg_variants = (int)(sizeof(g_wpg_variants) / sizeof(g_wpg_variants[0]));

@@ -82,4 +82,11 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
     return y;
 }
 
+// State of the thread that issues the copies, kept in shared memory so that it costs the consumer warps no registers.
+struct ProdState {
+    StepIter it;
+    uint32_t pi;   // copies issued so far
+    int done;      // end marker written, test hook reached, or a wait ran out
+};
+
 }  // namespace kdw
