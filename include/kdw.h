@@ -58,8 +58,8 @@ int kdw_device_status(int* status);
 
 /*
  * Test hook for the kernels' bounded waits (no reference counterpart; process-wide, not thread-safe, meant for
- * test programs only).  limit_ns: time after which a wait on a TMA barrier inside a kernel gives up (default
- * 2 s).  stop_after >= 0: the load warp of every TMA kernel stops after that many plane loads, so the next wait of
+ * test programs only).  limit_ns: time after which a wait on a TMA barrier inside a forward or weight-gradient
+ * kernel gives up (default 2 s).  stop_after >= 0: the load warp of those kernels stops after that many plane loads, so the next wait of
  * the compute warps runs out, the kernel raises status 1 (kdw_device_status) and returns with its output
  * incomplete - nothing faults and the context stays usable.  stop_after < 0 (default) switches the hook off.
  */
@@ -70,8 +70,8 @@ int kdw_test_wait_limits(int64_t limit_ns, int stop_after);
  * _DWConv_cl3d_impl) by one launch over the whole batch.
  *   x, y      fp16 volumes (N, C, H, W, D), strides in elements; y may have different N/H/W strides
  *   weight    fp16 [3][3][3][C]
- *   acc_type  KDW_ACC_F32: exact fp16 x fp16 products accumulated in fp32 (mixed-precision FMA), rounded once to
- *             fp16 - at least as accurate as the reference's 'float32' mode (fp16 products, fp16 sum of three,
+ *   acc_type  KDW_ACC_F32: exact fp16 x fp16 products accumulated in fp32 (tensor-core mma or mixed-precision FMA,
+ *             depending on the variant), rounded once to fp16 - at least as accurate as the reference's 'float32' mode (fp16 products, fp16 sum of three,
  *             fp32 sum of nine; kerops/kernels/dw_conv.py:49-52);  KDW_ACC_F16: all 27 taps in fp16 FMA chains
  *   tune      0 = built-in choice for this C, W and D; >0 = explicit kernel variant (see kdw_fprop_variants());
  *             takes the place of the num_warps / D_block keywords (dwconv.py:10-17)
@@ -116,8 +116,9 @@ int64_t kdw_wgrad_workspace_bytes(int64_t N, int64_t C, int64_t H, int64_t W, in
  *   workspace  >= kdw_wgrad_workspace_bytes() bytes, 16-byte aligned; holds one fp32 [27][C] row per CTA
  *   dw_f32     optional fp32 [3][3][3][C] result (NULL to skip) - the quantity to all-reduce across GPUs
  *   dw_f16     optional fp16 [3][3][3][C] result (NULL to skip) - what DWConvWGRAD returns (dwconv_wgrad.py:77)
- * Pass 1 accumulates per-CTA fp32 rows (fp16 products summed over 8 voxels, then fp32); pass 2 adds the rows
- * in CTA order.  No atomics: the result is bitwise reproducible for a given device and shape.
+ * Pass 1 accumulates fp32 rows per CTA (per warp group in the tensor-core kernels): every product is an exact
+ * fp16 x fp16 product added to an fp32 sum; pass 2 adds the rows in a fixed order.  No atomics: the result is
+ * bitwise reproducible for a given device and shape.
  */
 int kdw_wgrad_f16(const void* x, const void* grad, void* workspace, int64_t workspace_bytes, float* dw_f32,
                   void* dw_f16, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D, int64_t x_strideN,
@@ -162,13 +163,16 @@ int kdw_wgrad_auto_variant(int64_t C, int64_t W, int64_t D);
 /*
  * Multi-GPU sum of weight gradients by peer stores (no reference counterpart: the reference is single-GPU).
  *
- * Every rank owns one exchange buffer of kdw_allreduce_buffer_bytes(n, world) bytes, zero-filled once before the
- * first call, and can address the buffers of all ranks (`buffers[r]`, device pointers valid in the calling
+ * Every rank owns one exchange buffer of kdw_allreduce_buffer_bytes(capacity, world) bytes, zero-filled once
+ * before the first call, and can address the buffers of all ranks (`buffers[r]`, device pointers valid in the calling
  * process, mapped with access for the calling GPU, e.g. torch symmetric memory or cuMemMap +
  * cuMemSetAccess; buffers[rank] is the rank's own).  One kernel on each
  * rank writes `local` (n fp32 values, e.g. the [3][3][3][C] gradient from kdw_wgrad_f16) into its slot of
  * every buffer, raises a flag there, waits for the flags of all ranks in its own buffer and writes the sum,
  * added in rank order, to out_f32 and/or out_f16 - the same bits on every rank.
+ *   n           values to sum in this call, 1 <= n <= capacity; calls on one set of buffers may use different n
+ *               (the same n on every rank within a call)
+ *   capacity    the value the buffers were sized with; it alone fixes where slots and flags lie in a buffer
  *   seq         call counter, the same on every rank: 1 for the first call on these buffers, then 2, 3, ...
  *   timeout_ns  limit of the wait for the peers' flags; when it runs out the kernel sets the device status
  *               word to 3 (kdw_device_status) and leaves the outputs unwritten
@@ -176,9 +180,9 @@ int kdw_wgrad_auto_variant(int64_t C, int64_t W, int64_t D);
  * The function itself only enqueues the kernel; it returns KDW_ERR_ARG / KDW_ERR_ALIGN for bad arguments
  * (buffers must be 128-byte aligned).
  */
-int64_t kdw_allreduce_buffer_bytes(int64_t n, int world);
-int kdw_allreduce_push_f32(const float* local, float* out_f32, void* out_f16, void* const* buffers, int64_t n, int rank,
-                           int world, uint32_t seq, int64_t timeout_ns, void* stream);
+int64_t kdw_allreduce_buffer_bytes(int64_t capacity, int world);
+int kdw_allreduce_push_f32(const float* local, float* out_f32, void* out_f16, void* const* buffers, int64_t n,
+                           int64_t capacity, int rank, int world, uint32_t seq, int64_t timeout_ns, void* stream);
 
 /*
  * Forward pass with a fused residual add and per-channel statistics:

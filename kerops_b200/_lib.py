@@ -43,7 +43,7 @@ SIGNATURES = {
     'kdw_fprop_bnrelu_variants': (_int, []),
     'kdw_fprop_bnrelu_f16': (_int, [_ptr] * 5 + [_i64] * 5 + [_i64] * 6 + [_int, _int, _ptr]),
     'kdw_allreduce_buffer_bytes': (_i64, [_i64, _int]),
-    'kdw_allreduce_push_f32': (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _int, _int, ctypes.c_uint32, _i64, _ptr]),
+    'kdw_allreduce_push_f32': (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _int, _int, ctypes.c_uint32, _i64, _ptr]),
 }
 
 _lib = None

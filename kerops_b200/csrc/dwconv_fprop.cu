@@ -257,34 +257,60 @@ int launch_fprop_mma_variant(int which, const void* x, const void* w, void* y, i
                              int64_t ysH, int64_t ysW, int h_begin, int h_end, int y_h0, cudaStream_t stream);
 static int n_fprop_variants() { return g_n_table_variants + fprop_mma_variants(); }
 
-// Built-in choice.  Per channel count a short list of candidates with their time relative to the best one, measured
-// at (1, C, 350, 350, 128) on B200 inside the benchmark's sweep (the ranking of the 32- and 64-channel tiles moves
-// by a few per cent with the placement of x and y in memory).  A tile that does not divide W or D computes padding:
+// Built-in choice.  Per channel count and accumulate type a short list of candidates with their time relative to
+// the best one, measured at (1, C, 350, 350, 128) on B200.  A tile that does not divide W or D computes padding:
 // the candidate's time is scaled by the padded / real area and the cheapest one wins, so e.g. D = 40 does not run
-// on a 64-deep tile.
+// on a 64-deep tile.  KDW_ACC_F32 runs on the tensor-core kernels (ids after the table, dwconv_fprop_mma.cu: exact
+// fp16 products, fp32 sums); KDW_ACC_F16 exists only as packed-half FMA chains on the CUDA cores.
 struct FpropCand {
     int id;
     float rel;
 };
-static const FpropCand kFpropCand8[] = {{1, 1.00f}, {2, 1.12f}};
-static const FpropCand kFpropCand16[] = {{10, 1.00f}, {4, 1.03f}, {1, 1.75f}};
-static const FpropCand kFpropCand32[] = {{11, 1.00f}, {6, 1.02f}, {4, 1.02f}};
-static const FpropCand kFpropCand64[] = {{11, 1.00f}, {8, 1.02f}, {6, 1.03f}};
-static const FpropCand kFpropCand128[] = {{8, 1.00f}, {11, 1.01f}, {6, 1.03f}};
+void fprop_mma_variant_tile(int which, int* wt, int* dt);
+static const int kT = g_n_table_variants;  // tensor-core variant i has id kT + 1 + i
+static const FpropCand kFpropCand8[] = {{kT + 4, 1.00f}, {1, 1.05f}, {2, 1.18f}};
+static const FpropCand kFpropCand16[] = {{kT + 3, 1.00f}, {10, 1.50f}, {4, 1.55f}};
+static const FpropCand kFpropCand32[] = {{kT + 5, 1.00f}, {kT + 3, 1.03f}, {kT + 2, 1.06f}, {11, 1.75f}};
+static const FpropCand kFpropCand64[] = {{kT + 1, 1.00f}, {kT + 6, 1.02f}, {kT + 5, 1.09f}, {11, 1.80f}};
+static const FpropCand kFpropCand128[] = {{kT + 1, 1.00f}, {kT + 6, 1.07f}, {kT + 2, 1.12f}, {8, 1.80f}};
+static const FpropCand kFpropCandH8[] = {{1, 1.00f}, {2, 1.12f}};
+static const FpropCand kFpropCandH16[] = {{10, 1.00f}, {4, 1.03f}, {1, 1.75f}};
+static const FpropCand kFpropCandH32[] = {{11, 1.00f}, {6, 1.02f}, {4, 1.02f}};
+static const FpropCand kFpropCandH64[] = {{11, 1.00f}, {8, 1.02f}, {6, 1.03f}};
+static const FpropCand kFpropCandH128[] = {{8, 1.00f}, {11, 1.01f}, {6, 1.03f}};
 
-static int auto_fprop_variant(int64_t C, int64_t W, int64_t D) {
+static void fprop_variant_tile(int id, int* wt, int* dt) {
+    if (id > g_n_table_variants) {
+        fprop_mma_variant_tile(id - g_n_table_variants - 1, wt, dt);
+    } else {
+        *wt = g_fprop_variants[id - 1].wt;
+        *dt = g_fprop_variants[id - 1].dt;
+    }
+}
+
+#define KDW_CANDS(a) cand = a, n = (int)(sizeof(a) / sizeof(a[0]))
+static int auto_fprop_variant(int64_t C, int64_t W, int64_t D, int acc_type) {
     const FpropCand* cand;
     int n;
-    if (C == 8) { cand = kFpropCand8; n = 2; }
-    else if (C == 16) { cand = kFpropCand16; n = 3; }
-    else if (C == 32) { cand = kFpropCand32; n = 3; }
-    else if (C == 64) { cand = kFpropCand64; n = 3; }
-    else { cand = kFpropCand128; n = 3; }
+    if (acc_type == KDW_ACC_F16) {
+        if (C == 8) KDW_CANDS(kFpropCandH8);
+        else if (C == 16) KDW_CANDS(kFpropCandH16);
+        else if (C == 32) KDW_CANDS(kFpropCandH32);
+        else if (C == 64) KDW_CANDS(kFpropCandH64);
+        else KDW_CANDS(kFpropCandH128);
+    } else {
+        if (C == 8) KDW_CANDS(kFpropCand8);
+        else if (C == 16) KDW_CANDS(kFpropCand16);
+        else if (C == 32) KDW_CANDS(kFpropCand32);
+        else if (C == 64) KDW_CANDS(kFpropCand64);
+        else KDW_CANDS(kFpropCand128);
+    }
     int best = cand[0].id;
     double best_cost = 0.0;
     for (int i = 0; i < n; ++i) {
-        const FpropVariant& v = g_fprop_variants[cand[i].id - 1];
-        const double padded = (double)((W + v.wt - 1) / v.wt * v.wt) * (double)((D + v.dt - 1) / v.dt * v.dt);
+        int wt = 1, dt = 1;
+        fprop_variant_tile(cand[i].id, &wt, &dt);
+        const double padded = (double)((W + wt - 1) / wt * wt) * (double)((D + dt - 1) / dt * dt);
         const double cost = cand[i].rel * padded / ((double)W * (double)D);
         if (i == 0 || cost < best_cost) {
             best = cand[i].id;
@@ -293,6 +319,7 @@ static int auto_fprop_variant(int64_t C, int64_t W, int64_t D) {
     }
     return best;
 }
+#undef KDW_CANDS
 
 static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N, int64_t C, int64_t Hx, int64_t W,
                           int64_t D, int64_t xsN, int64_t xsH, int64_t xsW, int64_t Hy, int64_t ysN, int64_t ysH,
@@ -341,7 +368,7 @@ static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N,
         KDW_CUDA(cudaGetLastError());
         return 0;
     }
-    const int id = tune ? tune : auto_fprop_variant(C, W, D);
+    const int id = tune ? tune : auto_fprop_variant(C, W, D, acc_type);
     if (id > g_n_table_variants) {
         if (acc_type != KDW_ACC_F32) {
             set_error("fprop: variant %d (tensor cores) implements KDW_ACC_F32 only", id);
@@ -367,7 +394,7 @@ int kdw_fprop_variants(void) { return kdw::n_fprop_variants(); }
 
 int kdw_fprop_auto_variant(int64_t C, int64_t W, int64_t D) {
     if (C < 8 || (C & (C - 1)) != 0 || W <= 0 || D <= 0) return 0;
-    return kdw::auto_fprop_variant(C, W, D);
+    return kdw::auto_fprop_variant(C, W, D, KDW_ACC_F32);
 }
 
 int kdw_fprop_variant_channels(int id) {

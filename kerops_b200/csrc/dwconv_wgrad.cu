@@ -327,38 +327,57 @@ int launch_wgrad_mma_variant(int which, const void* x, const void* grad, float* 
 static int n_wgrad_variants() { return g_n_table_wgrad_variants + wgrad_mma_variants(); }
 
 // Built-in choice: per channel count a short list of candidates with their time relative to the best one, measured
-// on B200 at (1,C,350,350,128) (15 consumer warps on wide-w tiles win for C >= 32; C <= 16 runs on 8-channel
-// slices); each candidate's time is scaled by the padded / real area of its tiles on this W x D and the cheapest
-// one wins.
+// on B200 at (1,C,350,350,128); each candidate's time is scaled by the padded / real area of its tiles on this
+// W x D and the cheapest one wins.  The tensor-core kernels (ids after the table, dwconv_wgrad_mma.cu) lead for
+// every C; the CUDA-core tiles remain as candidates for shapes their tiles fit better.
 struct WgradCand {
     int id;
     float rel;
 };
-static const WgradCand kWgradCand8[] = {{24, 1.00f}, {11, 1.06f}, {1, 1.09f}, {2, 1.25f}};
-static const WgradCand kWgradCand16[] = {{1, 1.00f}, {2, 1.15f}};
-static const WgradCand kWgradCand32[] = {{14, 1.00f}, {10, 1.04f}, {3, 1.10f}, {4, 1.25f}};
-static const WgradCand kWgradCand64[] = {{22, 1.00f}, {16, 1.01f}, {8, 1.03f}, {14, 1.03f}, {5, 1.12f}};
+void wgrad_mma_variant_tile(int which, int* wt, int* dt);
+static const int kTW = (int)(sizeof(g_wgrad_variants) / sizeof(g_wgrad_variants[0]));  // tensor-core variant i: kTW + 1 + i
+static const WgradCand kWgradCand8[] = {{kTW + 4, 1.00f}, {24, 1.13f}, {11, 1.20f}, {1, 1.23f}};
+static const WgradCand kWgradCand16[] = {{kTW + 3, 1.00f}, {1, 1.75f}, {2, 2.00f}};
+static const WgradCand kWgradCand32[] = {{kTW + 2, 1.00f}, {kTW + 3, 1.03f}, {kTW + 6, 1.04f}, {14, 1.70f}};
+static const WgradCand kWgradCand64[] = {{kTW + 6, 1.00f}, {kTW + 1, 1.03f}, {kTW + 5, 1.09f}, {22, 1.65f}};
+static const WgradCand kWgradCand128[] = {{kTW + 1, 1.00f}, {kTW + 5, 1.02f}, {kTW + 2, 1.14f}, {22, 1.78f}};
 
-static int auto_wgrad_variant(int64_t C, int64_t W, int64_t D) {
+static void wgrad_variant_tile(int id, int* wt, int* dt) {
+    if (id > kTW) {
+        wgrad_mma_variant_tile(id - kTW - 1, wt, dt);
+    } else {
+        *wt = g_wgrad_variants[id - 1].wt;
+        *dt = g_wgrad_variants[id - 1].dt;
+    }
+}
+
+#define KDW_CANDS(a) cand = a, n = (int)(sizeof(a) / sizeof(a[0]))
+// table_only: consider the CUDA-core tiles only (one workspace row per CTA; the built-in workspace of
+// kdw_wgrad_f16_static is sized for that).
+static int auto_wgrad_variant(int64_t C, int64_t W, int64_t D, bool table_only = false) {
     const WgradCand* cand;
     int n;
-    if (C == 8) { cand = kWgradCand8; n = 4; }
-    else if (C == 16) { cand = kWgradCand16; n = 2; }
-    else if (C == 32) { cand = kWgradCand32; n = 4; }
-    else { cand = kWgradCand64; n = 5; }
-    int best = cand[0].id;
+    if (C == 8) KDW_CANDS(kWgradCand8);
+    else if (C == 16) KDW_CANDS(kWgradCand16);
+    else if (C == 32) KDW_CANDS(kWgradCand32);
+    else if (C == 64) KDW_CANDS(kWgradCand64);
+    else KDW_CANDS(kWgradCand128);
+    int best = 0;
     double best_cost = 0.0;
     for (int i = 0; i < n; ++i) {
-        const WgradVariant& v = g_wgrad_variants[cand[i].id - 1];
-        const double padded = (double)((W + v.wt - 1) / v.wt * v.wt) * (double)((D + v.dt - 1) / v.dt * v.dt);
+        if (table_only && cand[i].id > kTW) continue;
+        int wt = 1, dt = 1;
+        wgrad_variant_tile(cand[i].id, &wt, &dt);
+        const double padded = (double)((W + wt - 1) / wt * wt) * (double)((D + dt - 1) / dt * dt);
         const double cost = cand[i].rel * padded / ((double)W * (double)D);
-        if (i == 0 || cost < best_cost) {
+        if (best == 0 || cost < best_cost) {
             best = cand[i].id;
             best_cost = cost;
         }
     }
     return best;
 }
+#undef KDW_CANDS
 
 static int64_t ws_rows_for_device(int* rc_out) {
     int sms = 0;
@@ -518,7 +537,7 @@ static int wgrad_static_dispatch(const void* x, const void* grad, float* dw_f32,
         KDW_CUDA(cudaGetLastError());
         rows = (int)blocks;
     } else {
-        const WgradVariant& v = g_wgrad_variants[auto_wgrad_variant(C, W, D) - 1];
+        const WgradVariant& v = g_wgrad_variants[auto_wgrad_variant(C, W, D, true) - 1];
         WgradArgs a{x, grad, ws, kStaticRows, N, C, H, W, D, xsN, xsH, xsW, H, gsN, gsH, gsW, 0, (int)H, 0, st};
         rc = v.f(a, &rows);  // the launcher never uses more CTAs (= rows) than a.ws_rows
         if (rc) return rc;

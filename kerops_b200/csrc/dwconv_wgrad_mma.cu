@@ -367,6 +367,11 @@ int wgrad_mma_variant_channels(int which) {
     return g_wpg_variants[which].cs;
 }
 
+void wgrad_mma_variant_tile(int which, int* wt, int* dt) {
+    *wt = g_wpg_variants[which].wt;
+    *dt = g_wpg_variants[which].dt;
+}
+
 int launch_wgrad_mma_variant(int which, const void* x, const void* grad, float* ws, int64_t ws_rows, int64_t N, int64_t C,
                              int64_t Hx, int64_t W, int64_t D, int64_t xsN, int64_t xsH, int64_t xsW, int64_t Hg,
                              int64_t gsN, int64_t gsH, int64_t gsW, int h_begin, int h_end, int g_h0,

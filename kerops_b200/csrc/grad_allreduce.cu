@@ -3,8 +3,11 @@
 // there, waits - with a time limit - for the flags of all peers in its own buffer, and adds the slots in rank
 // order.  One kernel per rank does all four steps; the result is bitwise identical on every rank.
 //
-// Exchange buffer of one rank (kdw_allreduce_buffer_bytes):
-//   [parity 0 | parity 1] x [source rank 0 .. world-1] x { payload: round_up(n,32) floats, flag line: 32 words }
+// Exchange buffer of one rank (kdw_allreduce_buffer_bytes(capacity, world)):
+//   [parity 0 | parity 1] x [source rank 0 .. world-1] x { payload: round_up(capacity,32) floats, flag line: 32 words }
+// The layout depends on the CAPACITY the buffers were made for, never on the n of a call, so calls with different
+// n on one set of buffers use the same slots and flags (a layout derived from n would let a small call's region
+// overlap the region a slower peer is still summing for the previous, larger call).
 // A call with sequence number s uses parity s & 1 and writes s into the flag word.  Two parities are enough:
 // a rank can only start call s+2 after every peer has raised flag s+1, and a peer raises s+1 only after its
 // own call s (the reader of the parity about to be overwritten) has finished, because calls on one rank are
@@ -44,12 +47,12 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 __global__ void __launch_bounds__(kPushThreads) grad_push_sum_kernel(const float* __restrict__ local,
                                                                      float* __restrict__ out32,
                                                                      __half* __restrict__ out16, PushPeers peers, int n,
-                                                                     int rank, int world, unsigned seq,
+                                                                     long long capacity, int rank, int world, unsigned seq,
                                                                      unsigned long long timeout_ns, int* status) {
     __shared__ int s_failed;
     const int tid = threadIdx.x;
-    const long long slot = push_slot_floats(n);
-    const long long flag_off = push_payload_floats(n);
+    const long long slot = push_slot_floats(capacity);
+    const long long flag_off = push_payload_floats(capacity);
     const long long mine = ((long long)(seq & 1u) * world + rank) * slot;  // where this rank's data goes, in every buffer
     if (tid == 0) s_failed = 0;
     // 1. push the payload to every rank (own buffer included)
@@ -95,17 +98,18 @@ int64_t kdw_allreduce_buffer_bytes(int64_t n, int world) {
     return 2 * (int64_t)world * kdw::push_slot_floats(n) * 4;
 }
 
-int kdw_allreduce_push_f32(const float* local, float* out_f32, void* out_f16, void* const* buffers, int64_t n, int rank,
-                           int world, uint32_t seq, int64_t timeout_ns, void* stream) {
+int kdw_allreduce_push_f32(const float* local, float* out_f32, void* out_f16, void* const* buffers, int64_t n,
+                           int64_t capacity, int rank, int world, uint32_t seq, int64_t timeout_ns, void* stream) {
     using namespace kdw;
     if (!local || !buffers || (!out_f32 && !out_f16)) {
         set_error("allreduce_push: null pointer (local, buffers and at least one output are required)");
         return KDW_ERR_ARG;
     }
-    if (n <= 0 || n > (1 << 24) || world <= 0 || world > kMaxPushRanks || rank < 0 || rank >= world ||
-        timeout_ns <= 0) {
-        set_error("allreduce_push: n=%lld rank=%d world=%d timeout_ns=%lld out of range (1 <= world <= %d)",
-                  (long long)n, rank, world, (long long)timeout_ns, kMaxPushRanks);
+    if (n <= 0 || capacity > (1 << 24) || n > capacity || world <= 0 || world > kMaxPushRanks || rank < 0 ||
+        rank >= world || timeout_ns <= 0) {
+        set_error("allreduce_push: n=%lld capacity=%lld rank=%d world=%d timeout_ns=%lld out of range "
+                  "(1 <= n <= capacity, 1 <= world <= %d)",
+                  (long long)n, (long long)capacity, rank, world, (long long)timeout_ns, kMaxPushRanks);
         return KDW_ERR_ARG;
     }
     if (seq == 0) {
@@ -125,7 +129,7 @@ int kdw_allreduce_push_f32(const float* local, float* out_f32, void* out_f16, vo
     int rc = status_ptr(&status);
     if (rc) return rc;
     grad_push_sum_kernel<<<1, kPushThreads, 0, (cudaStream_t)stream>>>(local, out_f32, (__half*)out_f16, peers, (int)n,
-                                                                        rank, world, seq,
+                                                                        (long long)capacity, rank, world, seq,
                                                                         (unsigned long long)timeout_ns, status);
     KDW_CUDA(cudaGetLastError());
     return 0;

@@ -110,7 +110,7 @@ class GradPushAllReduce:
         with torch.cuda.device(self.device):
             stream = torch.cuda.current_stream(self.device).cuda_stream
             self._lib.check(self.lib.kdw_allreduce_push_f32(local.data_ptr(), out.data_ptr(), None, self._ptrs, n,
-                                                             self.rank, self.world, self.seq,
+                                                             self.max_numel, self.rank, self.world, self.seq,
                                                              self.timeout_ns, ctypes.c_void_p(stream)))
         return out
 

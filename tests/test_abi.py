@@ -57,13 +57,14 @@ def test_argument_errors_without_gpu(kdw_lib):
 
 
 def test_auto_variant_follows_the_shape(kdw_lib):
-    """tune = 0: the benchmark shape gets the tiles measured fastest there; a depth that a deep tile would pad
-    heavily gets a shallower tile; every choice is a variant whose channel slice divides C."""
+    """tune = 0: the benchmark shape gets the tiles measured fastest there (tensor-core kernels, numbered after the
+    12 / 24 CUDA-core table variants); a depth that a deep tile would pad heavily gets a shallower tile; every
+    choice is a variant whose channel slice divides C."""
     lib = kdw_lib
-    assert [lib.kdw_fprop_auto_variant(C, 350, 128) for C in (8, 16, 32, 64, 128)] == [1, 10, 11, 11, 8]
-    assert [lib.kdw_wgrad_auto_variant(C, 350, 128) for C in (8, 16, 32, 64, 128)] == [24, 1, 14, 22, 22]
-    assert lib.kdw_fprop_auto_variant(32, 350, 40) != 11   # 32-deep tiles would compute 64 of 40 planes
-    assert lib.kdw_wgrad_auto_variant(128, 48, 128) != 22  # 40-wide tiles would compute 80 of 48 columns
+    assert [lib.kdw_fprop_auto_variant(C, 350, 128) for C in (8, 16, 32, 64, 128)] == [16, 15, 17, 13, 13]
+    assert [lib.kdw_wgrad_auto_variant(C, 350, 128) for C in (8, 16, 32, 64, 128)] == [28, 27, 26, 30, 25]
+    assert lib.kdw_fprop_auto_variant(32, 350, 40) != 17   # 32-deep tiles would compute 64 of 40 planes
+    assert lib.kdw_fprop_auto_variant(8, 48, 24) != 16     # 64-deep tiles would compute 64 of 24 planes
     for C in (8, 16, 32, 64, 128, 256):
         for W, D in ((350, 128), (16, 8), (40, 40), (97, 61), (1, 1)):
             f, w = lib.kdw_fprop_auto_variant(C, W, D), lib.kdw_wgrad_auto_variant(C, W, D)

@@ -23,9 +23,19 @@ def _inputs(N, C, H, W, D, seed):
 
 
 def _composition(x, r, w):
+    """DWConv followed by a torch fp16 add and fp32 channel means.  The fused kernel runs on the CUDA cores; the
+    convolution it is compared with bit for bit is a CUDA-core variant of kdw_fprop_f16 too (same order of the fp32
+    sums).  The built-in choice of DWConv - a tensor-core kernel, whose fp32 sums are added in another order - must
+    agree to the last fp16 bit almost everywhere."""
     from kerops_b200.ops.conv import DWConv
 
-    out = DWConv(x, w, num_warps=8, D_block=8) + r  # keywords given: any power-of-two C is then accepted
+    from ._util import dwconv_cuda_core
+
+    y = dwconv_cuda_core(x, w)
+    y_default = DWConv(x, w, num_warps=8, D_block=8)  # keywords given: any power-of-two C is then accepted
+    assert float((y != y_default).float().mean()) < 1e-3
+    torch.testing.assert_close(y.float(), y_default.float(), rtol=1e-3, atol=2e-3)
+    out = y + r
     o = out.float()
     return out, o.mean(dim=(0, 2, 3, 4)), (o * o).mean(dim=(0, 2, 3, 4))
 

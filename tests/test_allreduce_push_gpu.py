@@ -9,10 +9,11 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _push(lib, local, out, bufs, rank, world, seq, timeout_ms):
+def _push(lib, local, out, bufs, rank, world, seq, timeout_ms, capacity=None):
     ptrs = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    return lib.kdw_allreduce_push_f32(local.data_ptr(), out.data_ptr(), None, ptrs, local.numel(), rank, world, seq,
+    return lib.kdw_allreduce_push_f32(local.data_ptr(), out.data_ptr(), None, ptrs, local.numel(),
+                                      local.numel() if capacity is None else capacity, rank, world, seq,
                                       int(timeout_ms * 1e6), stream)
 
 
@@ -70,6 +71,35 @@ def test_two_ranks_one_after_the_other(kdw_lib, n):
         assert _push(lib, a, out0, bufs, 0, 2, seq, 1000) == 0
         assert _lib.device_status() == 0
         assert torch.equal(out0, a + b)
+
+
+def test_alternating_sizes_on_one_buffer_set(kdw_lib):
+    """One reducer serving layers of different width: calls alternate between n = 27*128 and n = 27*8 on buffers made
+    for the larger one.  Slots and flags lie where the CAPACITY puts them, so the small call of step s+1 cannot land
+    in the region the large call of step s is still read from."""
+    from kerops_b200 import _lib
+
+    lib = kdw_lib
+    cap = 27 * 128
+    bufs = _buffers(lib, cap, 2)
+    for seq in range(1, 9):
+        n = cap if seq % 2 else 27 * 8
+        a = torch.randn(n, device='cuda')
+        b = torch.randn(n, device='cuda')
+        out0 = torch.full_like(a, float('nan'))
+        out1 = torch.full_like(a, float('nan'))
+        assert _push(lib, b, out1, bufs, 1, 2, seq, 10, capacity=cap) == 0  # rank 1 first: its own wait runs out
+        assert _lib.device_status() == 3
+        assert _push(lib, a, out0, bufs, 0, 2, seq, 1000, capacity=cap) == 0
+        assert _lib.device_status() == 0
+        assert torch.equal(out0, a + b)
+        # rank 1 again with the same sequence number: both flags are up now, its sum has the same bits
+        assert _push(lib, b, out1, bufs, 1, 2, seq, 1000, capacity=cap) == 0
+        assert _lib.device_status() == 0
+        assert torch.equal(out1, out0)
+    # n beyond the capacity is refused
+    big = torch.randn(cap + 32, device='cuda')
+    assert _push(lib, big, torch.empty_like(big), bufs, 0, 2, 9, 10, capacity=cap) == -1
 
 
 def test_argument_errors(kdw_lib):

@@ -71,6 +71,8 @@ def test_emulated_wgrad(kdw_lib, kdw_emu, shape):
             continue
         dw = np.zeros((3, 3, 3, C), np.float32)
         r = kdw_emu.emu_wgrad(v, x.ctypes.data, g.ctypes.data, dw.ctypes.data, N, C, H, W, D, H, 0, H, 0, grid)
+        if r == -1:
+            continue  # tensor-core variants (warp-level mma) are not emulated on the CPU
         assert r > 0
         err = np.abs(dw - dw_exact).max()
         scale = np.abs(dw_exact).max() + 1.0

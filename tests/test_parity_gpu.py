@@ -127,6 +127,25 @@ def test_wgrad_lattice(ops, C):
         assert torch.equal(dw32.to(torch.float16), dw16)
 
 
+@pytest.mark.parametrize('C', CHANNELS)
+def test_dense_small_lattice(ops, C):
+    """Every size triple from the small end of the reference's lattice (tests/conftest.py:19-31), every batch size
+    1, 2, 4 on a rotating schedule: all tails, sizes below a tile and below the stencil."""
+    DWConv, DWConvWGRAD, _launch = ops
+    sizes = [2, 3, 7, 13, 16, 32, 37]
+    k = 0
+    for H in sizes:
+        for W in sizes:
+            for D in sizes:
+                N = (1, 2, 4)[k % 3]
+                k += 1
+                x, g, w = make_inputs(7000 * C + k, N, C, H, W, D)
+                check_fprop(DWConv(x, w), to.fprop_shift_fp32(x, w))
+                if k % 2 == 0:  # the weight-gradient oracle is the slower one: every other shape
+                    dw32, dw16 = _launch.wgrad(x, g, want_f32=True, want_f16=True)
+                    check_wgrad(dw32, dw16, to.wgrad_fp64(x, g), bsize=N)
+
+
 def test_small_shapes_numpy_oracle(ops):
     """Small cases straight against the numpy oracle (no torch arithmetic on the checking side)."""
     DWConv, DWConvWGRAD, _ = ops
@@ -284,7 +303,7 @@ def checksum_property(x, w, y):
     return ((got - want).abs() / scale).max().item()
 
 
-@pytest.mark.parametrize('C', [8, 32, 128])
+@pytest.mark.parametrize('C', CHANNELS)
 def test_benchmark_volume(ops, C):
     DWConv, DWConvWGRAD, _launch = ops
     N, H, W, D = 1, 350, 350, 128

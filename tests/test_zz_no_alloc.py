@@ -45,6 +45,10 @@ def test_static_workspace_entry_point_matches_the_allocating_one(kdw_lib):
         err = float((got32.double() - ref32.double()).norm() / ref32.double().norm())
         assert err <= 1e-5, f'shape {shape}: relative L2 difference {err}'
         assert torch.allclose(got16.float(), ref16.float(), rtol=2e-3, atol=1e-3)
+        # and against the fp64 oracle, with the bar of the other weight-gradient tests
+        from oracle import torch_oracle as to
+
+        assert to.rel_l2(got32.cpu(), to.wgrad_fp64(x, grad).cpu()) <= 1e-3
     assert _lib.device_status() == 0
 
 
