@@ -348,7 +348,20 @@ class Ctx:
         torch.cuda.set_device(self.dev)
         _lib.load()
         if self.world > 1:
-            dist.init_process_group('nccl', device_id=self.dev)
+            # NCCL may print a version banner on stdout when it creates its communicator; stdout carries the one
+            # JSON line only, so file descriptor 1 points at stderr until the first collective has run
+            sys.stdout.flush()
+            saved = os.dup(1)
+            os.dup2(2, 1)
+            try:
+                dist.init_process_group('nccl', device_id=self.dev)
+                t = torch.zeros(1, device=self.dev)
+                dist.all_reduce(t)
+                torch.cuda.synchronize()
+            finally:
+                sys.stdout.flush()
+                os.dup2(saved, 1)
+                os.close(saved)
 
     def barrier(self):
         import torch
