@@ -267,9 +267,10 @@ struct FpropCand {
     float rel;
 };
 void fprop_mma_variant_tile(int which, int* wt, int* dt);
+bool fprop_mma_variant_fits(int which, int64_t C, int64_t D);
 static const int kT = g_n_table_variants;  // tensor-core variant i has id kT + 1 + i
-static const FpropCand kFpropCand8[] = {{kT + 4, 1.00f}, {1, 1.05f}, {2, 1.18f}};
-static const FpropCand kFpropCand16[] = {{kT + 3, 1.00f}, {10, 1.50f}, {4, 1.55f}};
+static const FpropCand kFpropCand8[] = {{kT + 7, 1.00f}, {kT + 4, 1.70f}, {1, 1.80f}, {2, 2.00f}};
+static const FpropCand kFpropCand16[] = {{kT + 8, 1.00f}, {kT + 3, 1.21f}, {kT + 9, 1.31f}, {10, 1.80f}, {4, 1.85f}};
 static const FpropCand kFpropCand32[] = {{kT + 5, 1.00f}, {kT + 3, 1.03f}, {kT + 2, 1.06f}, {11, 1.75f}};
 static const FpropCand kFpropCand64[] = {{kT + 1, 1.00f}, {kT + 6, 1.02f}, {kT + 5, 1.09f}, {11, 1.80f}};
 static const FpropCand kFpropCand128[] = {{kT + 1, 1.00f}, {kT + 6, 1.07f}, {kT + 2, 1.12f}, {8, 1.80f}};
@@ -305,14 +306,15 @@ static int auto_fprop_variant(int64_t C, int64_t W, int64_t D, int acc_type) {
         else if (C == 64) KDW_CANDS(kFpropCand64);
         else KDW_CANDS(kFpropCand128);
     }
-    int best = cand[0].id;
+    int best = 0;
     double best_cost = 0.0;
     for (int i = 0; i < n; ++i) {
+        if (cand[i].id > kT && !fprop_mma_variant_fits(cand[i].id - kT - 1, C, D)) continue;
         int wt = 1, dt = 1;
         fprop_variant_tile(cand[i].id, &wt, &dt);
         const double padded = (double)((W + wt - 1) / wt * wt) * (double)((D + dt - 1) / dt * dt);
         const double cost = cand[i].rel * padded / ((double)W * (double)D);
-        if (i == 0 || cost < best_cost) {
+        if (best == 0 || cost < best_cost) {
             best = cand[i].id;
             best_cost = cost;
         }

@@ -30,7 +30,7 @@
 
 namespace kdw {
 
-template <int CS_, int WW_, int WD_, int UPW_, int ST_>
+template <int CS_, int WW_, int WD_, int UPW_, int ST_, int MODE_ = 0>
 struct PCfg {
     static constexpr int CS = CS_;    // channels per CTA slice (8 .. 64)
     static constexpr int WW = WW_;    // units along w
@@ -49,18 +49,17 @@ struct PCfg {
     static constexpr int REGS_HELPER = 40, REGS_CONSUMER = 232;
     static constexpr int WT = 4 * WW;
     static constexpr int DT = 16 * WD;
-    static constexpr int VOXB = CS * 2;  // bytes of a voxel in shared memory
-    static constexpr int SWZ = CS == 8 ? 0 : VOXB;  // TMA swizzle span: one voxel (32, 64 or 128 bytes); none for 16
-    static constexpr int IN_BYTES = (WT + 2) * (DT + 2) * VOXB;
-    static constexpr int IN_STRIDE = (IN_BYTES + 1023) / 1024 * 1024;
-    static constexpr int OUT_BYTES = WT * DT * VOXB;
-    static constexpr int OUT_STRIDE = (OUT_BYTES + 1023) / 1024 * 1024;
+    using Geo = TileGeo<CS, WT, DT, MODE_>;  // staging of the tiles in shared memory and their TMA boxes
+    static constexpr int VOXB = Geo::VOXB;
+    static constexpr int SWZ = Geo::SWZ;
+    static constexpr int IN_BYTES = Geo::IN_BYTES, IN_STRIDE = Geo::IN_STRIDE;
+    static constexpr int OUT_BYTES = Geo::OUT_BYTES, OUT_STRIDE = Geo::OUT_STRIDE;
     static constexpr int SMEM = ST * IN_STRIDE + 2 * OUT_STRIDE + 16 * ST + 32 + 4 * ST + 256 + 1024;
     static_assert(CS == 8 || CS == 16 || CS == 32 || CS == 64, "a voxel must be one swizzle span (or 16 bytes)");
     static_assert(WW % UPW == 0, "units per warp");
     static_assert(NCW == 8, "register hand-over is laid out for two consumer warpgroups");
     static_assert(NTHREADS <= 1024, "thread count");
-    static_assert(DT + 2 <= 256 && WT + 2 <= 256, "TMA box limits");
+    static_assert(DT + 4 <= 256 && WT + 2 <= 256, "TMA box limits");
 };
 
 // One input plane of one unit.  X[r] = the thread's voxel of input row r (r = 0..5: rows w-1 .. w+4 of the unit),
@@ -166,7 +165,8 @@ __device__ __forceinline__ void pg_produce(ProdState* ps, const Sched& s, const 
     }
     st_shared_u32(desc0 + 4 * st, ((uint32_t)it.g.c0 << 8) | (it.q - 1 >= it.g.hb ? 1u : 0u));
     mbar_expect_tx(full0 + 8 * st, Cfg::IN_BYTES);
-    tma_load_5d(status, in0 + st * Cfg::IN_STRIDE, &tmx, full0 + 8 * st, it.g.c0, it.g.d0 - 1, it.g.w0 - 1, it.q, it.g.n);
+    tile_load_in<typename Cfg::Geo>(status, in0 + st * Cfg::IN_STRIDE, &tmx, full0 + 8 * st, it.g.c0, it.g.d0, it.g.w0, it.q,
+                                    it.g.n);
     it.next(s);
     ps->it = it;
     ps->pi = pi + 1;
@@ -186,7 +186,8 @@ __device__ __forceinline__ void pg_store(StoreState* ss, const Sched& s, const C
                 atomicExch(status, (int)KDW_STATUS_TMA_TIMEOUT);
                 break;
             }
-            tma_store_5d(status, &tmy, out0 + b * Cfg::OUT_STRIDE, it.g.c0, it.g.d0, it.g.w0, it.q - 1 - y_h0, it.g.n);
+            tile_store_out<typename Cfg::Geo>(status, &tmy, out0 + b * Cfg::OUT_STRIDE, it.g.c0, it.g.d0, it.g.w0,
+                                              it.q - 1 - y_h0, it.g.n);
             tma_commit();
             tma_wait_read_all();  // the store has read the tile: the consumers may overwrite it
             mbar_arrive(ofree0 + 8 * b);
@@ -270,17 +271,13 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
     // 16*ud + 2g + t; output voxel k of unit u: w index 4*(uwg*UPW+u) + 2k + (t>>1), d index 16*ud + 2g + (t&1).
     // Rows four apart (and units, and the two output rows) differ by a whole number of swizzle periods, so their
     // offsets differ by a constant: four input offsets and one output offset are kept in registers.
-    constexpr uint32_t IN_ROW4 = 4 * (Cfg::DT + 2) * Cfg::VOXB, OUT_ROW2 = 2 * Cfg::DT * Cfg::VOXB;
-    constexpr uint32_t SWZ_PERIOD = 8 * (Cfg::SWZ ? Cfg::SWZ : 1);
-    static_assert(Cfg::SWZ == 0 || (IN_ROW4 % SWZ_PERIOD == 0 && OUT_ROW2 % SWZ_PERIOD == 0),
-                  "row steps must preserve the swizzle phase");
+    using Geo = typename Cfg::Geo;
+    constexpr uint32_t IN_ROW4 = Geo::IN_ROW4, OUT_ROW2 = Geo::OUT_ROW2;
     uint32_t in_off[4], out_off;
 #pragma unroll
     for (int r = 0; r < 4; ++r)
-        in_off[r] = swz<Cfg::SWZ>(
-            (uint32_t)(((4 * uwg * UPW + r) * (Cfg::DT + 2) + 16 * ud + 2 * g + t) * Cfg::VOXB + 16 * ng));
-    out_off = swz<Cfg::SWZ>(
-        (uint32_t)(((4 * uwg * UPW + (t >> 1)) * Cfg::DT + 16 * ud + 2 * g + (t & 1)) * Cfg::VOXB + 16 * ng));
+        in_off[r] = swz<Cfg::SWZ>(Geo::in_off(4 * uwg * UPW + r, Geo::DPAD - 1 + 16 * ud + 2 * g + t) + 16 * ng);
+    out_off = swz<Cfg::SWZ>(Geo::out_off(4 * uwg * UPW + (t >> 1), 16 * ud + 2 * g + (t & 1)) + 16 * ng);
 
     uint32_t Bf[4][3][2][2];   // weight fragments [channel pair][a][k16 step][k half]
     float S0[UPW][4][4], S1[UPW][4][4];  // no initialisation: a plane's sum starts with an mma that ignores them
@@ -372,11 +369,9 @@ struct PgArgs {
 template <class Cfg>
 static int launch_fprop_pg(const PgArgs& a) {
     CUtensorMap tmx, tmy;
-    int rc = encode_volume_map(&tmx, a.x, a.N, a.C, a.Hx, a.W, a.D, a.xsN, a.xsH, a.xsW, Cfg::CS, Cfg::DT + 2,
-                               Cfg::WT + 2, false, Cfg::SWZ);
+    int rc = encode_tile_map<typename Cfg::Geo>(&tmx, a.x, a.N, a.C, a.Hx, a.W, a.D, a.xsN, a.xsH, a.xsW, true);
     if (rc) return rc;
-    rc = encode_volume_map(&tmy, a.y, a.N, a.C, a.Hy, a.W, a.D, a.ysN, a.ysH, a.ysW, Cfg::CS, Cfg::DT, Cfg::WT, false,
-                           Cfg::SWZ);
+    rc = encode_tile_map<typename Cfg::Geo>(&tmy, a.y, a.N, a.C, a.Hy, a.W, a.D, a.ysN, a.ysH, a.ysW, false);
     if (rc) return rc;
     if (((uintptr_t)a.w & 1) != 0) {
         set_error("weight pointer must be 2-byte aligned");
@@ -400,18 +395,22 @@ static int launch_fprop_pg(const PgArgs& a) {
 
 typedef int (*PgLaunch)(const PgArgs&);
 struct PgVariant {
-    int cs, dt, wt;
+    int cs, dt, wt, mode;
     PgLaunch f;
 };
-// PCfg<CS, WW, WD, UPW, ST>: tile 4*WW x 16*WD voxels (w, d), CS channels; 8 consumer warps, two units each
-#define KDW_PG(CS, WW, WD, UPW, ST) {CS, 16 * WD, 4 * WW, &launch_fprop_pg<PCfg<CS, WW, WD, UPW, ST>>}
+// PCfg<CS, WW, WD, UPW, ST, MODE>: tile 4*WW x 16*WD voxels (w, d), CS channels; 8 consumer warps, two units each;
+// MODE: how the tiles are staged (TileGeo): 0 any C that is a multiple of CS, 1 C == 8, 2 C == 16 and D even
+#define KDW_PG(CS, WW, WD, UPW, ST, MODE) {CS, 16 * WD, 4 * WW, MODE, &launch_fprop_pg<PCfg<CS, WW, WD, UPW, ST, MODE>>}
 static const PgVariant g_pg_variants[] = {
-    KDW_PG(64, 2, 1, 2, 4),  // 0: tile 8 x 16
-    KDW_PG(32, 4, 1, 2, 4),  // 1: tile 16 x 16
-    KDW_PG(16, 4, 2, 2, 4),  // 2: tile 16 x 32
-    KDW_PG(8, 4, 4, 2, 4),   // 3: tile 16 x 64
-    KDW_PG(32, 2, 2, 2, 4),  // 4: tile 8 x 32
-    KDW_PG(64, 2, 1, 2, 5),  // 5: as 0, five stages
+    KDW_PG(64, 2, 1, 2, 4, 0),  // 0: tile 8 x 16
+    KDW_PG(32, 4, 1, 2, 4, 0),  // 1: tile 16 x 16
+    KDW_PG(16, 4, 2, 2, 4, 0),  // 2: tile 16 x 32
+    KDW_PG(8, 4, 4, 2, 4, 0),   // 3: tile 16 x 64
+    KDW_PG(32, 2, 2, 2, 4, 0),  // 4: tile 8 x 32
+    KDW_PG(64, 2, 1, 2, 5, 0),  // 5: as 0, five stages
+    KDW_PG(8, 4, 4, 2, 4, 1),   // 6: C == 8, tile 16 x 64, long box rows
+    KDW_PG(16, 4, 2, 2, 4, 2),  // 7: C == 16, D even, tile 16 x 32, 64-byte box rows
+    KDW_PG(16, 8, 1, 2, 4, 2),  // 8: C == 16, D even, tile 32 x 16
 };
 #undef KDW_PG
 static const int g_n_pg_variants = (int)(sizeof(g_pg_variants) / sizeof(g_pg_variants[0]));
@@ -428,6 +427,12 @@ void fprop_mma_variant_tile(int which, int* wt, int* dt) {
     *dt = g_pg_variants[which].dt;
 }
 
+// whether variant `which` can run this (C, D): the merged-map variants need C equal to their slice (and an even D)
+bool fprop_mma_variant_fits(int which, int64_t C, int64_t D) {
+    const PgVariant& v = g_pg_variants[which];
+    return C % v.cs == 0 && (v.mode == 0 || C == v.cs) && (v.mode != 2 || (D & 1) == 0);
+}
+
 int launch_fprop_mma_variant(int which, const void* x, const void* w, void* y, int64_t N, int64_t C, int64_t Hx,
                              int64_t W, int64_t D, int64_t xsN, int64_t xsH, int64_t xsW, int64_t Hy, int64_t ysN,
                              int64_t ysH, int64_t ysW, int h_begin, int h_end, int y_h0, cudaStream_t stream) {
@@ -436,9 +441,9 @@ int launch_fprop_mma_variant(int which, const void* x, const void* w, void* y, i
         return KDW_ERR_TUNE;
     }
     const PgVariant& v = g_pg_variants[which];
-    if (C % v.cs != 0) {
-        set_error("fprop: tensor-core variant %d works on %d-channel slices, C=%lld is not a multiple", which, v.cs,
-                  (long long)C);
+    if (C % v.cs != 0 || (v.mode != 0 && C != v.cs) || (v.mode == 2 && (D & 1))) {
+        set_error("fprop: tensor-core variant %d needs C %s %d%s (C=%lld, D=%lld)", which, v.mode ? "==" : "a multiple of",
+                  v.cs, v.mode == 2 ? " and an even D" : "", (long long)C, (long long)D);
         return KDW_ERR_TUNE;
     }
     PgArgs a{x, w, y, N, C, Hx, W, D, xsN, xsH, xsW, Hy, ysN, ysH, ysW, h_begin, h_end, y_h0, stream};

@@ -335,9 +335,10 @@ struct WgradCand {
     float rel;
 };
 void wgrad_mma_variant_tile(int which, int* wt, int* dt);
+bool wgrad_mma_variant_fits(int which, int64_t C, int64_t D);
 static const int kTW = (int)(sizeof(g_wgrad_variants) / sizeof(g_wgrad_variants[0]));  // tensor-core variant i: kTW + 1 + i
-static const WgradCand kWgradCand8[] = {{kTW + 4, 1.00f}, {24, 1.13f}, {11, 1.20f}, {1, 1.23f}};
-static const WgradCand kWgradCand16[] = {{kTW + 3, 1.00f}, {1, 1.75f}, {2, 2.00f}};
+static const WgradCand kWgradCand8[] = {{kTW + 7, 1.00f}, {kTW + 4, 1.48f}, {24, 1.70f}, {11, 1.80f}, {1, 1.85f}};
+static const WgradCand kWgradCand16[] = {{kTW + 8, 1.00f}, {kTW + 9, 1.10f}, {kTW + 3, 1.18f}, {1, 2.00f}, {2, 2.30f}};
 static const WgradCand kWgradCand32[] = {{kTW + 2, 1.00f}, {kTW + 3, 1.03f}, {kTW + 6, 1.04f}, {14, 1.70f}};
 static const WgradCand kWgradCand64[] = {{kTW + 6, 1.00f}, {kTW + 1, 1.03f}, {kTW + 5, 1.09f}, {22, 1.65f}};
 static const WgradCand kWgradCand128[] = {{kTW + 1, 1.00f}, {kTW + 5, 1.02f}, {kTW + 2, 1.14f}, {22, 1.78f}};
@@ -366,6 +367,7 @@ static int auto_wgrad_variant(int64_t C, int64_t W, int64_t D, bool table_only =
     double best_cost = 0.0;
     for (int i = 0; i < n; ++i) {
         if (table_only && cand[i].id > kTW) continue;
+        if (cand[i].id > kTW && !wgrad_mma_variant_fits(cand[i].id - kTW - 1, C, D)) continue;
         int wt = 1, dt = 1;
         wgrad_variant_tile(cand[i].id, &wt, &dt);
         const double padded = (double)((W + wt - 1) / wt * wt) * (double)((D + dt - 1) / dt * dt);

@@ -23,7 +23,7 @@
 
 namespace kdw {
 
-template <int CS_, int WW_, int WD_, int UPW_, int ST_>
+template <int CS_, int WW_, int WD_, int UPW_, int ST_, int MODE_ = 0>
 struct WPCfg {
     static constexpr int CS = CS_, WW = WW_, WD = WD_, UPW = UPW_, ST = ST_;
     static constexpr int NG = CS / 8;               // channel groups of 8
@@ -39,17 +39,16 @@ struct WPCfg {
     static constexpr int REGS_HELPER = 40, REGS_CONSUMER = 232;
     static constexpr int WT = 4 * WW, DT = 16 * WD;
     static constexpr int VOXB = CS * 2;
-    static constexpr int SWZ = CS == 8 ? 0 : VOXB;
-    static constexpr int X_BYTES = (WT + 2) * (DT + 2) * VOXB;
-    static constexpr int X_STRIDE = (X_BYTES + 1023) / 1024 * 1024;
-    static constexpr int G_BYTES = WT * DT * VOXB;
-    static constexpr int G_STRIDE = (G_BYTES + 1023) / 1024 * 1024;
+    using Geo = TileGeo<CS, WT, DT, MODE_>;  // staging of the x ("in") and grad ("out") tiles and their TMA boxes
+    static constexpr int SWZ = Geo::SWZ;
+    static constexpr int X_BYTES = Geo::IN_BYTES, X_STRIDE = Geo::IN_STRIDE;
+    static constexpr int G_BYTES = Geo::OUT_BYTES, G_STRIDE = Geo::OUT_STRIDE;
     static constexpr int STAGE = X_STRIDE + G_STRIDE;
     static constexpr int SCRATCH = 32 * 16 * 4;     // per warp: 16 floats per lane (one plane a of the flush)
     static constexpr int SMEM = ST * STAGE + NCW * SCRATCH + 16 * ST + 4 * ST + 128 + 1024;
     static_assert(CS == 8 || CS == 16 || CS == 32 || CS == 64, "a voxel must be one swizzle span (or 16 bytes)");
     static_assert(WW % UPW == 0 && NCW == 8, "two consumer warpgroups");
-    static_assert(DT + 2 <= 256 && WT + 2 <= 256, "TMA box limits");
+    static_assert(DT + 4 <= 256 && WT + 2 <= 256, "TMA box limits");
 };
 
 // x plane q of one unit against the grad planes q+1 (a=0), q (a=1), q-1 (a=2).  R = (step count) % 3 names the
@@ -157,10 +156,10 @@ __device__ __forceinline__ void wg_produce(ProdState* ps, const Sched& s, const 
     const bool with_g = it.q + 1 < it.g.he;  // grad plane q+1 is owned by the segment
     st_shared_u32(desc0 + 4 * st, ((uint32_t)it.g.c0 << 8) | (it.q == it.g.hb - 1 ? 2u : 0u) | (with_g ? 1u : 0u));
     mbar_expect_tx(bar, Cfg::X_BYTES + (with_g ? Cfg::G_BYTES : 0));
-    tma_load_5d(status, stage0 + st * Cfg::STAGE, &tmx, bar, it.g.c0, it.g.d0 - 1, it.g.w0 - 1, it.q, it.g.n);
+    tile_load_in<typename Cfg::Geo>(status, stage0 + st * Cfg::STAGE, &tmx, bar, it.g.c0, it.g.d0, it.g.w0, it.q, it.g.n);
     if (with_g)
-        tma_load_5d(status, stage0 + st * Cfg::STAGE + Cfg::X_STRIDE, &tmg, bar, it.g.c0, it.g.d0, it.g.w0,
-                    it.q + 1 - g_h0, it.g.n);
+        tile_load_out<typename Cfg::Geo>(status, stage0 + st * Cfg::STAGE + Cfg::X_STRIDE, &tmg, bar, it.g.c0, it.g.d0,
+                                         it.g.w0, it.q + 1 - g_h0, it.g.n);
     it.next(s);
     ps->it = it;
     ps->pi = pi + 1;
@@ -221,17 +220,13 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
     const int su = cw / Cfg::NG;                   // spatial warp group
     const int uwg = su % (Cfg::WW / UPW), ud = su / (Cfg::WW / UPW);
     const int g = lane >> 2, t = lane & 3;
-    constexpr uint32_t IN_ROW4 = 4 * (Cfg::DT + 2) * Cfg::VOXB, G_ROW2 = 2 * Cfg::DT * Cfg::VOXB;
-    constexpr uint32_t SWZ_PERIOD = 8 * (Cfg::SWZ ? Cfg::SWZ : 1);
-    static_assert(Cfg::SWZ == 0 || (IN_ROW4 % SWZ_PERIOD == 0 && G_ROW2 % SWZ_PERIOD == 0),
-                  "row steps must preserve the swizzle phase");
+    using Geo = typename Cfg::Geo;
+    constexpr uint32_t IN_ROW4 = Geo::IN_ROW4, G_ROW2 = Geo::OUT_ROW2;
     uint32_t in_off[4], g_off;
 #pragma unroll
     for (int r = 0; r < 4; ++r)
-        in_off[r] = swz<Cfg::SWZ>(
-            (uint32_t)(((4 * uwg * UPW + r) * (Cfg::DT + 2) + 16 * ud + 2 * g + t) * Cfg::VOXB + 16 * ng));
-    g_off = Cfg::X_STRIDE + swz<Cfg::SWZ>((uint32_t)(((4 * uwg * UPW + (t >> 1)) * Cfg::DT + 16 * ud + 2 * g + (t & 1)) *
-                                                         Cfg::VOXB + 16 * ng));
+        in_off[r] = swz<Cfg::SWZ>(Geo::in_off(4 * uwg * UPW + r, Geo::DPAD - 1 + 16 * ud + 2 * g + t) + 16 * ng);
+    g_off = Cfg::X_STRIDE + swz<Cfg::SWZ>(Geo::out_off(4 * uwg * UPW + (t >> 1), 16 * ud + 2 * g + (t & 1)) + 16 * ng);
     float* scratch = scratch0 + cw * (Cfg::SCRATCH / 4);
     float* row = ws + ((size_t)blockIdx.x * Cfg::SU + su) * KC;
 
@@ -314,11 +309,9 @@ struct WpgArgs {
 template <class Cfg>
 static int launch_wgrad_pg(const WpgArgs& a, int* rows_used) {
     CUtensorMap tmx, tmg;
-    int rc = encode_volume_map(&tmx, a.x, a.N, a.C, a.Hx, a.W, a.D, a.xsN, a.xsH, a.xsW, Cfg::CS, Cfg::DT + 2,
-                               Cfg::WT + 2, false, Cfg::SWZ);
+    int rc = encode_tile_map<typename Cfg::Geo>(&tmx, a.x, a.N, a.C, a.Hx, a.W, a.D, a.xsN, a.xsH, a.xsW, true);
     if (rc) return rc;
-    rc = encode_volume_map(&tmg, a.g, a.N, a.C, a.Hg, a.W, a.D, a.gsN, a.gsH, a.gsW, Cfg::CS, Cfg::DT, Cfg::WT, false,
-                           Cfg::SWZ);
+    rc = encode_tile_map<typename Cfg::Geo>(&tmg, a.g, a.N, a.C, a.Hg, a.W, a.D, a.gsN, a.gsH, a.gsW, false);
     if (rc) return rc;
     static KernelSetup setup;  // one per kernel instantiation
     auto kern = wgrad_pg_kernel<Cfg>;
@@ -344,18 +337,22 @@ static int launch_wgrad_pg(const WpgArgs& a, int* rows_used) {
 
 typedef int (*WpgLaunch)(const WpgArgs&, int*);
 struct WpgVariant {
-    int cs, dt, wt;
+    int cs, dt, wt, mode;
     WpgLaunch f;
 };
-// WPCfg<CS, WW, WD, UPW, ST>: tile 4*WW x 16*WD voxels (w, d), CS channels; 8 consumer warps, two units each
-#define KDW_WPG(CS, WW, WD, UPW, ST) {CS, 16 * WD, 4 * WW, &launch_wgrad_pg<WPCfg<CS, WW, WD, UPW, ST>>}
+// WPCfg<CS, WW, WD, UPW, ST, MODE>: tile 4*WW x 16*WD voxels (w, d), CS channels; 8 consumer warps, two units each;
+// MODE: how the tiles are staged (TileGeo): 0 any C that is a multiple of CS, 1 C == 8, 2 C == 16 and D even
+#define KDW_WPG(CS, WW, WD, UPW, ST, MODE) {CS, 16 * WD, 4 * WW, MODE, &launch_wgrad_pg<WPCfg<CS, WW, WD, UPW, ST, MODE>>}
 static const WpgVariant g_wpg_variants[] = {
-    KDW_WPG(64, 2, 1, 2, 3),  // 0: tile 8 x 16
-    KDW_WPG(32, 4, 1, 2, 4),  // 1: tile 16 x 16
-    KDW_WPG(16, 4, 2, 2, 4),  // 2: tile 16 x 32
-    KDW_WPG(8, 4, 4, 2, 4),   // 3: tile 16 x 64
-    KDW_WPG(64, 2, 1, 2, 4),  // 4: as 0, four stages
-    KDW_WPG(32, 2, 2, 2, 4),  // 5: tile 8 x 32
+    KDW_WPG(64, 2, 1, 2, 3, 0),  // 0: tile 8 x 16
+    KDW_WPG(32, 4, 1, 2, 4, 0),  // 1: tile 16 x 16
+    KDW_WPG(16, 4, 2, 2, 4, 0),  // 2: tile 16 x 32
+    KDW_WPG(8, 4, 4, 2, 4, 0),   // 3: tile 16 x 64
+    KDW_WPG(64, 2, 1, 2, 4, 0),  // 4: as 0, four stages
+    KDW_WPG(32, 2, 2, 2, 4, 0),  // 5: tile 8 x 32
+    KDW_WPG(8, 4, 4, 2, 4, 1),   // 6: C == 8, tile 16 x 64, long box rows
+    KDW_WPG(16, 4, 2, 2, 4, 2),  // 7: C == 16, D even, tile 16 x 32, 64-byte box rows
+    KDW_WPG(16, 8, 1, 2, 4, 2),  // 8: C == 16, D even, tile 32 x 16
 };
 #undef KDW_WPG
 static const int g_n_wpg_variants = (int)(sizeof(g_wpg_variants) / sizeof(g_wpg_variants[0]));
@@ -372,6 +369,11 @@ void wgrad_mma_variant_tile(int which, int* wt, int* dt) {
     *dt = g_wpg_variants[which].dt;
 }
 
+bool wgrad_mma_variant_fits(int which, int64_t C, int64_t D) {
+    const WpgVariant& v = g_wpg_variants[which];
+    return C % v.cs == 0 && (v.mode == 0 || C == v.cs) && (v.mode != 2 || (D & 1) == 0);
+}
+
 int launch_wgrad_mma_variant(int which, const void* x, const void* grad, float* ws, int64_t ws_rows, int64_t N, int64_t C,
                              int64_t Hx, int64_t W, int64_t D, int64_t xsN, int64_t xsH, int64_t xsW, int64_t Hg,
                              int64_t gsN, int64_t gsH, int64_t gsW, int h_begin, int h_end, int g_h0,
@@ -381,9 +383,9 @@ int launch_wgrad_mma_variant(int which, const void* x, const void* grad, float* 
         return KDW_ERR_TUNE;
     }
     const WpgVariant& v = g_wpg_variants[which];
-    if (C % v.cs != 0) {
-        set_error("wgrad: tensor-core variant %d works on %d-channel slices, C=%lld is not a multiple", which, v.cs,
-                  (long long)C);
+    if (C % v.cs != 0 || (v.mode != 0 && C != v.cs) || (v.mode == 2 && (D & 1))) {
+        set_error("wgrad: tensor-core variant %d needs C %s %d%s (C=%lld, D=%lld)", which, v.mode ? "==" : "a multiple of",
+                  v.cs, v.mode == 2 ? " and an even D" : "", (long long)C, (long long)D);
         return KDW_ERR_TUNE;
     }
     WpgArgs a{x, grad, ws, ws_rows, N, C, Hx, W, D, xsN, xsH, xsW, Hg, gsN, gsH, gsW, h_begin, h_end, g_h0, stream};

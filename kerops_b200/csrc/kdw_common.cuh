@@ -49,6 +49,11 @@ int encode_volume_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, 
 int encode_merged_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
                       int64_t strideN, int64_t strideH, int64_t strideW, int boxDC, int boxW);
 
+// The volume with PAIRS of voxels along d as the innermost axis: dims (2*C, D/2, W, H, N), box (2*C, boxP, boxW, 1,
+// 1), 64-byte swizzle.  Needs C == 16 (64-byte rows) and an even D.
+int encode_paired_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
+                      int64_t strideN, int64_t strideH, int64_t strideW, int boxP, int boxW);
+
 int device_sm_count(int* sms);
 
 // Per kernel and device: the opt-in to `smem` bytes of dynamic shared memory, the CTAs per SM the kernel reaches

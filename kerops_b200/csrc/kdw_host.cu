@@ -172,6 +172,36 @@ int encode_merged_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, 
     return 0;
 }
 
+int encode_paired_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
+                      int64_t strideN, int64_t strideH, int64_t strideW, int boxP, int boxW) {
+    EncodeTiledFn fn;
+    int rc = get_encode_fn(&fn);
+    if (rc) return rc;
+    if (((uintptr_t)base & 15) != 0 || C != 16 || (D & 1) != 0 || (strideW % 8) != 0 || (strideH % 8) != 0 ||
+        (strideN % 8) != 0) {
+        set_error("paired tensor map needs C == 16, an even D, a 16-byte aligned base and strides that are multiples of 8");
+        return KDW_ERR_ALIGN;
+    }
+    if (boxP < 1 || boxP > 256 || boxW < 1 || boxW > 256) {
+        set_error("tensor-map box out of range");
+        return KDW_ERR_ARG;
+    }
+    const cuuint64_t dims[5] = {(cuuint64_t)(2 * C), (cuuint64_t)(D / 2), (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+    cuuint64_t strides[4] = {(cuuint64_t)C * 4, (cuuint64_t)strideW * 2, (cuuint64_t)strideH * 2, (cuuint64_t)strideN * 2};
+    for (int i = 0; i < 4; ++i)
+        if (strides[i] == 0) strides[i] = 16;
+    const cuuint32_t box[5] = {(cuuint32_t)(2 * C), (cuuint32_t)boxP, (cuuint32_t)boxW, 1, 1};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled (paired d axis) failed with CUresult %d", (int)r);
+        return (int)r;
+    }
+    return 0;
+}
+
 int make_sched(Sched* s, int64_t N, int64_t C, int64_t W, int64_t D, int h_begin, int h_end, int WT, int DT, int CS,
                int grid_target) {
     s->WT = WT;

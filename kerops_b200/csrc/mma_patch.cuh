@@ -21,6 +21,95 @@ KDW_HD uint32_t swz(uint32_t off) {
     return SWZ == 0 ? off : off ^ (((off >> 7) & (uint32_t)(SWZ / 16 - 1)) << 4);
 }
 
+// How a tile of the volume is staged in shared memory and which TMA boxes fill it.
+//   MODE 0: 5-D tensor map (C, D, W, H, N), one box per tile and plane, rows of one voxel (2*CS bytes) with the
+//           swizzle whose span is one voxel (none for 16-byte voxels).
+//   MODE 1: C == CS == 8: tensor map with the d and c axes merged, (D*C, W, H, N), so that a box row is a run of
+//           up to 32 voxels instead of 16 bytes - the TMA unit handles a fixed number of box rows per clock, and
+//           16-byte rows cap a kernel at less than half the HBM rate.  The d range of a tile is cut into NBX boxes
+//           staged one after the other: [box][w][KD][c].  16-byte voxels need no swizzle.
+//   MODE 2: C == CS == 16 and D even: 5-D map whose innermost axis is a PAIR of voxels, (2*16, D/2, W, H, N):
+//           64-byte rows with the 64-byte swizzle (conflict-free like MODE 0).  A tile then starts at an even d, one
+//           voxel earlier than the stencil needs.
+// "in" is the halo'd input tile of a plane ((WT+2) x DIN voxels, the tile's first voxel at (1, DPAD)), "out" the
+// WT x DT tile of outputs (or of grad in the weight gradient).
+template <int CS_, int WT_, int DT_, int MODE_>
+struct TileGeo {
+    static constexpr int CS = CS_, WT = WT_, DT = DT_, MODE = MODE_;
+    static constexpr int VOXB = CS * 2;
+    static constexpr int SWZ = MODE == 1 ? 0 : (MODE == 2 ? 64 : (CS == 8 ? 0 : VOXB));
+    static constexpr int DPAD = MODE == 2 ? 2 : 1;
+    static constexpr int DIN = DT + 2 * DPAD;  // MODE 2 stages one voxel more than needed at either end (whole pairs)
+    static constexpr int NBX = MODE == 1 ? (DIN + 31) / 32 : 1;
+    static constexpr int KD = (DIN + NBX - 1) / NBX;
+    static constexpr int IN_BOX = ((WT + 2) * KD * VOXB + 127) / 128 * 128;  // bytes from one box to the next
+    static constexpr int IN_BYTES = NBX * (WT + 2) * KD * VOXB;              // bytes the copies of a plane deliver
+    static constexpr int IN_STRIDE = (NBX * IN_BOX + 1023) / 1024 * 1024;
+    static constexpr int NBO = MODE == 1 ? (DT + 31) / 32 : 1;
+    static constexpr int KDO = DT / NBO;
+    static constexpr int OUT_BOX = WT * KDO * VOXB;
+    static constexpr int OUT_BYTES = WT * DT * VOXB;
+    static constexpr int OUT_STRIDE = (OUT_BYTES + 1023) / 1024 * 1024;
+    static_assert(MODE == 0 || (MODE == 1 && CS == 8) || (MODE == 2 && CS == 16), "merged maps need CS == C");
+    static_assert(DT % NBO == 0 && OUT_BOX % 128 == 0, "output boxes");
+    static_assert(MODE != 1 || (KD * CS <= 256 && KDO * CS <= 256), "a box row holds at most 256 elements");
+    static_assert(MODE != 2 || (DIN % 2 == 0 && DT % 2 == 0), "pairs of voxels");
+    // byte offset (before the swizzle) of input voxel (row wr, column dd of the staged tile) / output voxel (wr, dd)
+    KDW_HD static constexpr uint32_t in_off(int wr, int dd) {
+        return (uint32_t)((dd / KD) * IN_BOX + (wr * KD + dd % KD) * VOXB);
+    }
+    KDW_HD static constexpr uint32_t out_off(int wr, int dd) {
+        return (uint32_t)((dd / KDO) * OUT_BOX + (wr * KDO + dd % KDO) * VOXB);
+    }
+    // rows four apart in the input tile / two apart in the output tile differ by a constant that preserves the
+    // swizzle phase
+    static constexpr uint32_t IN_ROW4 = 4 * KD * VOXB, OUT_ROW2 = 2 * KDO * VOXB;
+    static constexpr uint32_t SWZ_PERIOD = 8 * (SWZ ? SWZ : 1);
+    static_assert(SWZ == 0 || (IN_ROW4 % SWZ_PERIOD == 0 && OUT_ROW2 % SWZ_PERIOD == 0), "row steps and swizzle phase");
+};
+
+// The copies of one input tile (plane q of sample n, tile origin (w0, d0), channel slice c0) into `dst`, all
+// completing on `bar`; and the store of / the copy of one output-shaped tile.
+template <class Geo>
+__device__ __forceinline__ void tile_load_in(int* status, uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int d0,
+                                             int w0, int q, int n) {
+    if (Geo::MODE == 1) {
+#pragma unroll
+        for (int k = 0; k < Geo::NBX; ++k)
+            tma_load_5d(status, dst + k * Geo::IN_BOX, tm, bar, (d0 - Geo::DPAD + k * Geo::KD) * Geo::CS, w0 - 1, q, n, 0);
+    } else if (Geo::MODE == 2) {
+        tma_load_5d(status, dst, tm, bar, 0, (d0 - Geo::DPAD) / 2, w0 - 1, q, n);
+    } else {
+        tma_load_5d(status, dst, tm, bar, c0, d0 - Geo::DPAD, w0 - 1, q, n);
+    }
+}
+template <class Geo>
+__device__ __forceinline__ void tile_load_out(int* status, uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0,
+                                              int d0, int w0, int h, int n) {
+    if (Geo::MODE == 1) {
+#pragma unroll
+        for (int k = 0; k < Geo::NBO; ++k)
+            tma_load_5d(status, dst + k * Geo::OUT_BOX, tm, bar, (d0 + k * Geo::KDO) * Geo::CS, w0, h, n, 0);
+    } else if (Geo::MODE == 2) {
+        tma_load_5d(status, dst, tm, bar, 0, d0 / 2, w0, h, n);
+    } else {
+        tma_load_5d(status, dst, tm, bar, c0, d0, w0, h, n);
+    }
+}
+template <class Geo>
+__device__ __forceinline__ void tile_store_out(int* status, const CUtensorMap* tm, uint32_t src, int c0, int d0, int w0,
+                                               int h, int n) {
+    if (Geo::MODE == 1) {
+#pragma unroll
+        for (int k = 0; k < Geo::NBO; ++k)
+            tma_store_5d(status, tm, src + k * Geo::OUT_BOX, (d0 + k * Geo::KDO) * Geo::CS, w0, h, n, 0);
+    } else if (Geo::MODE == 2) {
+        tma_store_5d(status, tm, src, 0, d0 / 2, w0, h, n);
+    } else {
+        tma_store_5d(status, tm, src, c0, d0, w0, h, n);
+    }
+}
+
 // d = a * b + c (m16n8k16, fp16 operands, fp32 accumulate); ZERO: c = 0.  The four A registers and the four
 // accumulator registers of an mma are register QUADS (consecutive registers) in the machine instruction, the two
 // B registers a pair; Quad / the arrays below are laid out accordingly.
@@ -89,4 +178,27 @@ struct ProdState {
     int done;      // end marker written, test hook reached, or a wait ran out
 };
 
+// Host: the tensor maps of a TileGeo over volume `base` (H planes); `in` selects the halo'd input box.
+template <class Geo>
+int encode_tile_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
+                    int64_t sN, int64_t sH, int64_t sW, bool in) {
+    if (Geo::MODE == 1) {
+        if (C != Geo::CS) {
+            set_error("this kernel variant needs C == %d", Geo::CS);
+            return KDW_ERR_TUNE;
+        }
+        return encode_merged_map(map, base, N, C, H, W, D, sN, sH, sW, (in ? Geo::KD : Geo::KDO) * Geo::CS,
+                                 in ? Geo::WT + 2 : Geo::WT);
+    }
+    if (Geo::MODE == 2) {
+        if (C != Geo::CS || (D & 1)) {
+            set_error("this kernel variant needs C == %d and an even D", Geo::CS);
+            return KDW_ERR_TUNE;
+        }
+        return encode_paired_map(map, base, N, C, H, W, D, sN, sH, sW, (in ? Geo::DIN : Geo::DT) / 2,
+                                 in ? Geo::WT + 2 : Geo::WT);
+    }
+    return encode_volume_map(map, base, N, C, H, W, D, sN, sH, sW, Geo::CS, in ? Geo::DIN : Geo::DT,
+                             in ? Geo::WT + 2 : Geo::WT, false, Geo::SWZ);
+}
 }  // namespace kdw

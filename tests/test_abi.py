@@ -61,10 +61,12 @@ def test_auto_variant_follows_the_shape(kdw_lib):
     12 / 24 CUDA-core table variants); a depth that a deep tile would pad heavily gets a shallower tile; every
     choice is a variant whose channel slice divides C."""
     lib = kdw_lib
-    assert [lib.kdw_fprop_auto_variant(C, 350, 128) for C in (8, 16, 32, 64, 128)] == [16, 15, 17, 13, 13]
-    assert [lib.kdw_wgrad_auto_variant(C, 350, 128) for C in (8, 16, 32, 64, 128)] == [28, 27, 26, 30, 25]
+    assert [lib.kdw_fprop_auto_variant(C, 350, 128) for C in (8, 16, 32, 64, 128)] == [19, 20, 17, 13, 13]
+    assert [lib.kdw_wgrad_auto_variant(C, 350, 128) for C in (8, 16, 32, 64, 128)] == [31, 32, 26, 30, 25]
     assert lib.kdw_fprop_auto_variant(32, 350, 40) != 17   # 32-deep tiles would compute 64 of 40 planes
-    assert lib.kdw_fprop_auto_variant(8, 48, 24) != 16     # 64-deep tiles would compute 64 of 24 planes
+    assert lib.kdw_wgrad_auto_variant(8, 48, 24) != 31     # 64-deep tiles would compute 64 of 24 planes
+    assert lib.kdw_fprop_auto_variant(16, 350, 127) not in (20, 21)  # the paired-voxel tensor map needs an even D
+    assert lib.kdw_wgrad_auto_variant(16, 350, 127) not in (32, 33)
     for C in (8, 16, 32, 64, 128, 256):
         for W, D in ((350, 128), (16, 8), (40, 40), (97, 61), (1, 1)):
             f, w = lib.kdw_fprop_auto_variant(C, W, D), lib.kdw_wgrad_auto_variant(C, W, D)
