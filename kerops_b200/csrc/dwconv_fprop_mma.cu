@@ -73,13 +73,6 @@ template <class Cfg>
 __device__ __forceinline__ void pg_step(const uint4 (&X)[6], const uint32_t (&Bf)[4][3][2][2], float (&FIN)[4][4],
                                         float (&MID)[4][4], bool store, uint32_t out_addr0, uint32_t out_addr1,
                                         uint32_t zero) {
-#if defined(KDW_PG_PROBE) && KDW_PG_PROBE == 1
-    if (store) {
-        sts128(out_addr0, X[1]);
-        sts128(out_addr1, X[3]);
-    }
-    return;
-#endif
     Quad Q[2][4];
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks) {
@@ -92,23 +85,14 @@ __device__ __forceinline__ void pg_step(const uint4 (&X)[6], const uint32_t (&Bf
         Q[ks][3].r[0] = reg_copy(X[2 * ks].w, zero), Q[ks][3].r[1] = reg_copy(X[2 * ks + 2].w, zero);
         Q[ks][3].r[2] = reg_copy(X[2 * ks + 1].w, zero), Q[ks][3].r[3] = reg_copy(X[2 * ks + 3].w, zero);
     }
-#if defined(KDW_PG_PROBE) && KDW_PG_PROBE == 2
-    if (store) {
-        sts128(out_addr0, make_uint4(Q[0][0].r[0] ^ Q[1][0].r[0], Q[0][1].r[1] ^ Q[1][1].r[1], Q[0][2].r[2] ^ Q[1][2].r[2], Q[0][3].r[3] ^ Q[1][3].r[3]));
-        sts128(out_addr1, make_uint4(Q[0][0].r[1] ^ Q[1][0].r[2], Q[0][1].r[2] ^ Q[1][1].r[3], Q[0][2].r[3] ^ Q[1][2].r[0], Q[0][3].r[0] ^ Q[1][3].r[1]));
-    }
-    return;
-#endif
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks)
 #pragma unroll
         for (int cp = 0; cp < 4; ++cp) mma16816<false>(FIN[cp], Q[ks][cp], Bf[cp][2][ks][0], Bf[cp][2][ks][1]);
-#if !(defined(KDW_PG_PROBE) && KDW_PG_PROBE == 3)
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks)
 #pragma unroll
         for (int cp = 0; cp < 4; ++cp) mma16816<false>(MID[cp], Q[ks][cp], Bf[cp][1][ks][0], Bf[cp][1][ks][1]);
-#endif
     if (store) {
         uint4 o0, o1;  // block row g: outputs (t>>1, t&1) of block (bw=0); row g+8: the same of block (bw=1)
         o0.x = pack_h2(FIN[0][0], FIN[0][1]);
@@ -122,12 +106,10 @@ __device__ __forceinline__ void pg_step(const uint4 (&X)[6], const uint32_t (&Bf
         sts128(out_addr0, o0);
         sts128(out_addr1, o1);
     }
-#if !(defined(KDW_PG_PROBE) && KDW_PG_PROBE == 3)
 #pragma unroll
     for (int cp = 0; cp < 4; ++cp) mma16816<true>(FIN[cp], Q[0][cp], Bf[cp][0][0][0], Bf[cp][0][0][1]);
 #pragma unroll
     for (int cp = 0; cp < 4; ++cp) mma16816<false>(FIN[cp], Q[1][cp], Bf[cp][0][1][0], Bf[cp][0][1][1]);
-#endif
 }
 
 // Schedule position of the store warp, kept in shared memory like ProdState (the helper warps run on 40 registers).
