@@ -50,17 +50,16 @@ VOX = SHAPE[0] * SHAPE[1] * SHAPE[2]
 ALL_CHANNELS = [8, 16, 32, 64, 128]
 FALLBACK_HBM_GBS = 6650.0
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, from the ncu capture summarised in
-# profiles/fprop_wgrad_c8_c32_c128_planes100.md: captured on (1, C, 100, 350, 128) volumes and scaled by
-# 350/100 planes (traffic grows in proportion to the planes a launch processes).  Bytes per (1,C,350,350,128)
-# launch; None where no capture has been taken.
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the kernels the library chooses by itself, from one
+# `ncu --set full` capture on (1, C, 100, 350, 128) volumes, scaled by 350/100 planes (traffic grows in proportion to
+# the planes a launch processes).  Bytes per (1,C,350,350,128) launch; None where no capture has been taken.
 NCU_TRAFFIC = {
-    ('fprop', 8): int((0.078799 + 0.026727) * 3.5e9),
-    ('wgrad', 8): int((0.156367 + 0.004412) * 3.5e9),
-    ('fprop', 32): int((0.290660 + 0.248650) * 3.5e9),
-    ('wgrad', 32): int((0.581526 + 0.006321) * 3.5e9),
-    ('fprop', 128): int((1.344124 + 1.114130) * 3.5e9),
-    ('wgrad', 128): int((2.334769 + 0.006344) * 3.5e9),
+    ('fprop', 8): int((0.079654 + 0.026692) * 3.5e9),
+    ('wgrad', 8): int((0.151513 + 0.005427) * 3.5e9),
+    ('fprop', 32): int((0.290732 + 0.245913) * 3.5e9),
+    ('wgrad', 32): int((0.577497 + 0.005466) * 3.5e9),
+    ('fprop', 128): int((1.316454 + 1.107569) * 3.5e9),
+    ('wgrad', 128): int((2.548305 + 0.006967) * 3.5e9),
 }
 
 

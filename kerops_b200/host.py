@@ -1,6 +1,7 @@
 """Operators on HOST-resident volumes: the same DWConv / DWConvWGRAD arithmetic for callers whose
-activations live in (pinned) host memory, e.g. out-of-core volumes.  No counterpart in the
-reference, which only takes device tensors.
+activations live in (pinned) host memory.  They overlap the PCIe copies with the kernels; they do NOT
+bound device memory: full-size device copies of the volumes are allocated, so a volume must still fit
+on the device.  No counterpart in the reference, which only takes device tensors.
 
 The volume is cut into slabs of h-planes.  Three CUDA streams form a pipeline: slab i+1 is copied
 host->device while slab i is convolved (the plane-range entry points of the C-ABI read the halo

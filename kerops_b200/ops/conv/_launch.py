@@ -15,6 +15,9 @@ def _stream_ptr(device):
 
 
 def _env_tune(name):
+    """Kernel-variant override from the environment, for timing one variant through the unchanged Python operators:
+    KDW_FPROP_TUNE, KDW_WGRAD_TUNE, KDW_ADDSTATS_TUNE, KDW_BNRELU_TUNE = a variant id of the respective entry point
+    (1 .. kdw_*_variants()); unset or 0 = the library chooses.  An explicit `tune=` argument wins."""
     v = os.environ.get(name)
     return int(v) if v else 0
 

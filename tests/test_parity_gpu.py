@@ -210,6 +210,25 @@ def test_all_wgrad_variants(ops, kdw_lib):
         assert ran, f'weight-gradient variant {v} ran on none of the shapes'
 
 
+def test_sixteen_channel_slices_on_a_mid_size_volume(ops, kdw_lib):
+    """(1, 16, 40, 60, 64): the smallest volume on which a long-deleted weight-gradient kernel with 16-channel slices
+    stopped with CUDA error 715; every kernel that slices 16 channels today has to pass on it."""
+    _, _, _launch = ops
+    x, g, w = make_inputs(715, 1, 16, 40, 60, 64)
+    ref_y, ref_dw = to.fprop_shift_fp32(x, w), to.wgrad_fp64(x, g)
+    ran = 0
+    for v in [0] + [v for v in range(1, kdw_lib.kdw_fprop_variants() + 1) if kdw_lib.kdw_fprop_variant_channels(v) == 16]:
+        y = torch.full_like(x, float('nan'))
+        _launch.fprop(x, w, y, tune=v)
+        check_fprop(y, ref_y)
+        ran += 1
+    for v in [0] + [v for v in range(1, kdw_lib.kdw_wgrad_variants() + 1) if kdw_lib.kdw_wgrad_variant_channels(v) == 16]:
+        dw32, dw16 = _launch.wgrad(x, g, want_f32=True, want_f16=True, tune=v)
+        check_wgrad(dw32, dw16, ref_dw, bsize=1)
+        ran += 1
+    assert ran >= 6
+
+
 def test_acctype_float16_keyword(ops):
     DWConv, _, _ = ops
     x, _, w = make_inputs(77, 1, 16, 20, 21, 22)
