@@ -340,7 +340,7 @@ static const int kTW = (int)(sizeof(g_wgrad_variants) / sizeof(g_wgrad_variants[
 static const WgradCand kWgradCand8[] = {{kTW + 7, 1.00f}, {kTW + 4, 1.48f}, {24, 1.70f}, {11, 1.80f}, {1, 1.85f}};
 static const WgradCand kWgradCand16[] = {{kTW + 8, 1.00f}, {kTW + 9, 1.10f}, {kTW + 3, 1.18f}, {1, 2.00f}, {2, 2.30f}};
 static const WgradCand kWgradCand32[] = {{kTW + 2, 1.00f}, {kTW + 3, 1.03f}, {kTW + 6, 1.04f}, {14, 1.70f}};
-static const WgradCand kWgradCand64[] = {{kTW + 6, 1.00f}, {kTW + 1, 1.03f}, {kTW + 5, 1.09f}, {22, 1.65f}};
+static const WgradCand kWgradCand64[] = {{kTW + 1, 1.00f}, {kTW + 5, 1.03f}, {kTW + 6, 1.10f}, {kTW + 2, 1.11f}, {22, 1.65f}};
 static const WgradCand kWgradCand128[] = {{kTW + 1, 1.00f}, {kTW + 5, 1.02f}, {kTW + 2, 1.14f}, {22, 1.78f}};
 
 static void wgrad_variant_tile(int id, int* wt, int* dt) {
