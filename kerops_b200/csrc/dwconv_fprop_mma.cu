@@ -18,6 +18,17 @@
 // for a block-diagonal formulation over 8 channels; with the tensor pipe at about 1000 multiply-adds per clock per
 // SM that leaves room for the full HBM rate.  fp16 x fp16 products are exact and sums are fp32 (KDW_ACC_F32).
 //
+// Per-channel form (PCfg::PERCH, used by the 64-channel-slice tiles).  The same patches with K = the 16 slots of ONE
+// channel and N = 4 outputs x 2 LANES, the two lanes of an accumulator being two output planes: one mma per channel
+// adds the a = 2 taps to the lane that finishes with this step and the a = 1 taps to the other lane; the finished
+// lane is rounded, staged and cleared, and a second mma starts the next plane in it with the a = 0 taps (the other
+// lane's columns of that B are zero).  From step to step the lanes swap roles; the B fragments exist for both
+// assignments and the step is instantiated twice.  16 instead of 24 mma per unit and plane (27 of 64 products
+// useful); the A fragment wants two SLOTS of one channel in a word, which is one PRMT from the words of two voxels -
+// the same count as the register copies of the channel-pair form.  Measured in one call on one GPU: equal within
+// 1 % in bursts of five launches, 4 % faster at C = 64 and 128 in runs of 300 launches, where the kernels sit at
+// the board's power limit and the saved tensor-pipe work buys SM clock; equal or slower on the narrower tiles.
+//
 // A warp owns a UNIT: 16 blocks (2 along w x 8 along d, i.e. 4 x 16 voxels) x 8 channels.  Per input plane it
 // reads 6 voxel rows with 16-byte loads (shared memory is laid out with the TMA swizzle whose span is one voxel, which makes
 // the loads of a quarter-warp hit distinct banks) and issues 24 mma on two sets of fp32 accumulators that swap roles
@@ -30,13 +41,14 @@
 
 namespace kdw {
 
-template <int CS_, int WW_, int WD_, int UPW_, int ST_, int MODE_ = 0>
+template <int CS_, int WW_, int WD_, int UPW_, int ST_, int MODE_ = 0, int PERCH_ = 0>
 struct PCfg {
     static constexpr int CS = CS_;    // channels per CTA slice (8 .. 64)
     static constexpr int WW = WW_;    // units along w
     static constexpr int WD = WD_;    // units along d
     static constexpr int UPW = UPW_;  // units (along w) per warp; they share the weight fragments
     static constexpr int ST = ST_;    // input pipeline stages
+    static constexpr int PERCH = PERCH_;  // 1: per-channel form (16 mma per unit and plane), 0: channel-pair form (24)
     static constexpr int NG = CS / 8;  // channel groups of 8 (one 16-byte chunk of a voxel)
     static constexpr int NCW = NG * (WW / UPW) * WD;  // consumer warps
     static constexpr int NT = NCW * 32;
@@ -110,6 +122,47 @@ __device__ __forceinline__ void pg_step(const uint4 (&X)[6], const uint32_t (&Bf
     for (int cp = 0; cp < 4; ++cp) mma16816<true>(FIN[cp], Q[0][cp], Bf[cp][0][0][0], Bf[cp][0][0][1]);
 #pragma unroll
     for (int cp = 0; cp < 4; ++cp) mma16816<false>(FIN[cp], Q[1][cp], Bf[cp][0][1][0], Bf[cp][0][1][1]);
+}
+
+// The per-channel form of the same step.  Q[c] = the accumulators of channel c: elements 0 / 1 are the two lanes of
+// block row g (bw = 0), elements 2 / 3 those of block row g+8 (bw = 1); FL = the lane that finishes with this step.
+// k = 2t + j + 8h is the slot (patch row pw = j + 2h, patch column pd = t), so the A quad of a channel is (rows 0,1),
+// (rows 2,3), (rows 2,3), (rows 4,5) of the thread's voxel column; B column n = 2 out + lane; D element
+// (g, 2t + lane) is output out = t (ow = t >> 1, od = t & 1) of block (bw, g), as in the channel-pair form.
+template <int FL>
+__device__ __forceinline__ void pg_step_ch(const uint4 (&X)[6], const uint32_t (&B21)[2][8][2],
+                                           const uint32_t (&B0)[2][8][2], float (&Q)[8][4], bool store,
+                                           uint32_t out_addr0, uint32_t out_addr1) {
+    Quad A[8];
+#pragma unroll
+    for (int cp = 0; cp < 4; ++cp) {
+        const uint32_t x0 = (&X[0].x)[cp], x1 = (&X[1].x)[cp], x2 = (&X[2].x)[cp];
+        const uint32_t x3 = (&X[3].x)[cp], x4 = (&X[4].x)[cp], x5 = (&X[5].x)[cp];
+        A[2 * cp].r[0] = pair_lo(x0, x1), A[2 * cp].r[1] = pair_lo(x2, x3);
+        A[2 * cp].r[2] = pair_lo(x2, x3), A[2 * cp].r[3] = pair_lo(x4, x5);
+        A[2 * cp + 1].r[0] = pair_hi(x0, x1), A[2 * cp + 1].r[1] = pair_hi(x2, x3);
+        A[2 * cp + 1].r[2] = pair_hi(x2, x3), A[2 * cp + 1].r[3] = pair_hi(x4, x5);
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) mma16816<false>(Q[c], A[c], B21[FL][c][0], B21[FL][c][1]);
+    if (store) {
+        uint4 o0, o1;  // the finished lane: block (bw=0) in elements 0/1, block (bw=1) in elements 2/3
+        o0.x = pack_h2(Q[0][FL], Q[1][FL]);
+        o0.y = pack_h2(Q[2][FL], Q[3][FL]);
+        o0.z = pack_h2(Q[4][FL], Q[5][FL]);
+        o0.w = pack_h2(Q[6][FL], Q[7][FL]);
+        o1.x = pack_h2(Q[0][2 + FL], Q[1][2 + FL]);
+        o1.y = pack_h2(Q[2][2 + FL], Q[3][2 + FL]);
+        o1.z = pack_h2(Q[4][2 + FL], Q[5][2 + FL]);
+        o1.w = pack_h2(Q[6][2 + FL], Q[7][2 + FL]);
+        sts128(out_addr0, o0);
+        sts128(out_addr1, o1);
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        Q[c][FL] = 0.f, Q[c][2 + FL] = 0.f;  // the lane starts its next plane
+        mma16816<false>(Q[c], A[c], B0[FL][c][0], B0[FL][c][1]);
+    }
 }
 
 // Schedule position of the store warp, kept in shared memory like ProdState (the helper warps run on 40 registers).
@@ -261,15 +314,12 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
         in_off[r] = swz<Cfg::SWZ>(Geo::in_off(4 * uwg * UPW + r, Geo::DPAD - 1 + 16 * ud + 2 * g + t) + 16 * ng);
     out_off = swz<Cfg::SWZ>(Geo::out_off(4 * uwg * UPW + (t >> 1), 16 * ud + 2 * g + (t & 1)) + 16 * ng);
 
-    uint32_t Bf[4][3][2][2];   // weight fragments [channel pair][a][k16 step][k half]
-    float S0[UPW][4][4], S1[UPW][4][4];  // no initialisation: a plane's sum starts with an mma that ignores them
-
     uint32_t ci = 0, oc = 0;
     int cur_c0 = -1;
-    // One plane step; FINS / MIDS are the two accumulator sets in the roles of this step.  Returns false when the
-    // warp is done (no more planes, or a wait ran out).  The loop below calls it with the sets swapped every other
-    // step, so the role change costs neither a branch nor a register move.
-    auto plane_step = [&](float(&FINS)[UPW][4][4], float(&MIDS)[UPW][4][4]) -> bool {
+    // One plane step, common to both forms: `rebuild(c0)` loads the weight fragments of a new channel slice,
+    // `unit(u, X, store, a0, a1)` applies the plane to unit u and, when `store`, stages the finished plane at the two
+    // shared-memory addresses.  Returns false when the warp is done (no more planes, or a wait ran out).
+    auto plane_step = [&](auto&& rebuild, auto&& unit) -> bool {
         const uint32_t st = ci % ST;
         const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u, wt.limit_ns);
         if (__any_sync(0xffffffffu, !ok)) {
@@ -280,26 +330,8 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
         if (dsc == 0xffffffffu) return false;  // the load warp has no more planes
         const int c0 = (int)(dsc >> 8);
         if (c0 != cur_c0) {
-            // new channel slice: B[(slot, cc), (out, cc')] for this thread's column n = g -> out = g >> 1, cc' = g & 1
-            // and its rows k = (slot t of patch row 2ks + j, cc): the tap (b, tt) = (patch row - ow, t - od), zero
-            // outside 0..2
             cur_c0 = c0;
-            const unsigned short* wp = reinterpret_cast<const unsigned short*>(weight) + c0 + 8 * ng + (g & 1);
-            const int ow = g >> 2, od = (g >> 1) & 1;
-            const int tt = t - od;
-#pragma unroll
-            for (int cp = 0; cp < 4; ++cp)
-#pragma unroll
-                for (int a = 0; a < 3; ++a)
-#pragma unroll
-                    for (int ks = 0; ks < 2; ++ks)
-#pragma unroll
-                        for (int j = 0; j < 2; ++j) {
-                            const int b = 2 * ks + j - ow;
-                            uint32_t v = 0;
-                            if (b >= 0 && b <= 2 && tt >= 0 && tt <= 2) v = wp[(size_t)((a * 3 + b) * 3 + tt) * C + 2 * cp];
-                            Bf[cp][a][ks][j] = (g & 1) ? (v << 16) : v;
-                        }
+            rebuild(c0);
         }
         const bool store = (dsc & 1u) != 0;  // this step finishes a plane the segment owns
         const uint32_t stage = in0 + st * Cfg::IN_STRIDE;
@@ -320,8 +352,7 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty0 + 8 * st);  // the values are in registers: the stage can be refilled
             }
-            pg_step<Cfg>(X, Bf, FINS[u], MIDS[u], store, ob + out_off + u * 2 * OUT_ROW2,
-                         ob + out_off + (u * 2 + 1) * OUT_ROW2, wt.zero);
+            unit(u, X, store, ob + out_off + u * 2 * OUT_ROW2, ob + out_off + (u * 2 + 1) * OUT_ROW2);
         }
         if (store) {
             fence_proxy_async_smem();  // the tile must be visible to the TMA store
@@ -332,7 +363,76 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
         ++ci;
         return true;
     };
-    while (plane_step(S0, S1) && plane_step(S1, S0)) {
+    // This thread's B column is n = g.  Its taps: output (ow, od) against patch slot (pw, pd = t) is the tap
+    // (b, tt) = (pw - ow, t - od), zero outside 0..2.
+    const int tt = t - ((g >> 1) & 1), ow = g >> 2;
+    if constexpr (Cfg::PERCH) {
+        // column n = 2 out + lane: out = g >> 1, lane = g & 1.  Fragments for both lane assignments (index = the
+        // finishing lane): B21 = a=2 taps to the finishing lane, a=1 taps to the other; B0 = a=0 taps to the (cleared)
+        // finishing lane, zero columns for the other.  A register holds the slots (pw = 0, 1) or (pw = 2, 3).
+        uint32_t B21[2][8][2], B0[2][8][2];
+        float Q[UPW][8][4];  // no initialisation: nothing is stored before a lane was cleared and got its three planes
+        auto rebuild = [&](int c0) {
+            const unsigned short* wp = reinterpret_cast<const unsigned short*>(weight) + c0 + 8 * ng;
+            const int ln = g & 1;
+            auto taps = [&](int a, int pw, int c) -> uint32_t {  // slots (pw, pw + 1) of plane tap a, channel c
+                uint32_t v = 0;
+                if (tt >= 0 && tt <= 2) {
+                    const int b0 = pw - ow, b1 = pw + 1 - ow;
+                    if (b0 >= 0 && b0 <= 2) v = wp[(size_t)((a * 3 + b0) * 3 + tt) * C + c];
+                    if (b1 >= 0 && b1 <= 2) v |= (uint32_t)wp[(size_t)((a * 3 + b1) * 3 + tt) * C + c] << 16;
+                }
+                return v;
+            };
+#pragma unroll
+            for (int fl = 0; fl < 2; ++fl)
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        B21[fl][c][h] = taps(ln == fl ? 2 : 1, 2 * h, c);
+                        B0[fl][c][h] = ln == fl ? taps(0, 2 * h, c) : 0u;
+                    }
+        };
+        // The two instantiations alternate, so the role change of the lanes costs neither a branch nor a move.
+        while (plane_step(rebuild,
+                          [&](int u, const uint4(&X)[6], bool store, uint32_t a0, uint32_t a1) {
+                              pg_step_ch<0>(X, B21, B0, Q[u], store, a0, a1);
+                          }) &&
+               plane_step(rebuild, [&](int u, const uint4(&X)[6], bool store, uint32_t a0, uint32_t a1) {
+                   pg_step_ch<1>(X, B21, B0, Q[u], store, a0, a1);
+               })) {
+        }
+    } else {
+        // column n = g: out = g >> 1, cc' = g & 1; rows k = (slot t of patch row 2ks + j, cc)
+        uint32_t Bf[4][3][2][2];             // weight fragments [channel pair][a][k16 step][k half]
+        float S0[UPW][4][4], S1[UPW][4][4];  // no initialisation: a plane's sum starts with an mma that ignores them
+        auto rebuild = [&](int c0) {
+            const unsigned short* wp = reinterpret_cast<const unsigned short*>(weight) + c0 + 8 * ng + (g & 1);
+#pragma unroll
+            for (int cp = 0; cp < 4; ++cp)
+#pragma unroll
+                for (int a = 0; a < 3; ++a)
+#pragma unroll
+                    for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const int b = 2 * ks + j - ow;
+                            uint32_t v = 0;
+                            if (b >= 0 && b <= 2 && tt >= 0 && tt <= 2) v = wp[(size_t)((a * 3 + b) * 3 + tt) * C + 2 * cp];
+                            Bf[cp][a][ks][j] = (g & 1) ? (v << 16) : v;
+                        }
+        };
+        // The two accumulator sets swap roles (finishing / middle plane) every step: the step is called with the
+        // sets exchanged, which costs neither a branch nor a register move.
+        while (plane_step(rebuild,
+                          [&](int u, const uint4(&X)[6], bool store, uint32_t a0, uint32_t a1) {
+                              pg_step<Cfg>(X, Bf, S0[u], S1[u], store, a0, a1, wt.zero);
+                          }) &&
+               plane_step(rebuild, [&](int u, const uint4(&X)[6], bool store, uint32_t a0, uint32_t a1) {
+                   pg_step<Cfg>(X, Bf, S1[u], S0[u], store, a0, a1, wt.zero);
+               })) {
+        }
     }
 }
 
@@ -383,18 +483,21 @@ struct PgVariant {
 // PCfg<CS, WW, WD, UPW, ST, MODE>: tile 4*WW x 16*WD voxels (w, d), CS channels; 8 consumer warps, two units each;
 // MODE: how the tiles are staged (TileGeo): 0 any C that is a multiple of CS, 1 C == 8, 2 C == 16 and D even
 #define KDW_PG(CS, WW, WD, UPW, ST, MODE) {CS, 16 * WD, 4 * WW, MODE, &launch_fprop_pg<PCfg<CS, WW, WD, UPW, ST, MODE>>}
+#define KDW_PGC(CS, WW, WD, UPW, ST, MODE) {CS, 16 * WD, 4 * WW, MODE, &launch_fprop_pg<PCfg<CS, WW, WD, UPW, ST, MODE, 1>>}
 static const PgVariant g_pg_variants[] = {
-    KDW_PG(64, 2, 1, 2, 4, 0),  // 0: tile 8 x 16
+    KDW_PGC(64, 2, 1, 2, 4, 0),  // 0: tile 8 x 16, per-channel form
     KDW_PG(32, 4, 1, 2, 4, 0),  // 1: tile 16 x 16
     KDW_PG(16, 4, 2, 2, 4, 0),  // 2: tile 16 x 32
     KDW_PG(8, 4, 4, 2, 4, 0),   // 3: tile 16 x 64
     KDW_PG(32, 2, 2, 2, 4, 0),  // 4: tile 8 x 32
-    KDW_PG(64, 2, 1, 2, 5, 0),  // 5: as 0, five stages
+    KDW_PG(64, 2, 1, 2, 5, 0),  // 5: five stages, channel-pair form
     KDW_PG(8, 4, 4, 2, 4, 1),   // 6: C == 8, tile 16 x 64, long box rows
     KDW_PG(16, 4, 2, 2, 4, 2),  // 7: C == 16, D even, tile 16 x 32, 64-byte box rows
     KDW_PG(16, 8, 1, 2, 4, 2),  // 8: C == 16, D even, tile 32 x 16
+    KDW_PG(64, 2, 1, 2, 4, 0),  // 9: as 0, channel-pair form
 };
 #undef KDW_PG
+#undef KDW_PGC
 static const int g_n_pg_variants = (int)(sizeof(g_pg_variants) / sizeof(g_pg_variants[0]));
 
 int fprop_mma_variants() { return g_n_pg_variants; }

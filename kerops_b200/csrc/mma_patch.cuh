@@ -163,6 +163,19 @@ __device__ __forceinline__ uint32_t reg_copy(uint32_t x, uint32_t zero) {
     return y;
 }
 
+// Two halves of two words in one register (PRMT with a constant selector): pair_lo(a, b) = (a.lo, b.lo) with a in
+// the low half of the result, pair_hi(a, b) = (a.hi, b.hi) - the same channel of two voxels, out of channel-pair words.
+__device__ __forceinline__ uint32_t pair_lo(uint32_t a, uint32_t b) {
+    uint32_t y;
+    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(y) : "r"(a), "r"(b));
+    return y;
+}
+__device__ __forceinline__ uint32_t pair_hi(uint32_t a, uint32_t b) {
+    uint32_t y;
+    asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(y) : "r"(a), "r"(b));
+    return y;
+}
+
 // Transpose of an 8 x 8 matrix of 16-bit elements held one row per four lanes (lane (g, t): row g, columns 2t, 2t+1),
 // the layout in which raw channels-last words arrive: rows = blocks, columns = (voxel t, channel of the pair).
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
