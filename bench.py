@@ -54,12 +54,12 @@ FALLBACK_HBM_GBS = 6650.0
 # `ncu --set full` capture on (1, C, 100, 350, 128) volumes, scaled by 350/100 planes (traffic grows in proportion to
 # the planes a launch processes).  Bytes per (1,C,350,350,128) launch; None where no capture has been taken.
 NCU_TRAFFIC = {
-    ('fprop', 8): int((0.079654 + 0.026692) * 3.5e9),
-    ('wgrad', 8): int((0.151513 + 0.005427) * 3.5e9),
-    ('fprop', 32): int((0.290732 + 0.245913) * 3.5e9),
-    ('wgrad', 32): int((0.577497 + 0.005466) * 3.5e9),
-    ('fprop', 128): int((1.316454 + 1.107569) * 3.5e9),
-    ('wgrad', 128): int((2.548305 + 0.006967) * 3.5e9),
+    ('fprop', 8): int((0.079657 + 0.026334) * 3.5e9),
+    ('wgrad', 8): int((0.151532 + 0.004746) * 3.5e9),
+    ('fprop', 32): int((0.290739 + 0.246126) * 3.5e9),
+    ('wgrad', 32): int((0.577468 + 0.004517) * 3.5e9),
+    ('fprop', 128): int((1.314928 + 1.107812) * 3.5e9),
+    ('wgrad', 128): int((2.545495 + 0.007897) * 3.5e9),
 }
 
 
