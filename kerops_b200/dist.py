@@ -270,9 +270,13 @@ def sample_sharded_step(x, weight, grad, group=None, ops=None, reducer=None, y=N
     if y is None:
         y = torch.empty((N, H, W, D, C), dtype=x.dtype, device=x.device).permute(0, 4, 1, 2, 3)
     _mark(events, 0)
-    ops.fprop_range(x, weight, y, 0, H, 0)
+    if N > 0:
+        ops.fprop_range(x, weight, y, 0, H, 0)
     _mark(events, 1)
-    dw = ops.wgrad_range(x, grad, 0, H, 0)
+    if N > 0:
+        dw = ops.wgrad_range(x, grad, 0, H, 0)
+    else:  # a rank without samples (batch smaller than the group) still takes part in the sum
+        dw = torch.zeros(3, 3, 3, C, dtype=torch.float32, device=x.device)
     _mark(events, 2)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         dw = _reduce(dw, group, reducer)

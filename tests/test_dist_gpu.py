@@ -18,12 +18,27 @@ def _free_port():
 
 
 def _worker(rank, world, port, shape, out_dir):
+    try:
+        _worker_body(rank, world, port, shape, out_dir)
+    except BaseException:
+        # leave at once, without the process-group teardown: the other ranks may be inside a collective this rank
+        # will never join, and the parent ends them as soon as it sees this exit code
+        import traceback
+
+        traceback.print_exc()
+        os._exit(1)
+
+
+def _worker_body(rank, world, port, shape, out_dir):
+    import datetime
+
     os.environ['MASTER_ADDR'] = '127.0.0.1'
     os.environ['MASTER_PORT'] = str(port)
     os.environ['NCCL_NVLS_ENABLE'] = '0'
     torch.cuda.set_device(rank)
     dev = torch.device('cuda', rank)
-    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=dev,
+                            timeout=datetime.timedelta(seconds=60))
     try:
         from kerops_b200 import _lib
         from kerops_b200 import dist as kd
@@ -72,8 +87,10 @@ def _worker(rank, world, port, shape, out_dir):
             'status': _lib.device_status(),
         }
         torch.save(ok, os.path.join(out_dir, f'rank{rank}.pt'))
+        dist.barrier()
     finally:
-        dist.destroy_process_group()
+        pass
+    dist.destroy_process_group()
 
 
 @pytest.mark.parametrize('shape', [(2, 32, 37, 21, 40), (2, 128, 11, 9, 33)])
