@@ -77,9 +77,35 @@ def build(force=False, verbose=False):
     return LIB
 
 
+PROBES = {'issue_rate': [], 'tma_rows': ['-lcuda'], 'tcgen05_small_n': []}
+
+
+def build_probes(force=False):
+    """Compiles the stand-alone microbenchmarks of csrc/probes (not part of the library; run by hand on a GPU)."""
+    nvcc = find_nvcc()
+    pdir = os.path.join(CSRC, 'probes')
+
+    def one(item):
+        name, libs = item
+        src, exe = os.path.join(pdir, name + '.cu'), os.path.join(pdir, name)
+        if not force and _newer(exe, [src]):
+            return exe
+        r = subprocess.run([nvcc, '-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-o', exe, src] + libs,
+                           capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f'nvcc failed on probes/{name}.cu:\n{r.stdout}\n{r.stderr}')
+        return exe
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=len(PROBES)) as ex:
+        return list(ex.map(one, PROBES.items()))
+
+
 if __name__ == '__main__':
     ap = argparse.ArgumentParser()
     ap.add_argument('--force', action='store_true')
     ap.add_argument('--verbose', action='store_true')
+    ap.add_argument('--probes', action='store_true', help='also build the microbenchmarks of csrc/probes')
     a = ap.parse_args()
     print(build(force=a.force, verbose=a.verbose))
+    if a.probes:
+        print('\n'.join(build_probes(force=a.force)))

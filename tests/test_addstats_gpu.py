@@ -62,6 +62,33 @@ def test_fused_equals_composition(shape):
     assert _lib.device_status() == 0
 
 
+def test_benchmark_volume():
+    """(1, 32, 350, 350, 128), the benchmark volume at one channel count: output bits against the composition,
+    statistics against fp64 sums taken slab by slab."""
+    from kerops_b200 import _lib
+    from kerops_b200.ops.conv import DWConvAddStats
+
+    from ._util import dwconv_cuda_core
+
+    N, C, H, W, D = 1, 32, 350, 350, 128
+    x, r, w = _inputs(N, C, H, W, D, seed=9)
+    out, mean, sqmean = DWConvAddStats(x, w, r)
+    ref = dwconv_cuda_core(x, w)
+    ref += r
+    assert torch.equal(out, ref)
+    del ref
+    s1 = torch.zeros(C, dtype=torch.float64, device='cuda')
+    s2 = torch.zeros(C, dtype=torch.float64, device='cuda')
+    for h0 in range(0, H, 50):
+        o = out[:, :, h0:h0 + 50].double()
+        s1 += o.sum(dim=(0, 2, 3, 4))
+        s2 += (o * o).sum(dim=(0, 2, 3, 4))
+    n = N * H * W * D
+    torch.testing.assert_close(mean.double(), s1 / n, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(sqmean.double(), s2 / n, rtol=1e-5, atol=1e-6)
+    assert _lib.device_status() == 0
+
+
 def test_every_tile_and_inplace():
     from kerops_b200 import _lib
     from kerops_b200.ops.conv import DWConvAddStats, _launch

@@ -54,6 +54,33 @@ def test_fused_equals_composition(shape):
     assert _lib.device_status() == 0
 
 
+def test_benchmark_volume():
+    """(1, 32, 350, 350, 128), the benchmark volume at one channel count, against the composition (the activation
+    is formed slab by slab to bound the fp64 temporaries)."""
+    from kerops_b200 import _lib
+    from kerops_b200.ops.conv import DWConvBNReLU
+
+    from ._util import dwconv_cuda_core
+
+    N, C, H, W, D = 1, 32, 350, 350, 128
+    x, scale, shift, w = _inputs(N, C, H, W, D, seed=9)
+    y = DWConvBNReLU(x, scale, shift, w)
+    act = torch.empty_like(x)
+    s = scale.view(1, -1, 1, 1, 1).double()
+    b = shift.view(1, -1, 1, 1, 1).double()
+    for h0 in range(0, H, 50):
+        act[:, :, h0:h0 + 50] = torch.clamp_min((x[:, :, h0:h0 + 50].double() * s + b).float(), 0).half()
+    ref = dwconv_cuda_core(act, w)
+    del act
+    mismatches = 0
+    for h0 in range(0, H, 50):
+        ys, rs = y[:, :, h0:h0 + 50], ref[:, :, h0:h0 + 50]
+        mismatches += int((ys != rs).sum())
+        torch.testing.assert_close(ys.float(), rs.float(), rtol=1e-3, atol=2e-3)
+    assert mismatches < 1e-3 * y.numel()  # equal but for double rounding inside the activation
+    assert _lib.device_status() == 0
+
+
 def test_every_tile():
     from kerops_b200 import _lib
     from kerops_b200.ops.conv import _launch
