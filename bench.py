@@ -23,7 +23,8 @@ reference's own Triton kernels from baseline/_ref timed on the same tensors) wit
 speed-ups), and - at every N - the two strong-scaling workloads as sub-records:
 `dshard` = one (1,128,1400,350,128) volume sharded along H over the ranks with halo exchange (BASELINE configs[3]) and
 `dpstep` = a batch of 8 x (32,350,350,128) samples split by sample (configs[4]), each with its per-rank breakdown,
-so that strong-scaling efficiency can be computed from the lines of a 1/2/4/8-GPU series alone.
+so that strong-scaling efficiency can be computed from the lines of a 1/2/4/8-GPU series alone; at one GPU also
+`fused` = the record of --workload fused (below).
 
 --workload dshard | dpstep | fused run one of the other workloads alone (`fused` = DWConvAddStats and DWConvBNReLU
 against the unfused and the reference two-operator chains, one GPU).
@@ -621,6 +622,13 @@ def run_ours(args):
                 rec = {'error': f'{type(e).__name__}: {e}'[:300]}
             if line is not None:
                 line[name] = rec
+        if ctx.world == 1 and not args.no_fused:  # the two fused neighbours of the path, one GPU only
+            gc.collect()
+            torch.cuda.empty_cache()
+            try:
+                line['fused'] = fused_record(args, args.sub_steps)
+            except Exception as e:
+                line['fused'] = {'error': f'{type(e).__name__}: {e}'[:300]}
     if line is not None:
         print(json.dumps(line), flush=True)
     ctx.close()
@@ -875,6 +883,11 @@ def run_sharded(args, fn):
 
 
 def run_fused(args):
+    """--workload fused alone: the record as the JSON line."""
+    print(json.dumps(fused_record(args, args.steps)), flush=True)
+
+
+def fused_record(args, steps):
     """The fused neighbours, per C of the sweep, one GPU.  Headline: DWConvAddStats(x, weight, residual), algorithmic
     bytes per call read x + read residual + write out = 6*V*C; comparators timed in the same run: our DWConv followed
     by a torch fp16 add and channel means, and - when baseline/_ref is present - the reference's
@@ -925,7 +938,7 @@ def run_fused(args):
     for C in args.channels:
         x, r, w = make_gpu_inputs(C, dev, seed=C)
         nbytes = 6 * VOX * C
-        ms = timeit(lambda: DWConvAddStats(x, w, r), args.steps)
+        ms = timeit(lambda: DWConvAddStats(x, w, r), steps)
         row = {'ms': round(ms, 4), 'gbs': round(nbytes / ms / 1e6, 1), 'frac': round(nbytes / ms / 1e6 / peak, 4),
                'unfused_ms': round(timeit(lambda: unfused(x, w, r), 3), 4)}
         if ref_ops is not None:
@@ -935,8 +948,8 @@ def run_fused(args):
                 row['reference_chain_ms'] = f'{type(e).__name__}'
         # the prologue neighbour: y = DWConv(relu(x * scale + shift)); algorithmic bytes 4*V*C like the plain conv
         scale, shift = torch.rand(C, device=dev) + 0.5, torch.randn(C, device=dev) * 0.5
-        ms_b = timeit(lambda: DWConvBNReLU(x, scale, shift, w), args.steps)
-        ms_h = timeit(lambda: DWConvBNReLU(x, scale, shift, w, PROLOGUE='float16'), args.steps)
+        ms_b = timeit(lambda: DWConvBNReLU(x, scale, shift, w), steps)
+        ms_h = timeit(lambda: DWConvBNReLU(x, scale, shift, w, PROLOGUE='float16'), steps)
         row['bnrelu'] = {'ms': round(ms_b, 4), 'gbs': round(4 * VOX * C / ms_b / 1e6, 1),
                          'frac': round(4 * VOX * C / ms_b / 1e6 / peak, 4), 'ms_packed_half_prologue': round(ms_h, 4)}
         if ref_ops is not None:
@@ -951,18 +964,18 @@ def run_fused(args):
         del x, r, w
     clocks = sampler.stop()
     value = tot_bytes / tot_ms / 1e6
-    print(json.dumps({
+    return {
         'metric': 'DWConvAddStats algorithmic HBM GB/s at (1,C,%d,350,128) fp16 channels_last_3d' % SHAPE[0],
-        'value': round(value, 1), 'unit': 'GB/s', 'n_gpus': 1, 'steps': args.steps, 'warmup': 3,
+        'value': round(value, 1), 'unit': 'GB/s', 'n_gpus': 1, 'steps': steps, 'warmup': 3,
         'ms_per_step': round(tot_ms, 4), 'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None,
         'dtype': 'f16 products, f32 accumulation', 'data': 'synthetic',
         'config': {'workload': 'fused forward + residual add + channel statistics, C in '
                                + ','.join(map(str, args.channels)), 'l2': 'inputs larger than L2'},
         'roofline': {'bound': 'hbm', 'kernel': 'fprop_addstats_kernel, all C', 'achieved': round(value, 1), 'peak': peak,
                      'peak_kind': peak_kind, 'unit': 'GB/s', 'frac': round(value / peak, 4), 'traffic': None},
-        'clocks': clocks, 'gpu_launches': 4 * len(args.channels) * args.steps, 'detail': detail,
+        'clocks': clocks, 'gpu_launches': 4 * len(args.channels) * steps, 'detail': detail,
         'device_status': _lib.device_status(),
-    }), flush=True)
+    }
 
 
 def main():
@@ -974,6 +987,7 @@ def main():
     ap.add_argument('--channels', default=','.join(map(str, ALL_CHANNELS)))
     ap.add_argument('--planes', type=int, default=SHAPE[0],
                     help='h extent of the volume (default 350); smaller values are for profiler captures only')
+    ap.add_argument('--no-fused', action='store_true', help='sweep workload at one GPU: skip the `fused` sub-record')
     ap.add_argument('--workload', default='sweep', choices=['sweep', 'dshard', 'dpstep', 'fused'],
                     help="'sweep' (default): the headline per-C sweep, one sample per GPU; 'dshard': one large volume "
                          "sharded along H over the GPUs; 'dpstep': a batch of (32,350,350,128) samples split by sample; 'fused': DWConvAddStats, one GPU")

@@ -32,7 +32,8 @@
 // A warp owns a UNIT: 16 blocks (2 along w x 8 along d, i.e. 4 x 16 voxels) x 8 channels.  Per input plane it
 // reads 6 voxel rows with 16-byte loads (shared memory is laid out with the TMA swizzle whose span is one voxel, which makes
 // the loads of a quarter-warp hit distinct banks) and issues 24 mma on two sets of fp32 accumulators that swap roles
-// from step to step (finishing plane / middle plane), as in fprop_step_f32.  Finished planes are staged in shared
+// from step to step (finishing plane / middle plane), as in fprop_step_f32 - or, in the per-channel form, 16 mma on
+// one set whose lanes swap roles.  Finished planes are staged in shared
 // memory and leave through ONE TMA store per CTA and plane, issued by a dedicated warp; all hand-overs are
 // mbarriers with bounded waits.
 #include "../../include/kdw.h"
@@ -168,8 +169,6 @@ __device__ __forceinline__ void pg_step_ch(const uint4 (&X)[6], const uint32_t (
 // Schedule position of the store warp, kept in shared memory like ProdState (the helper warps run on 40 registers).
 struct StoreState {
     StepIter it;
-    uint32_t issued, retired;
-    int done;
 };
 
 // Issues the copy of the next input plane (or the end marker) into the next stage, waiting for the stage to be
@@ -277,8 +276,6 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
     }
     if (warp == 1 && lane == 0) {
         ss->it.init(s, (int)blockIdx.x, (int)gridDim.x);
-        ss->issued = ss->retired = 0;
-        ss->done = 0;
     }
     __syncwarp();
     if (warp < Cfg::NHELP) {
