@@ -72,7 +72,9 @@ int kdw_test_wait_limits(int64_t limit_ns, int stop_after);
  *   weight    fp16 [3][3][3][C]
  *   acc_type  KDW_ACC_F32: exact fp16 x fp16 products accumulated in fp32 (tensor-core mma or mixed-precision FMA,
  *             depending on the variant), rounded once to fp16 - at least as accurate as the reference's 'float32' mode (fp16 products, fp16 sum of three,
- *             fp32 sum of nine; kerops/kernels/dw_conv.py:49-52);  KDW_ACC_F16: all 27 taps in fp16 FMA chains
+ *             fp32 sum of nine; kerops/kernels/dw_conv.py:49-52);  KDW_ACC_F16: sums of no more than fp16 accuracy
+ *             are asked for - the built-in choice and the tensor-core variants then still accumulate in fp32 (more
+ *             accurate and faster), only the CUDA-core variants named by `tune` run packed-half FMA chains
  *   tune      0 = built-in choice for this C, W and D; >0 = explicit kernel variant (see kdw_fprop_variants());
  *             takes the place of the num_warps / D_block keywords (dwconv.py:10-17)
  * C must be a power of two.  C >= 8 uses the TMA kernel (x, y 16-byte aligned, strides multiples of 8);

@@ -260,8 +260,10 @@ static int n_fprop_variants() { return g_n_table_variants + fprop_mma_variants()
 // Built-in choice.  Per channel count and accumulate type a short list of candidates with their time relative to
 // the best one, measured at (1, C, 350, 350, 128) on B200.  A tile that does not divide W or D computes padding:
 // the candidate's time is scaled by the padded / real area and the cheapest one wins, so e.g. D = 40 does not run
-// on a 64-deep tile.  KDW_ACC_F32 runs on the tensor-core kernels (ids after the table, dwconv_fprop_mma.cu: exact
-// fp16 products, fp32 sums); KDW_ACC_F16 exists only as packed-half FMA chains on the CUDA cores.
+// on a 64-deep tile.  The tensor-core kernels (ids after the table, dwconv_fprop_mma.cu: exact fp16 products, fp32
+// sums) serve both accumulate types: KDW_ACC_F16 asks for no MORE than fp16 sums, and the fp32-accumulating mma
+// kernel is both more accurate and faster than the packed-half FMA chains of the CUDA-core tiles, which run in
+// that arithmetic only when a table variant is named explicitly together with KDW_ACC_F16.
 struct FpropCand {
     int id;
     float rel;
@@ -274,12 +276,6 @@ static const FpropCand kFpropCand16[] = {{kT + 8, 1.00f}, {kT + 3, 1.21f}, {kT +
 static const FpropCand kFpropCand32[] = {{kT + 5, 1.00f}, {kT + 3, 1.03f}, {kT + 2, 1.06f}, {11, 1.75f}};
 static const FpropCand kFpropCand64[] = {{kT + 1, 1.00f}, {kT + 6, 1.02f}, {kT + 5, 1.09f}, {11, 1.80f}};
 static const FpropCand kFpropCand128[] = {{kT + 1, 1.00f}, {kT + 6, 1.07f}, {kT + 2, 1.12f}, {8, 1.80f}};
-static const FpropCand kFpropCandH8[] = {{1, 1.00f}, {2, 1.12f}};
-static const FpropCand kFpropCandH16[] = {{10, 1.00f}, {4, 1.03f}, {1, 1.75f}};
-static const FpropCand kFpropCandH32[] = {{11, 1.00f}, {6, 1.02f}, {4, 1.02f}};
-static const FpropCand kFpropCandH64[] = {{11, 1.00f}, {8, 1.02f}, {6, 1.03f}};
-static const FpropCand kFpropCandH128[] = {{8, 1.00f}, {11, 1.01f}, {6, 1.03f}};
-
 static void fprop_variant_tile(int id, int* wt, int* dt) {
     if (id > g_n_table_variants) {
         fprop_mma_variant_tile(id - g_n_table_variants - 1, wt, dt);
@@ -293,19 +289,12 @@ static void fprop_variant_tile(int id, int* wt, int* dt) {
 static int auto_fprop_variant(int64_t C, int64_t W, int64_t D, int acc_type) {
     const FpropCand* cand;
     int n;
-    if (acc_type == KDW_ACC_F16) {
-        if (C == 8) KDW_CANDS(kFpropCandH8);
-        else if (C == 16) KDW_CANDS(kFpropCandH16);
-        else if (C == 32) KDW_CANDS(kFpropCandH32);
-        else if (C == 64) KDW_CANDS(kFpropCandH64);
-        else KDW_CANDS(kFpropCandH128);
-    } else {
-        if (C == 8) KDW_CANDS(kFpropCand8);
-        else if (C == 16) KDW_CANDS(kFpropCand16);
-        else if (C == 32) KDW_CANDS(kFpropCand32);
-        else if (C == 64) KDW_CANDS(kFpropCand64);
-        else KDW_CANDS(kFpropCand128);
-    }
+    (void)acc_type;  // both accumulate types share the choice: see the comment above
+    if (C == 8) KDW_CANDS(kFpropCand8);
+    else if (C == 16) KDW_CANDS(kFpropCand16);
+    else if (C == 32) KDW_CANDS(kFpropCand32);
+    else if (C == 64) KDW_CANDS(kFpropCand64);
+    else KDW_CANDS(kFpropCand128);
     int best = 0;
     double best_cost = 0.0;
     for (int i = 0; i < n; ++i) {
@@ -372,10 +361,6 @@ static int fprop_dispatch(const void* x, const void* weight, void* y, int64_t N,
     }
     const int id = tune ? tune : auto_fprop_variant(C, W, D, acc_type);
     if (id > g_n_table_variants) {
-        if (acc_type != KDW_ACC_F32) {
-            set_error("fprop: variant %d (tensor cores) implements KDW_ACC_F32 only", id);
-            return KDW_ERR_TUNE;
-        }
         return launch_fprop_mma_variant(id - g_n_table_variants - 1, x, weight, y, N, C, Hx, W, D, xsN, xsH, xsW, Hy, ysN,
                                         ysH, ysW, (int)h_begin, (int)h_end, (int)y_h0, st);
     }

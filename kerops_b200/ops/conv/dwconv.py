@@ -33,7 +33,8 @@ def DWConv(x, weight, *, ACCTYPE: ConfigurableArg, num_warps: ConfigurableArg, D
 
     x       (N, C, H, W, D) fp16 CUDA tensor, contiguous in channels_last_3d
     weight  [3, 3, 3, C] fp16 contiguous: weight[a, b, t, c] = torch_weight[c, 0, a, b, t]
-    ACCTYPE 'float32' (exact products accumulated in fp32, one rounding to fp16) or 'float16' (fp16 FMA chains)
+    ACCTYPE 'float32' (exact products accumulated in fp32, one rounding to fp16) or 'float16' (the reference's faster,
+            less accurate mode; here it runs the same fp32-accumulating kernel, so it is neither)
     num_warps, D_block  accepted for call compatibility; D_block must be a power of two
     Returns a new tensor with the shape, strides and dtype of x.
     """
