@@ -196,6 +196,12 @@ static const BnReluVariant g_bnrelu_variants[] = {
 #undef KDW_BNRELU_TILE
 static const int g_n_bnrelu_variants = (int)(sizeof(g_bnrelu_variants) / sizeof(g_bnrelu_variants[0]));
 
+// dwconv_fprop_mma.cu
+bool fprop_bnrelu_mma_fits(int64_t C, int64_t D);
+int launch_fprop_bnrelu_mma(const void* x, const float* scale, const float* shift, const void* w, void* y, int64_t N,
+                            int64_t C, int64_t H, int64_t W, int64_t D, int64_t xsN, int64_t xsH, int64_t xsW,
+                            int64_t ysN, int64_t ysH, int64_t ysW, cudaStream_t stream);
+
 static int auto_bnrelu_variant(int64_t C, int64_t D) {
     if (C == 8) return 1;
     if (C == 16) return (D % 64 == 0 || D > 192) ? 2 : 3;
@@ -234,6 +240,11 @@ int kdw_fprop_bnrelu_f16(const void* x, const float* scale, const float* shift, 
     if (tune < 0 || tune > g_n_bnrelu_variants) {
         set_error("fprop_bnrelu: tune=%d names no kernel variant (1..%d)", tune, g_n_bnrelu_variants);
         return KDW_ERR_TUNE;
+    }
+    if (tune == 0 && prologue_type == KDW_ACC_F16 && fprop_bnrelu_mma_fits(C, D)) {
+        // packed-half prologue: the tensor-core forward kernel with the activation applied to its operand words
+        return launch_fprop_bnrelu_mma(x, scale, shift, weight, y, N, C, H, W, D, x_strideN, x_strideH, x_strideW,
+                                       y_strideN, y_strideH, y_strideW, (cudaStream_t)stream);
     }
     const int id = tune ? tune : auto_bnrelu_variant(C, D);
     const BnReluVariant& v = g_bnrelu_variants[id - 1];

@@ -42,7 +42,7 @@
 
 namespace kdw {
 
-template <int CS_, int WW_, int WD_, int UPW_, int ST_, int MODE_ = 0, int PERCH_ = 0>
+template <int CS_, int WW_, int WD_, int UPW_, int ST_, int MODE_ = 0, int PERCH_ = 0, int PRO_ = 0>
 struct PCfg {
     static constexpr int CS = CS_;    // channels per CTA slice (8 .. 64)
     static constexpr int WW = WW_;    // units along w
@@ -50,6 +50,11 @@ struct PCfg {
     static constexpr int UPW = UPW_;  // units (along w) per warp; they share the weight fragments
     static constexpr int ST = ST_;    // input pipeline stages
     static constexpr int PERCH = PERCH_;  // 1: per-channel form (16 mma per unit and plane), 0: channel-pair form (24)
+    // 1: fused prologue y = conv(relu(x * scale[c] + shift[c])) with scale / shift rounded to fp16 (one packed-half
+    // fused multiply-add and a maximum per channel-pair word as it arrives from shared memory).  The input tensor map
+    // then fills out-of-bounds elements with NaN, NaN survives the multiply-add, and max(NaN, 0) = 0 restores the zero
+    // padding of the ACTIVATED tensor without masks.
+    static constexpr int PRO = PRO_;
     static constexpr int NG = CS / 8;  // channel groups of 8 (one 16-byte chunk of a voxel)
     static constexpr int NCW = NG * (WW / UPW) * WD;  // consumer warps
     static constexpr int NT = NCW * 32;
@@ -234,7 +239,8 @@ __device__ __forceinline__ void pg_store(StoreState* ss, const Sched& s, const C
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
     fprop_pg_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
-                    const __half* __restrict__ weight, const Sched s, const int C, const int y_h0, int* status,
+                    const __half* __restrict__ weight, const float* __restrict__ bn_scale,
+                    const float* __restrict__ bn_shift, const Sched s, const int C, const int y_h0, int* status,
                     const WaitTest wt) {
     constexpr int ST = Cfg::ST, NCW = Cfg::NCW, UPW = Cfg::UPW;
     extern __shared__ unsigned char smem_raw[];
@@ -313,6 +319,7 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
 
     uint32_t ci = 0, oc = 0;
     int cur_c0 = -1;
+    __half2 sc16[4], sh16[4];  // prologue only: scale / shift of the thread's four channel pairs
     // One plane step, common to both forms: `rebuild(c0)` loads the weight fragments of a new channel slice,
     // `unit(u, X, store, a0, a1)` applies the plane to unit u and, when `store`, stages the finished plane at the two
     // shared-memory addresses.  Returns false when the warp is done (no more planes, or a wait ran out).
@@ -329,6 +336,14 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
         if (c0 != cur_c0) {
             cur_c0 = c0;
             rebuild(c0);
+            if (Cfg::PRO) {
+#pragma unroll
+                for (int cp = 0; cp < 4; ++cp) {
+                    const int c = c0 + 8 * ng + 2 * cp;
+                    sc16[cp] = __floats2half2_rn(bn_scale[c], bn_scale[c + 1]);
+                    sh16[cp] = __floats2half2_rn(bn_shift[c], bn_shift[c + 1]);
+                }
+            }
         }
         const bool store = (dsc & 1u) != 0;  // this step finishes a plane the segment owns
         const uint32_t stage = in0 + st * Cfg::IN_STRIDE;
@@ -348,6 +363,14 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
             if (u == UPW - 1) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty0 + 8 * st);  // the values are in registers: the stage can be refilled
+            }
+            if (Cfg::PRO) {
+#pragma unroll
+                for (int r = 0; r < 6; ++r) {
+                    __half2* xw = reinterpret_cast<__half2*>(&X[r]);
+#pragma unroll
+                    for (int cp = 0; cp < 4; ++cp) xw[cp] = h2_relu_nan0(h2_fma(xw[cp], sc16[cp], sh16[cp]));
+                }
             }
             unit(u, X, store, ob + out_off + u * 2 * OUT_ROW2, ob + out_off + (u * 2 + 1) * OUT_ROW2);
         }
@@ -440,6 +463,7 @@ struct PgArgs {
     const void* x;
     const void* w;
     void* y;
+    const float *scale, *shift;  // prologue variants only
     int64_t N, C, Hx, W, D, xsN, xsH, xsW, Hy, ysN, ysH, ysW;
     int h_begin, h_end, y_h0;
     cudaStream_t stream;
@@ -448,7 +472,7 @@ struct PgArgs {
 template <class Cfg>
 static int launch_fprop_pg(const PgArgs& a) {
     CUtensorMap tmx, tmy;
-    int rc = encode_tile_map<typename Cfg::Geo>(&tmx, a.x, a.N, a.C, a.Hx, a.W, a.D, a.xsN, a.xsH, a.xsW, true);
+    int rc = encode_tile_map<typename Cfg::Geo>(&tmx, a.x, a.N, a.C, a.Hx, a.W, a.D, a.xsN, a.xsH, a.xsW, true, Cfg::PRO != 0);
     if (rc) return rc;
     rc = encode_tile_map<typename Cfg::Geo>(&tmy, a.y, a.N, a.C, a.Hy, a.W, a.D, a.ysN, a.ysH, a.ysW, false);
     if (rc) return rc;
@@ -466,7 +490,7 @@ static int launch_fprop_pg(const PgArgs& a) {
     if (rc) return rc;
     Sched s;
     const int grid = make_sched(&s, a.N, a.C, a.W, a.D, a.h_begin, a.h_end, Cfg::WT, Cfg::DT, Cfg::CS, sms * occ);
-    kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, a.stream>>>(tmx, tmy, (const __half*)a.w, s, (int)a.C, a.y_h0, status,
+    kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, a.stream>>>(tmx, tmy, (const __half*)a.w, a.scale, a.shift, s, (int)a.C, a.y_h0, status,
                                                        wait_test());
     KDW_CUDA(cudaGetLastError());
     return 0;
@@ -528,8 +552,23 @@ int launch_fprop_mma_variant(int which, const void* x, const void* w, void* y, i
                   v.cs, v.mode == 2 ? " and an even D" : "", (long long)C, (long long)D);
         return KDW_ERR_TUNE;
     }
-    PgArgs a{x, w, y, N, C, Hx, W, D, xsN, xsH, xsW, Hy, ysN, ysH, ysW, h_begin, h_end, y_h0, stream};
+    PgArgs a{x, w, y, nullptr, nullptr, N, C, Hx, W, D, xsN, xsH, xsW, Hy, ysN, ysH, ysW, h_begin, h_end, y_h0, stream};
     return v.f(a);
+}
+
+// Fused prologue (kdw_fprop_bnrelu_f16 with the packed-half prologue): the built-in tile of each channel count with
+// PCfg::PRO.  Returns KDW_ERR_TUNE without touching the error text when no tensor-core tile takes the shape (the
+// caller then falls back to its CUDA-core kernels).
+bool fprop_bnrelu_mma_fits(int64_t C, int64_t D) { return C >= 32 || C == 8 || (C == 16 && (D & 1) == 0); }
+
+int launch_fprop_bnrelu_mma(const void* x, const float* scale, const float* shift, const void* w, void* y, int64_t N,
+                            int64_t C, int64_t H, int64_t W, int64_t D, int64_t xsN, int64_t xsH, int64_t xsW,
+                            int64_t ysN, int64_t ysH, int64_t ysW, cudaStream_t stream) {
+    PgArgs a{x, w, y, scale, shift, N, C, H, W, D, xsN, xsH, xsW, H, ysN, ysH, ysW, 0, (int)H, 0, stream};
+    if (C == 8) return launch_fprop_pg<PCfg<8, 4, 4, 2, 4, 1, 0, 1>>(a);
+    if (C == 16) return launch_fprop_pg<PCfg<16, 4, 2, 2, 4, 2, 0, 1>>(a);
+    if (C == 32) return launch_fprop_pg<PCfg<32, 2, 2, 2, 4, 0, 0, 1>>(a);
+    return launch_fprop_pg<PCfg<64, 2, 1, 2, 4, 0, 1, 1>>(a);
 }
 
 }  // namespace kdw

@@ -47,12 +47,12 @@ int encode_volume_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, 
 
 // As encode_volume_map with the D and C axes merged (see kdw_host.cu).
 int encode_merged_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
-                      int64_t strideN, int64_t strideH, int64_t strideW, int boxDC, int boxW);
+                      int64_t strideN, int64_t strideH, int64_t strideW, int boxDC, int boxW, bool nan_fill = false);
 
 // The volume with PAIRS of voxels along d as the innermost axis: dims (2*C, D/2, W, H, N), box (2*C, boxP, boxW, 1,
 // 1), 64-byte swizzle.  Needs C == 16 (64-byte rows) and an even D.
 int encode_paired_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
-                      int64_t strideN, int64_t strideH, int64_t strideW, int boxP, int boxW);
+                      int64_t strideN, int64_t strideH, int64_t strideW, int boxP, int boxW, bool nan_fill = false);
 
 int device_sm_count(int* sms);
 

@@ -142,7 +142,7 @@ int encode_volume_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, 
 // C (a 16-byte row per voxel makes poor use of the TMA unit).  Zero fill works as before because W stays an
 // axis of its own; only usable when a CTA takes all channels of a voxel.
 int encode_merged_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
-                      int64_t strideN, int64_t strideH, int64_t strideW, int boxDC, int boxW) {
+                      int64_t strideN, int64_t strideH, int64_t strideW, int boxDC, int boxW, bool nan_fill) {
     EncodeTiledFn fn;
     int rc = get_encode_fn(&fn);
     if (rc) return rc;
@@ -164,7 +164,7 @@ int encode_merged_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, 
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    nan_fill ? CU_TENSOR_MAP_FLOAT_OOB_FILL_NAN_REQUEST_ZERO_FMA : CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled (merged D*C axis) failed with CUresult %d", (int)r);
         return (int)r;
@@ -173,7 +173,7 @@ int encode_merged_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, 
 }
 
 int encode_paired_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
-                      int64_t strideN, int64_t strideH, int64_t strideW, int boxP, int boxW) {
+                      int64_t strideN, int64_t strideH, int64_t strideW, int boxP, int boxW, bool nan_fill) {
     EncodeTiledFn fn;
     int rc = get_encode_fn(&fn);
     if (rc) return rc;
@@ -194,7 +194,7 @@ int encode_paired_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, 
     const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    nan_fill ? CU_TENSOR_MAP_FLOAT_OOB_FILL_NAN_REQUEST_ZERO_FMA : CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled (paired d axis) failed with CUresult %d", (int)r);
         return (int)r;

@@ -194,14 +194,14 @@ struct ProdState {
 // Host: the tensor maps of a TileGeo over volume `base` (H planes); `in` selects the halo'd input box.
 template <class Geo>
 int encode_tile_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, int64_t H, int64_t W, int64_t D,
-                    int64_t sN, int64_t sH, int64_t sW, bool in) {
+                    int64_t sN, int64_t sH, int64_t sW, bool in, bool nan_fill = false) {
     if (Geo::MODE == 1) {
         if (C != Geo::CS) {
             set_error("this kernel variant needs C == %d", Geo::CS);
             return KDW_ERR_TUNE;
         }
         return encode_merged_map(map, base, N, C, H, W, D, sN, sH, sW, (in ? Geo::KD : Geo::KDO) * Geo::CS,
-                                 in ? Geo::WT + 2 : Geo::WT);
+                                 in ? Geo::WT + 2 : Geo::WT, nan_fill);
     }
     if (Geo::MODE == 2) {
         if (C != Geo::CS || (D & 1)) {
@@ -209,9 +209,9 @@ int encode_tile_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, in
             return KDW_ERR_TUNE;
         }
         return encode_paired_map(map, base, N, C, H, W, D, sN, sH, sW, (in ? Geo::DIN : Geo::DT) / 2,
-                                 in ? Geo::WT + 2 : Geo::WT);
+                                 in ? Geo::WT + 2 : Geo::WT, nan_fill);
     }
     return encode_volume_map(map, base, N, C, H, W, D, sN, sH, sW, Geo::CS, in ? Geo::DIN : Geo::DT,
-                             in ? Geo::WT + 2 : Geo::WT, false, Geo::SWZ);
+                             in ? Geo::WT + 2 : Geo::WT, nan_fill, Geo::SWZ);
 }
 }  // namespace kdw
