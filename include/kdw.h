@@ -195,7 +195,8 @@ int kdw_allreduce_push_f32(const float* local, float* out_f32, void* out_f16, vo
  * convolution's output.  KDW_ACC_F32 arithmetic.  C a power of two >= 8; x, residual, y are (N, C, H, W, D) fp16
  * volumes with the layout rules of kdw_fprop_f16; mean, sqmean fp32 [C]; workspace of
  * kdw_fprop_addstats_workspace_bytes() bytes (no initialisation needed).  The sums are reproducible (no atomics).
- *   tune  0 = built-in choice; 1..kdw_fprop_addstats_variants() = explicit tile
+ *   tune  0 = built-in choice (the tensor-core forward kernel with the add and the sums in its epilogue, where one
+ *         of its tiles takes the shape); 1..kdw_fprop_addstats_variants() = explicit CUDA-core tile
  */
 int64_t kdw_fprop_addstats_workspace_bytes(int64_t N, int64_t C, int64_t H, int64_t W, int64_t D);
 int kdw_fprop_addstats_variants(void);

@@ -288,6 +288,13 @@ static int auto_addstats_variant(int64_t C, int64_t D) {
     return 5;
 }
 
+// dwconv_fprop_mma.cu
+bool fprop_addstats_mma_fits(int64_t C, int64_t D);
+int launch_fprop_addstats_mma(const void* x, const void* w, const void* res, void* y, float* stats_ws, int64_t stats_rows,
+                              int64_t N, int64_t C, int64_t H, int64_t W, int64_t D, int64_t xsN, int64_t xsH, int64_t xsW,
+                              int64_t rsN, int64_t rsH, int64_t rsW, int64_t ysN, int64_t ysH, int64_t ysW,
+                              cudaStream_t stream, int* rows_used);
+
 static int64_t addstats_rows(int* rc_out) {
     int sms = 0;
     *rc_out = device_sm_count(&sms);
@@ -342,18 +349,26 @@ int kdw_fprop_addstats_f16(const void* x, const void* weight, const void* residu
                   (long long)(rows_cap * 2 * C * 4));
         return KDW_ERR_WORKSPACE;
     }
-    const int id = tune ? tune : auto_addstats_variant(C, D);
-    const AddStatsVariant& v = g_addstats_variants[id - 1];
-    if (C % v.cs != 0) {
-        set_error("fprop_addstats: variant %d works on %d-channel slices, C=%lld is not a multiple", id, v.cs,
-                  (long long)C);
-        return KDW_ERR_TUNE;
-    }
-    AddStatsArgs a{x, weight, residual, y, (float*)workspace, rows_cap, N, C, H, W, D, x_strideN, x_strideH, x_strideW,
-                   r_strideN, r_strideH, r_strideW, y_strideN, y_strideH, y_strideW, (cudaStream_t)stream};
     int rows = 0;
-    rc = v.f(a, &rows);
-    if (rc) return rc;
+    if (tune == 0 && fprop_addstats_mma_fits(C, D)) {
+        // built-in choice: the tensor-core forward kernel with the residual add and the sums in its epilogue
+        rc = launch_fprop_addstats_mma(x, weight, residual, y, (float*)workspace, rows_cap, N, C, H, W, D, x_strideN,
+                                       x_strideH, x_strideW, r_strideN, r_strideH, r_strideW, y_strideN, y_strideH,
+                                       y_strideW, (cudaStream_t)stream, &rows);
+        if (rc) return rc;
+    } else {
+        const int id = tune ? tune : auto_addstats_variant(C, D);
+        const AddStatsVariant& v = g_addstats_variants[id - 1];
+        if (C % v.cs != 0) {
+            set_error("fprop_addstats: variant %d works on %d-channel slices, C=%lld is not a multiple", id, v.cs,
+                      (long long)C);
+            return KDW_ERR_TUNE;
+        }
+        AddStatsArgs a{x, weight, residual, y, (float*)workspace, rows_cap, N, C, H, W, D, x_strideN, x_strideH, x_strideW,
+                       r_strideN, r_strideH, r_strideW, y_strideN, y_strideH, y_strideW, (cudaStream_t)stream};
+        rc = v.f(a, &rows);
+        if (rc) return rc;
+    }
     const float inv = (float)(1.0 / ((double)N * (double)H * (double)W * (double)D));
     stats_reduce_kernel<<<(2 * (int)C + 3) / 4, 128, 0, (cudaStream_t)stream>>>((const float*)workspace, rows, (int)C, inv,
                                                                                 mean, sqmean);

@@ -42,7 +42,7 @@
 
 namespace kdw {
 
-template <int CS_, int WW_, int WD_, int UPW_, int ST_, int MODE_ = 0, int PERCH_ = 0, int PRO_ = 0>
+template <int CS_, int WW_, int WD_, int UPW_, int ST_, int MODE_ = 0, int PERCH_ = 0, int PRO_ = 0, int EPI_ = 0>
 struct PCfg {
     static constexpr int CS = CS_;    // channels per CTA slice (8 .. 64)
     static constexpr int WW = WW_;    // units along w
@@ -55,6 +55,11 @@ struct PCfg {
     // then fills out-of-bounds elements with NaN, NaN survives the multiply-add, and max(NaN, 0) = 0 restores the zero
     // padding of the ACTIVATED tensor without masks.
     static constexpr int PRO = PRO_;
+    // 1: fused epilogue out = fp16(conv) + residual with per-channel sums of out and out^2 (kdw_fprop_addstats_f16).
+    // A stage then also carries the residual tile of the plane the step finishes; the consumer threads add it to the
+    // rounded outputs before staging them and accumulate the stored values in fp32; the sums leave the CTA through one
+    // workspace row per (CTA, consumer warp), added by a second pass in a fixed order (no atomics).
+    static constexpr int EPI = EPI_;
     static constexpr int NG = CS / 8;  // channel groups of 8 (one 16-byte chunk of a voxel)
     static constexpr int NCW = NG * (WW / UPW) * WD;  // consumer warps
     static constexpr int NT = NCW * 32;
@@ -72,7 +77,8 @@ struct PCfg {
     static constexpr int SWZ = Geo::SWZ;
     static constexpr int IN_BYTES = Geo::IN_BYTES, IN_STRIDE = Geo::IN_STRIDE;
     static constexpr int OUT_BYTES = Geo::OUT_BYTES, OUT_STRIDE = Geo::OUT_STRIDE;
-    static constexpr int SMEM = ST * IN_STRIDE + 2 * OUT_STRIDE + 16 * ST + 32 + 4 * ST + 256 + 1024;
+    static constexpr int SMEM =
+        ST * IN_STRIDE + 2 * OUT_STRIDE + (EPI_ ? ST * OUT_STRIDE + 8 * ST + 16 : 0) + 16 * ST + 32 + 4 * ST + 256 + 1024;
     static_assert(CS == 8 || CS == 16 || CS == 32 || CS == 64, "a voxel must be one swizzle span (or 16 bytes)");
     static_assert(WW % UPW == 0, "units per warp");
     static_assert(NCW == 8, "register hand-over is laid out for two consumer warpgroups");
@@ -87,10 +93,9 @@ struct PCfg {
 // covers the patch rows pw = 2ks (k 0-7: slot t) and 2ks+1 (k 8-15), patch column pd = t, i.e. the A quad of
 // (ks, channel pair) is the word of input rows 2ks, 2ks+2, 2ks+1, 2ks+3.
 // Consecutive mma never touch the same accumulator, so they issue back to back.
-template <class Cfg>
+template <class Cfg, class Emit>
 __device__ __forceinline__ void pg_step(const uint4 (&X)[6], const uint32_t (&Bf)[4][3][2][2], float (&FIN)[4][4],
-                                        float (&MID)[4][4], bool store, uint32_t out_addr0, uint32_t out_addr1,
-                                        uint32_t zero) {
+                                        float (&MID)[4][4], bool store, Emit&& emit, uint32_t zero) {
     Quad Q[2][4];
 #pragma unroll
     for (int ks = 0; ks < 2; ++ks) {
@@ -121,8 +126,7 @@ __device__ __forceinline__ void pg_step(const uint4 (&X)[6], const uint32_t (&Bf
         o1.y = pack_h2(FIN[1][2], FIN[1][3]);
         o1.z = pack_h2(FIN[2][2], FIN[2][3]);
         o1.w = pack_h2(FIN[3][2], FIN[3][3]);
-        sts128(out_addr0, o0);
-        sts128(out_addr1, o1);
+        emit(o0, o1);
     }
 #pragma unroll
     for (int cp = 0; cp < 4; ++cp) mma16816<true>(FIN[cp], Q[0][cp], Bf[cp][0][0][0], Bf[cp][0][0][1]);
@@ -135,10 +139,9 @@ __device__ __forceinline__ void pg_step(const uint4 (&X)[6], const uint32_t (&Bf
 // k = 2t + j + 8h is the slot (patch row pw = j + 2h, patch column pd = t), so the A quad of a channel is (rows 0,1),
 // (rows 2,3), (rows 2,3), (rows 4,5) of the thread's voxel column; B column n = 2 out + lane; D element
 // (g, 2t + lane) is output out = t (ow = t >> 1, od = t & 1) of block (bw, g), as in the channel-pair form.
-template <int FL>
+template <int FL, class Emit>
 __device__ __forceinline__ void pg_step_ch(const uint4 (&X)[6], const uint32_t (&B21)[2][8][2],
-                                           const uint32_t (&B0)[2][8][2], float (&Q)[8][4], bool store,
-                                           uint32_t out_addr0, uint32_t out_addr1) {
+                                           const uint32_t (&B0)[2][8][2], float (&Q)[8][4], bool store, Emit&& emit) {
     Quad A[8];
 #pragma unroll
     for (int cp = 0; cp < 4; ++cp) {
@@ -161,8 +164,7 @@ __device__ __forceinline__ void pg_step_ch(const uint4 (&X)[6], const uint32_t (
         o1.y = pack_h2(Q[2][2 + FL], Q[3][2 + FL]);
         o1.z = pack_h2(Q[4][2 + FL], Q[5][2 + FL]);
         o1.w = pack_h2(Q[6][2 + FL], Q[7][2 + FL]);
-        sts128(out_addr0, o0);
-        sts128(out_addr1, o1);
+        emit(o0, o1);
     }
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
@@ -179,8 +181,9 @@ struct StoreState {
 // Issues the copy of the next input plane (or the end marker) into the next stage, waiting for the stage to be
 // free.  The position in the schedule lives in shared memory (ProdState).
 template <class Cfg>
-__device__ __forceinline__ void pg_produce(ProdState* ps, const Sched& s, const CUtensorMap& tmx, uint32_t in0,
-                                           uint32_t full0, uint32_t empty0, uint32_t desc0, int* status, const WaitTest& wt) {
+__device__ __forceinline__ void pg_produce(ProdState* ps, const Sched& s, const CUtensorMap& tmx, const CUtensorMap& tmr,
+                                           uint32_t in0, uint32_t res0, uint32_t full0, uint32_t empty0, uint32_t desc0,
+                                           uint32_t lim0, int W, int D, int* status, const WaitTest& wt) {
     constexpr int ST = Cfg::ST;
     const uint32_t pi = ps->pi;
     if (wt.stop_after >= 0 && (int)pi >= wt.stop_after) {  // test hook: the consumers' wait runs out
@@ -202,10 +205,18 @@ __device__ __forceinline__ void pg_produce(ProdState* ps, const Sched& s, const 
         ps->done = 1;
         return;
     }
-    st_shared_u32(desc0 + 4 * st, ((uint32_t)it.g.c0 << 8) | (it.q - 1 >= it.g.hb ? 1u : 0u));
-    mbar_expect_tx(full0 + 8 * st, Cfg::IN_BYTES);
+    const bool fin = it.q - 1 >= it.g.hb;  // the step finishes a plane the segment owns
+    st_shared_u32(desc0 + 4 * st, ((uint32_t)it.g.c0 << 8) | (fin ? 1u : 0u));
+    if (Cfg::EPI) {  // how much of the tile lies inside the volume (the statistics skip the rest)
+        st_shared_u32(lim0 + 8 * st, (uint32_t)(W - it.g.w0));
+        st_shared_u32(lim0 + 8 * st + 4, (uint32_t)(D - it.g.d0));
+    }
+    mbar_expect_tx(full0 + 8 * st, Cfg::IN_BYTES + (Cfg::EPI && fin ? Cfg::OUT_BYTES : 0));
     tile_load_in<typename Cfg::Geo>(status, in0 + st * Cfg::IN_STRIDE, &tmx, full0 + 8 * st, it.g.c0, it.g.d0, it.g.w0, it.q,
                                     it.g.n);
+    if (Cfg::EPI && fin)
+        tile_load_out<typename Cfg::Geo>(status, res0 + st * Cfg::OUT_STRIDE, &tmr, full0 + 8 * st, it.g.c0, it.g.d0,
+                                         it.g.w0, it.q - 1, it.g.n);
     it.next(s);
     ps->it = it;
     ps->pi = pi + 1;
@@ -239,6 +250,7 @@ __device__ __forceinline__ void pg_store(StoreState* ss, const Sched& s, const C
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
     fprop_pg_kernel(const __grid_constant__ CUtensorMap tmx, const __grid_constant__ CUtensorMap tmy,
+                    const __grid_constant__ CUtensorMap tmr, float* __restrict__ stats_ws, const int W, const int D,
                     const __half* __restrict__ weight, const float* __restrict__ bn_scale,
                     const float* __restrict__ bn_shift, const Sched s, const int C, const int y_h0, int* status,
                     const WaitTest wt) {
@@ -247,7 +259,8 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
     const uint32_t in0 = base;
     const uint32_t out0 = base + ST * Cfg::IN_STRIDE;
-    const uint32_t full0 = out0 + 2 * Cfg::OUT_STRIDE;  // full[ST], empty[ST], staged[2], ofree[2]
+    const uint32_t res0 = out0 + 2 * Cfg::OUT_STRIDE;   // epilogue only: the residual tile of each stage
+    const uint32_t full0 = res0 + (Cfg::EPI ? ST * Cfg::OUT_STRIDE : 0);  // full[ST], empty[ST], staged[2], ofree[2]
     const uint32_t empty0 = full0 + 8 * ST;
     const uint32_t staged0 = empty0 + 8 * ST;
     const uint32_t ofree0 = staged0 + 16;
@@ -261,6 +274,7 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
     if (tid == 0) {
         prefetch_tmap(&tmx);
         prefetch_tmap(&tmy);
+        if (Cfg::EPI) prefetch_tmap(&tmr);
         for (int k = 0; k < ST; ++k) {
             mbar_init(full0 + 8 * k, 1);
             mbar_init(empty0 + 8 * k, NCW);
@@ -273,7 +287,8 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
     }
     __syncthreads();  // the only CTA-wide barrier
 
-    ProdState* ps = reinterpret_cast<ProdState*>(smem_raw + ((desc0 + 4 * ST + 15) / 16 * 16 - smem_u32(smem_raw)));
+    const uint32_t lim0 = (desc0 + 4 * ST + 15) / 16 * 16;  // epilogue only: (w, d) extent of the tile inside the volume
+    ProdState* ps = reinterpret_cast<ProdState*>(smem_raw + ((lim0 + (Cfg::EPI ? 8 * ST : 0) + 15) / 16 * 16 - smem_u32(smem_raw)));
     StoreState* ss = reinterpret_cast<StoreState*>(reinterpret_cast<unsigned char*>(ps) + 128);
     if (warp == 0 && lane == 0) {
         ps->it.init(s, (int)blockIdx.x, (int)gridDim.x);
@@ -289,7 +304,7 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
         if (lane != 0) return;
         if (warp == 0) {
             // ---------------- load warp: one lane streams the input planes of the CTA's range ----------------
-            while (!ps->done) pg_produce<Cfg>(ps, s, tmx, in0, full0, empty0, desc0, status, wt);
+            while (!ps->done) pg_produce<Cfg>(ps, s, tmx, tmr, in0, res0, full0, empty0, desc0, lim0, W, D, status, wt);
         } else if (warp == 1) {
             // ---------------- store warp: one TMA store per finished plane of the tile ----------------
             pg_store<Cfg>(ss, s, tmy, out0, staged0, ofree0, y_h0, status, wt);
@@ -320,9 +335,36 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
     uint32_t ci = 0, oc = 0;
     int cur_c0 = -1;
     __half2 sc16[4], sh16[4];  // prologue only: scale / shift of the thread's four channel pairs
+    // epilogue only: sums of the stored values and of their squares, per channel pair of the thread; the warp's own
+    // workspace row [2][C] (sums, sums of squares), zeroed here and added to when the channel slice changes / at the end
+    float2 ssum[4], ssq[4];
+    float* const srow = Cfg::EPI ? stats_ws + (size_t)((int)blockIdx.x * NCW + cw) * 2 * C : nullptr;
+    const int w_t = 4 * uwg * UPW + (t >> 1), d_t = 16 * ud + 2 * g + (t & 1);  // the thread's first output voxel
+    if (Cfg::EPI) {
+        for (int k = lane; k < 2 * C; k += 32) srow[k] = 0.f;
+#pragma unroll
+        for (int cp = 0; cp < 4; ++cp) ssum[cp] = ssq[cp] = make_float2(0.f, 0.f);
+        __syncwarp();
+    }
+    auto flush_stats = [&](int c0) {  // all lanes of a warp hold the same eight channels
+#pragma unroll
+        for (int cp = 0; cp < 4; ++cp) {
+            float v[4] = {ssum[cp].x, ssum[cp].y, ssq[cp].x, ssq[cp].y};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) v[i] += __shfl_xor_sync(0xffffffffu, v[i], off);
+            }
+            if (lane == 0) {
+                const int c = c0 + 8 * ng + 2 * cp;
+                srow[c] += v[0], srow[c + 1] += v[1], srow[C + c] += v[2], srow[C + c + 1] += v[3];
+            }
+            ssum[cp] = ssq[cp] = make_float2(0.f, 0.f);
+        }
+    };
     // One plane step, common to both forms: `rebuild(c0)` loads the weight fragments of a new channel slice,
-    // `unit(u, X, store, a0, a1)` applies the plane to unit u and, when `store`, stages the finished plane at the two
-    // shared-memory addresses.  Returns false when the warp is done (no more planes, or a wait ran out).
+    // `unit(u, X, store, emit)` applies the plane to unit u and, when `store`, hands the two finished, rounded voxels of
+    // the thread to `emit`, which (adds the residual and counts them, then) stages them.  Returns false when the warp is done (no more planes, or a wait ran out).
     auto plane_step = [&](auto&& rebuild, auto&& unit) -> bool {
         const uint32_t st = ci % ST;
         const bool ok = mbar_wait_bounded(full0 + 8 * st, (ci / ST) & 1u, wt.limit_ns);
@@ -334,6 +376,7 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
         if (dsc == 0xffffffffu) return false;  // the load warp has no more planes
         const int c0 = (int)(dsc >> 8);
         if (c0 != cur_c0) {
+            if (Cfg::EPI && cur_c0 >= 0) flush_stats(cur_c0);
             cur_c0 = c0;
             rebuild(c0);
             if (Cfg::PRO) {
@@ -347,6 +390,8 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
         }
         const bool store = (dsc & 1u) != 0;  // this step finishes a plane the segment owns
         const uint32_t stage = in0 + st * Cfg::IN_STRIDE;
+        int w_lim = 0, d_lim = 0;
+        if (Cfg::EPI) w_lim = (int)ld_shared_u32(lim0 + 8 * st), d_lim = (int)ld_shared_u32(lim0 + 8 * st + 4);
         const uint32_t ob = out0 + (oc & 1u) * Cfg::OUT_STRIDE;
         if (store && oc >= 2) {  // the store that last read this staging tile must have finished
             const bool free_ok = mbar_wait_bounded(ofree0 + 8 * (oc & 1u), ((oc >> 1) - 1u) & 1u, wt.limit_ns);
@@ -372,7 +417,30 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
                     for (int cp = 0; cp < 4; ++cp) xw[cp] = h2_relu_nan0(h2_fma(xw[cp], sc16[cp], sh16[cp]));
                 }
             }
-            unit(u, X, store, ob + out_off + u * 2 * OUT_ROW2, ob + out_off + (u * 2 + 1) * OUT_ROW2);
+            unit(u, X, store, [&](uint4 o0, uint4 o1) {
+                const uint32_t a0 = out_off + u * 2 * OUT_ROW2, a1 = out_off + (u * 2 + 1) * OUT_ROW2;
+                if (Cfg::EPI) {
+                    const uint32_t rs = res0 + st * Cfg::OUT_STRIDE;
+                    const uint4 r0 = lds128(rs + a0), r1 = lds128(rs + a1);
+                    __half2* h0 = reinterpret_cast<__half2*>(&o0);
+                    __half2* h1 = reinterpret_cast<__half2*>(&o1);
+                    const __half2* q0 = reinterpret_cast<const __half2*>(&r0);
+                    const __half2* q1 = reinterpret_cast<const __half2*>(&r1);
+                    // voxels of the tile that lie outside the volume are not stored (the TMA store clips them) and
+                    // must not be counted
+                    const bool in0 = d_t < d_lim && w_t + 4 * u < w_lim, in1 = d_t < d_lim && w_t + 4 * u + 2 < w_lim;
+                    const __half2 one = __float2half2_rn(1.f);
+#pragma unroll
+                    for (int cp = 0; cp < 4; ++cp) {
+                        h0[cp] = __hadd2(h0[cp], q0[cp]);
+                        h1[cp] = __hadd2(h1[cp], q1[cp]);
+                        if (in0) ssum[cp] = fma_h2_f2(h0[cp], one, ssum[cp]), ssq[cp] = fma_h2_f2(h0[cp], h0[cp], ssq[cp]);
+                        if (in1) ssum[cp] = fma_h2_f2(h1[cp], one, ssum[cp]), ssq[cp] = fma_h2_f2(h1[cp], h1[cp], ssq[cp]);
+                    }
+                }
+                sts128(ob + a0, o0);
+                sts128(ob + a1, o1);
+            });
         }
         if (store) {
             fence_proxy_async_smem();  // the tile must be visible to the TMA store
@@ -416,11 +484,11 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
         };
         // The two instantiations alternate, so the role change of the lanes costs neither a branch nor a move.
         while (plane_step(rebuild,
-                          [&](int u, const uint4(&X)[6], bool store, uint32_t a0, uint32_t a1) {
-                              pg_step_ch<0>(X, B21, B0, Q[u], store, a0, a1);
+                          [&](int u, const uint4(&X)[6], bool store, auto&& emit) {
+                              pg_step_ch<0>(X, B21, B0, Q[u], store, emit);
                           }) &&
-               plane_step(rebuild, [&](int u, const uint4(&X)[6], bool store, uint32_t a0, uint32_t a1) {
-                   pg_step_ch<1>(X, B21, B0, Q[u], store, a0, a1);
+               plane_step(rebuild, [&](int u, const uint4(&X)[6], bool store, auto&& emit) {
+                   pg_step_ch<1>(X, B21, B0, Q[u], store, emit);
                })) {
         }
     } else {
@@ -446,14 +514,15 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
         // The two accumulator sets swap roles (finishing / middle plane) every step: the step is called with the
         // sets exchanged, which costs neither a branch nor a register move.
         while (plane_step(rebuild,
-                          [&](int u, const uint4(&X)[6], bool store, uint32_t a0, uint32_t a1) {
-                              pg_step<Cfg>(X, Bf, S0[u], S1[u], store, a0, a1, wt.zero);
+                          [&](int u, const uint4(&X)[6], bool store, auto&& emit) {
+                              pg_step<Cfg>(X, Bf, S0[u], S1[u], store, emit, wt.zero);
                           }) &&
-               plane_step(rebuild, [&](int u, const uint4(&X)[6], bool store, uint32_t a0, uint32_t a1) {
-                   pg_step<Cfg>(X, Bf, S1[u], S0[u], store, a0, a1, wt.zero);
+               plane_step(rebuild, [&](int u, const uint4(&X)[6], bool store, auto&& emit) {
+                   pg_step<Cfg>(X, Bf, S1[u], S0[u], store, emit, wt.zero);
                })) {
         }
     }
+    if (Cfg::EPI && cur_c0 >= 0) flush_stats(cur_c0);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -464,6 +533,11 @@ struct PgArgs {
     const void* w;
     void* y;
     const float *scale, *shift;  // prologue variants only
+    const void* res;             // epilogue variants only: residual (strides rsN, rsH, rsW), statistics workspace
+    int64_t rsN, rsH, rsW;
+    float* stats_ws;
+    int64_t stats_rows;
+    int* rows_used;
     int64_t N, C, Hx, W, D, xsN, xsH, xsW, Hy, ysN, ysH, ysW;
     int h_begin, h_end, y_h0;
     cudaStream_t stream;
@@ -476,6 +550,11 @@ static int launch_fprop_pg(const PgArgs& a) {
     if (rc) return rc;
     rc = encode_tile_map<typename Cfg::Geo>(&tmy, a.y, a.N, a.C, a.Hy, a.W, a.D, a.ysN, a.ysH, a.ysW, false);
     if (rc) return rc;
+    CUtensorMap tmr = tmy;  // unused without the epilogue
+    if (Cfg::EPI) {
+        rc = encode_tile_map<typename Cfg::Geo>(&tmr, a.res, a.N, a.C, a.Hx, a.W, a.D, a.rsN, a.rsH, a.rsW, false);
+        if (rc) return rc;
+    }
     if (((uintptr_t)a.w & 1) != 0) {
         set_error("weight pointer must be 2-byte aligned");
         return KDW_ERR_ALIGN;
@@ -489,8 +568,18 @@ static int launch_fprop_pg(const PgArgs& a) {
     rc = status_ptr(&status);
     if (rc) return rc;
     Sched s;
-    const int grid = make_sched(&s, a.N, a.C, a.W, a.D, a.h_begin, a.h_end, Cfg::WT, Cfg::DT, Cfg::CS, sms * occ);
-    kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, a.stream>>>(tmx, tmy, (const __half*)a.w, a.scale, a.shift, s, (int)a.C, a.y_h0, status,
+    long long target = (long long)sms * occ;
+    if (Cfg::EPI) {  // one statistics row per (CTA, consumer warp)
+        if (target * Cfg::NCW > a.stats_rows) target = a.stats_rows / Cfg::NCW;
+        if (target < 1) {
+            set_error("fprop_addstats: workspace has %lld rows, the tensor-core kernel needs %d per CTA", (long long)a.stats_rows,
+                      Cfg::NCW);
+            return KDW_ERR_WORKSPACE;
+        }
+    }
+    const int grid = make_sched(&s, a.N, a.C, a.W, a.D, a.h_begin, a.h_end, Cfg::WT, Cfg::DT, Cfg::CS, (int)target);
+    if (Cfg::EPI && a.rows_used) *a.rows_used = grid * Cfg::NCW;
+    kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, a.stream>>>(tmx, tmy, tmr, a.stats_ws, (int)a.W, (int)a.D, (const __half*)a.w, a.scale, a.shift, s, (int)a.C, a.y_h0, status,
                                                        wait_test());
     KDW_CUDA(cudaGetLastError());
     return 0;
@@ -552,8 +641,25 @@ int launch_fprop_mma_variant(int which, const void* x, const void* w, void* y, i
                   v.cs, v.mode == 2 ? " and an even D" : "", (long long)C, (long long)D);
         return KDW_ERR_TUNE;
     }
-    PgArgs a{x, w, y, nullptr, nullptr, N, C, Hx, W, D, xsN, xsH, xsW, Hy, ysN, ysH, ysW, h_begin, h_end, y_h0, stream};
+    PgArgs a{x, w, y, nullptr, nullptr, nullptr, 0, 0, 0, nullptr, 0, nullptr, N, C, Hx, W, D, xsN, xsH, xsW, Hy, ysN, ysH, ysW,
+             h_begin, h_end, y_h0, stream};
     return v.f(a);
+}
+
+// Fused epilogue (kdw_fprop_addstats_f16): the built-in tile of each channel count with PCfg::EPI.  *rows_used = the
+// statistics rows the launch writes (all of them: each warp zeroes its own).
+bool fprop_addstats_mma_fits(int64_t C, int64_t D) { return C >= 32 || C == 8 || (C == 16 && (D & 1) == 0); }
+
+int launch_fprop_addstats_mma(const void* x, const void* w, const void* res, void* y, float* stats_ws, int64_t stats_rows,
+                              int64_t N, int64_t C, int64_t H, int64_t W, int64_t D, int64_t xsN, int64_t xsH, int64_t xsW,
+                              int64_t rsN, int64_t rsH, int64_t rsW, int64_t ysN, int64_t ysH, int64_t ysW,
+                              cudaStream_t stream, int* rows_used) {
+    PgArgs a{x, w, y, nullptr, nullptr, res, rsN, rsH, rsW, stats_ws, stats_rows, rows_used, N, C, H, W, D, xsN, xsH, xsW, H,
+             ysN, ysH, ysW, 0, (int)H, 0, stream};
+    if (C == 8) return launch_fprop_pg<PCfg<8, 4, 4, 2, 4, 1, 0, 0, 1>>(a);
+    if (C == 16) return launch_fprop_pg<PCfg<16, 4, 2, 2, 4, 2, 0, 0, 1>>(a);
+    if (C == 32) return launch_fprop_pg<PCfg<32, 2, 2, 2, 4, 0, 0, 0, 1>>(a);
+    return launch_fprop_pg<PCfg<64, 2, 1, 2, 4, 0, 0, 0, 1>>(a);
 }
 
 // Fused prologue (kdw_fprop_bnrelu_f16 with the packed-half prologue): the built-in tile of each channel count with
@@ -564,7 +670,8 @@ bool fprop_bnrelu_mma_fits(int64_t C, int64_t D) { return C >= 32 || C == 8 || (
 int launch_fprop_bnrelu_mma(const void* x, const float* scale, const float* shift, const void* w, void* y, int64_t N,
                             int64_t C, int64_t H, int64_t W, int64_t D, int64_t xsN, int64_t xsH, int64_t xsW,
                             int64_t ysN, int64_t ysH, int64_t ysW, cudaStream_t stream) {
-    PgArgs a{x, w, y, scale, shift, N, C, H, W, D, xsN, xsH, xsW, H, ysN, ysH, ysW, 0, (int)H, 0, stream};
+    PgArgs a{x, w, y, scale, shift, nullptr, 0, 0, 0, nullptr, 0, nullptr, N, C, H, W, D, xsN, xsH, xsW, H, ysN, ysH, ysW,
+             0, (int)H, 0, stream};
     if (C == 8) return launch_fprop_pg<PCfg<8, 4, 4, 2, 4, 1, 0, 1>>(a);
     if (C == 16) return launch_fprop_pg<PCfg<16, 4, 2, 2, 4, 2, 0, 1>>(a);
     if (C == 32) return launch_fprop_pg<PCfg<32, 2, 2, 2, 4, 0, 0, 1>>(a);

@@ -22,16 +22,26 @@ def _inputs(N, C, H, W, D, seed):
     return x, r, w
 
 
-def _composition(x, r, w):
+def _composition(x, r, w, cuda_core=False):
     """DWConv followed by a torch fp16 add and fp32 channel means.  The fused kernel runs on the CUDA cores; the
     convolution it is compared with bit for bit is a CUDA-core variant of kdw_fprop_f16 too (same order of the fp32
     sums).  The built-in choice of DWConv - a tensor-core kernel, whose fp32 sums are added in another order - must
     agree to the last fp16 bit almost everywhere."""
     from kerops_b200.ops.conv import DWConv
 
+    from kerops_b200.ops.conv import _launch
+
     from ._util import dwconv_cuda_core
 
-    y = dwconv_cuda_core(x, w)
+    # The fused kernel is, where a tensor-core forward tile takes the shape, that tile (a kdw_fprop_f16 variant id)
+    # with the add and the sums in its epilogue; elsewhere a CUDA-core kernel.  Same arithmetic, same bits.
+    C, D = x.shape[1], x.shape[4]
+    twin = 0 if cuda_core else {8: 19, 16: 20 if D % 2 == 0 else 0, 32: 17}.get(C, 22)
+    if twin:
+        y = torch.empty_like(x)
+        _launch.fprop(x, w, y, tune=twin)
+    else:
+        y = dwconv_cuda_core(x, w)
     y_default = DWConv(x, w, num_warps=8, D_block=8)  # keywords given: any power-of-two C is then accepted
     assert float((y != y_default).float().mean()) < 1e-3
     torch.testing.assert_close(y.float(), y_default.float(), rtol=1e-3, atol=2e-3)
@@ -73,7 +83,10 @@ def test_benchmark_volume():
     N, C, H, W, D = 1, 32, 350, 350, 128
     x, r, w = _inputs(N, C, H, W, D, seed=9)
     out, mean, sqmean = DWConvAddStats(x, w, r)
-    ref = dwconv_cuda_core(x, w)
+    from kerops_b200.ops.conv import _launch
+
+    ref = torch.empty_like(x)
+    _launch.fprop(x, w, ref, tune=17)  # the forward tile whose epilogue the fused kernel extends
     ref += r
     assert torch.equal(out, ref)
     del ref
@@ -97,7 +110,7 @@ def test_every_tile_and_inplace():
     n_var = lib.kdw_fprop_addstats_variants()
     assert n_var >= 5
     x, r, w = _inputs(2, 64, 7, 19, 45, seed=5)
-    out_ref, mean_ref, sq_ref = _composition(x, r, w)
+    out_ref, mean_ref, sq_ref = _composition(x, r, w, cuda_core=True)
     for tune in range(1, n_var + 1):
         y = torch.full_like(x, float('nan'))
         mean, sqmean = _launch.fprop_addstats(x, w, r, y, tune=tune)
@@ -105,8 +118,8 @@ def test_every_tile_and_inplace():
         torch.testing.assert_close(mean, mean_ref, rtol=2e-5, atol=2e-6)
         torch.testing.assert_close(sqmean, sq_ref, rtol=2e-5, atol=2e-6)
     r2 = r.clone()
-    out, _, _ = DWConvAddStats(x, w, r2, inplace=True)
-    assert out.data_ptr() == r2.data_ptr() and torch.equal(r2, out_ref)
+    out, _, _ = DWConvAddStats(x, w, r2, inplace=True)  # the built-in choice, writing over the residual
+    assert out.data_ptr() == r2.data_ptr() and torch.equal(r2, _composition(x, r, w)[0])
     assert _lib.device_status() == 0
 
 
