@@ -216,8 +216,9 @@ int kdw_fprop_addstats_f16(const void* x, const void* weight, const void* residu
  *   prologue_type  KDW_ACC_F32: activation computed in fp32 from the fp32 scale / shift and rounded to fp16 - the
  *                  reference operator's arithmetic;  KDW_ACC_F16: scale and shift rounded to fp16, activation one
  *                  packed-half fused multiply-add with ReLU (single rounding) - faster, differs from the fp32 form
- *                  only through the rounding of scale and shift; with tune = 0 it runs on the tensor-core forward
- *                  kernel (the activation is applied to the operand words on their way from shared memory)
+ *                  only through the rounding of scale and shift
+ *                  With tune = 0 both run on the tensor-core forward kernel where one of its tiles takes the shape (the
+ *                  activation is applied to the operand words on their way from shared memory).
  *   tune           0 = built-in choice, 1..kdw_fprop_bnrelu_variants() = explicit tile
  */
 int kdw_fprop_bnrelu_variants(void);

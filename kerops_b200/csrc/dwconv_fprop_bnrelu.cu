@@ -200,7 +200,7 @@ static const int g_n_bnrelu_variants = (int)(sizeof(g_bnrelu_variants) / sizeof(
 bool fprop_bnrelu_mma_fits(int64_t C, int64_t D);
 int launch_fprop_bnrelu_mma(const void* x, const float* scale, const float* shift, const void* w, void* y, int64_t N,
                             int64_t C, int64_t H, int64_t W, int64_t D, int64_t xsN, int64_t xsH, int64_t xsW,
-                            int64_t ysN, int64_t ysH, int64_t ysW, cudaStream_t stream);
+                            int64_t ysN, int64_t ysH, int64_t ysW, bool packed_half, cudaStream_t stream);
 
 static int auto_bnrelu_variant(int64_t C, int64_t D) {
     if (C == 8) return 1;
@@ -241,10 +241,11 @@ int kdw_fprop_bnrelu_f16(const void* x, const float* scale, const float* shift, 
         set_error("fprop_bnrelu: tune=%d names no kernel variant (1..%d)", tune, g_n_bnrelu_variants);
         return KDW_ERR_TUNE;
     }
-    if (tune == 0 && prologue_type == KDW_ACC_F16 && fprop_bnrelu_mma_fits(C, D)) {
-        // packed-half prologue: the tensor-core forward kernel with the activation applied to its operand words
+    if (tune == 0 && fprop_bnrelu_mma_fits(C, D)) {
+        // built-in choice: the tensor-core forward kernel with the activation applied to its operand words
         return launch_fprop_bnrelu_mma(x, scale, shift, weight, y, N, C, H, W, D, x_strideN, x_strideH, x_strideW,
-                                       y_strideN, y_strideH, y_strideW, (cudaStream_t)stream);
+                                       y_strideN, y_strideH, y_strideW, prologue_type == KDW_ACC_F16,
+                                       (cudaStream_t)stream);
     }
     const int id = tune ? tune : auto_bnrelu_variant(C, D);
     const BnReluVariant& v = g_bnrelu_variants[id - 1];

@@ -54,7 +54,8 @@ struct PCfg {
     // fused multiply-add and a maximum per channel-pair word as it arrives from shared memory).  The input tensor map
     // then fills out-of-bounds elements with NaN, NaN survives the multiply-add, and max(NaN, 0) = 0 restores the zero
     // padding of the ACTIVATED tensor without masks.
-    static constexpr int PRO = PRO_;
+    static constexpr int PRO = PRO_;  // 2: the same prologue in fp32 (the reference operator's own arithmetic: fp32
+                                      // multiply-add from the fp32 scale / shift, maximum, one rounding to fp16)
     // 1: fused epilogue out = fp16(conv) + residual with per-channel sums of out and out^2 (kdw_fprop_addstats_f16).
     // A stage then also carries the residual tile of the plane the step finishes; the consumer threads add it to the
     // rounded outputs before staging them and accumulate the stored values in fp32; the sums leave the CTA through one
@@ -334,7 +335,8 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
 
     uint32_t ci = 0, oc = 0;
     int cur_c0 = -1;
-    __half2 sc16[4], sh16[4];  // prologue only: scale / shift of the thread's four channel pairs
+    __half2 sc16[4], sh16[4];  // prologue only: scale / shift of the thread's four channel pairs,
+    float2 sc32[4], sh32[4];   // rounded to fp16 (PRO == 1) or as given (PRO == 2); the unused set costs no registers
     // epilogue only: sums of the stored values and of their squares, per channel pair of the thread; the warp's own
     // workspace row [2][C] (sums, sums of squares), zeroed here and added to when the channel slice changes / at the end
     float2 ssum[4], ssq[4];
@@ -383,8 +385,10 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
 #pragma unroll
                 for (int cp = 0; cp < 4; ++cp) {
                     const int c = c0 + 8 * ng + 2 * cp;
-                    sc16[cp] = __floats2half2_rn(bn_scale[c], bn_scale[c + 1]);
-                    sh16[cp] = __floats2half2_rn(bn_shift[c], bn_shift[c + 1]);
+                    sc32[cp] = make_float2(bn_scale[c], bn_scale[c + 1]);
+                    sh32[cp] = make_float2(bn_shift[c], bn_shift[c + 1]);
+                    sc16[cp] = __float22half2_rn(sc32[cp]);
+                    sh16[cp] = __float22half2_rn(sh32[cp]);
                 }
             }
         }
@@ -414,7 +418,16 @@ __global__ void __launch_bounds__(Cfg::NTHREADS, 1)
                 for (int r = 0; r < 6; ++r) {
                     __half2* xw = reinterpret_cast<__half2*>(&X[r]);
 #pragma unroll
-                    for (int cp = 0; cp < 4; ++cp) xw[cp] = h2_relu_nan0(h2_fma(xw[cp], sc16[cp], sh16[cp]));
+                    for (int cp = 0; cp < 4; ++cp) {
+                        if (Cfg::PRO == 2) {
+                            float2 f = __half22float2(xw[cp]);
+                            f.x = fmaxf(fmaf(f.x, sc32[cp].x, sh32[cp].x), 0.f);  // fmaxf(NaN, 0) = 0
+                            f.y = fmaxf(fmaf(f.y, sc32[cp].y, sh32[cp].y), 0.f);
+                            xw[cp] = __float22half2_rn(f);
+                        } else {
+                            xw[cp] = h2_relu_nan0(h2_fma(xw[cp], sc16[cp], sh16[cp]));
+                        }
+                    }
                 }
             }
             unit(u, X, store, [&](uint4 o0, uint4 o1) {
@@ -662,20 +675,26 @@ int launch_fprop_addstats_mma(const void* x, const void* w, const void* res, voi
     return launch_fprop_pg<PCfg<64, 2, 1, 2, 4, 0, 0, 0, 1>>(a);
 }
 
-// Fused prologue (kdw_fprop_bnrelu_f16 with the packed-half prologue): the built-in tile of each channel count with
-// PCfg::PRO.  Returns KDW_ERR_TUNE without touching the error text when no tensor-core tile takes the shape (the
+// Fused prologue (kdw_fprop_bnrelu_f16): the built-in tile of each channel count with PCfg::PRO = 1 (packed half) or
+// 2 (fp32).  Returns KDW_ERR_TUNE without touching the error text when no tensor-core tile takes the shape (the
 // caller then falls back to its CUDA-core kernels).
 bool fprop_bnrelu_mma_fits(int64_t C, int64_t D) { return C >= 32 || C == 8 || (C == 16 && (D & 1) == 0); }
 
 int launch_fprop_bnrelu_mma(const void* x, const float* scale, const float* shift, const void* w, void* y, int64_t N,
                             int64_t C, int64_t H, int64_t W, int64_t D, int64_t xsN, int64_t xsH, int64_t xsW,
-                            int64_t ysN, int64_t ysH, int64_t ysW, cudaStream_t stream) {
+                            int64_t ysN, int64_t ysH, int64_t ysW, bool packed_half, cudaStream_t stream) {
     PgArgs a{x, w, y, scale, shift, nullptr, 0, 0, 0, nullptr, 0, nullptr, N, C, H, W, D, xsN, xsH, xsW, H, ysN, ysH, ysW,
              0, (int)H, 0, stream};
-    if (C == 8) return launch_fprop_pg<PCfg<8, 4, 4, 2, 4, 1, 0, 1>>(a);
-    if (C == 16) return launch_fprop_pg<PCfg<16, 4, 2, 2, 4, 2, 0, 1>>(a);
-    if (C == 32) return launch_fprop_pg<PCfg<32, 2, 2, 2, 4, 0, 0, 1>>(a);
-    return launch_fprop_pg<PCfg<64, 2, 1, 2, 4, 0, 1, 1>>(a);
+    if (packed_half) {
+        if (C == 8) return launch_fprop_pg<PCfg<8, 4, 4, 2, 4, 1, 0, 1>>(a);
+        if (C == 16) return launch_fprop_pg<PCfg<16, 4, 2, 2, 4, 2, 0, 1>>(a);
+        if (C == 32) return launch_fprop_pg<PCfg<32, 2, 2, 2, 4, 0, 0, 1>>(a);
+        return launch_fprop_pg<PCfg<64, 2, 1, 2, 4, 0, 1, 1>>(a);
+    }
+    if (C == 8) return launch_fprop_pg<PCfg<8, 4, 4, 2, 4, 1, 0, 2>>(a);
+    if (C == 16) return launch_fprop_pg<PCfg<16, 4, 2, 2, 4, 2, 0, 2>>(a);
+    if (C == 32) return launch_fprop_pg<PCfg<32, 2, 2, 2, 4, 0, 0, 2>>(a);
+    return launch_fprop_pg<PCfg<64, 2, 1, 2, 4, 0, 1, 2>>(a);
 }
 
 }  // namespace kdw

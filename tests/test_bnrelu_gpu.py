@@ -101,19 +101,27 @@ def test_every_tile():
 def test_identity_prologue_is_plain_dwconv_of_relu():
     from kerops_b200.ops.conv import DWConv, DWConvBNReLU
 
+    from kerops_b200.ops.conv import _launch
+
     from ._util import dwconv_cuda_core
 
     x, _, _, w = _inputs(1, 32, 9, 17, 40, seed=3)
     one, zero = torch.ones(32, device='cuda'), torch.zeros(32, device='cuda')
-    y = DWConvBNReLU(x, one, zero, w)
-    # bit for bit against a CUDA-core variant of the plain forward pass (the fused kernel runs on the CUDA cores:
-    # same order of the fp32 sums) ...
     xr = torch.relu(x)
+    # the built-in choice is the tensor-core forward tile 17 with the activation applied to its operands: the same
+    # bits as that tile on relu(x), in both prologue arithmetics (scale 1 and shift 0 are exact in fp16)
+    ref = torch.empty_like(xr)
+    _launch.fprop(xr, w, ref, tune=17)
+    assert torch.equal(DWConvBNReLU(x, one, zero, w), ref)
+    assert torch.equal(DWConvBNReLU(x, one, zero, w, PROLOGUE='float16'), ref)
+    # a CUDA-core tile of the fused kernel against a CUDA-core variant of the plain forward pass: same order of the
+    # fp32 sums, same bits
+    y = torch.empty_like(x)
+    _launch.fprop_bnrelu(x, one, zero, w, y, tune=4)
     assert torch.equal(y, dwconv_cuda_core(xr, w))
-    # ... and to the last fp16 bit almost everywhere against the built-in (tensor-core) choice
-    y_def = DWConv(xr, w)
-    assert float((y != y_def).float().mean()) < 1e-3
-    torch.testing.assert_close(y.float(), y_def.float(), rtol=1e-3, atol=2e-3)
+    # ... and to the last fp16 bit almost everywhere against the tensor-core tile
+    assert float((y != ref).float().mean()) < 1e-3
+    torch.testing.assert_close(y.float(), ref.float(), rtol=1e-3, atol=2e-3)
 
 
 def test_against_reference_two_operator_chain():
