@@ -10,6 +10,25 @@ from ... import _lib
 ACC_TYPES = {'float32': 0, 'float16': 1}
 
 
+class _NoSwitch:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def _on(device):
+    """Context in which `device` is the current CUDA device: torch's device guard, or nothing at all when it already
+    is (the usual case; the guard costs several microseconds of a call that takes some forty)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
+
+
 def _stream_ptr(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
@@ -42,7 +61,7 @@ def fprop(x, weight, y, h_begin=None, h_end=None, y_h0=0, acc='float32', tune=0)
     xs = volume_strides(x)
     ys = volume_strides(y)
     tune = tune or _env_tune('KDW_FPROP_TUNE')
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         rc = lib.kdw_fprop_f16_range(
             x.data_ptr(), weight.data_ptr(), y.data_ptr(), N, C, Hx, W, D, xs[0], xs[1], xs[2], Hy, ys[0], ys[1],
             ys[2], h_begin, h_end, y_h0, ACC_TYPES[acc], tune, _stream_ptr(x.device),
@@ -54,7 +73,7 @@ def fprop(x, weight, y, h_begin=None, h_end=None, y_h0=0, acc='float32', tune=0)
 def wgrad_workspace(x):
     lib = _lib.load()
     N, C, H, W, D = x.shape
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         nbytes = lib.kdw_wgrad_workspace_bytes(N, C, H, W, D)
     if nbytes < 0:
         _lib.check(int(nbytes))
@@ -83,7 +102,7 @@ def wgrad(x, grad, h_begin=None, h_end=None, g_h0=0, want_f32=False, want_f16=Tr
         dw32 = torch.empty([3, 3, 3, C], dtype=torch.float32, device=x.device) if want_f32 else None
     dw16 = torch.empty([3, 3, 3, C], dtype=torch.float16, device=x.device) if want_f16 else None
     tune = tune or _env_tune('KDW_WGRAD_TUNE')
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         rc = lib.kdw_wgrad_f16_range(
             x.data_ptr(), grad.data_ptr(), ws.data_ptr(), ws.numel(),
             dw32.data_ptr() if want_f32 else None, dw16.data_ptr() if want_f16 else None,
@@ -100,7 +119,7 @@ def fprop_addstats(x, weight, residual, y, tune=0):
     N, C, H, W, D = x.shape
     xs, rs, ys = volume_strides(x), volume_strides(residual), volume_strides(y)
     tune = tune or _env_tune('KDW_ADDSTATS_TUNE')
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         nbytes = lib.kdw_fprop_addstats_workspace_bytes(N, C, H, W, D)
         ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
         mean = torch.empty(C, dtype=torch.float32, device=x.device)
@@ -120,7 +139,7 @@ def fprop_bnrelu(x, scale, shift, weight, y, prologue='float32', tune=0):
     N, C, H, W, D = x.shape
     xs, ys = volume_strides(x), volume_strides(y)
     tune = tune or _env_tune('KDW_BNRELU_TUNE')
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         rc = lib.kdw_fprop_bnrelu_f16(
             x.data_ptr(), scale.data_ptr(), shift.data_ptr(), weight.data_ptr(), y.data_ptr(), N, C, H, W, D, xs[0],
             xs[1], xs[2], ys[0], ys[1], ys[2], ACC_TYPES[prologue], tune, _stream_ptr(x.device),
