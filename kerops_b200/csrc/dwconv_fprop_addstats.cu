@@ -206,6 +206,7 @@ __global__ void __launch_bounds__(128) stats_reduce_kernel(const float* __restri
     const int k = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (k >= 2 * C) return;
+    grid_dependency_wait();  // launched with launch_overlapping_previous: pass 1 may still be running
     float acc = 0.f;
     for (int r = lane; r < rows; r += 32) acc += ws[(size_t)r * 2 * C + k];
 #pragma unroll
@@ -370,9 +371,8 @@ int kdw_fprop_addstats_f16(const void* x, const void* weight, const void* residu
         if (rc) return rc;
     }
     const float inv = (float)(1.0 / ((double)N * (double)H * (double)W * (double)D));
-    stats_reduce_kernel<<<(2 * (int)C + 3) / 4, 128, 0, (cudaStream_t)stream>>>((const float*)workspace, rows, (int)C, inv,
-                                                                                mean, sqmean);
-    KDW_CUDA(cudaGetLastError());
+    KDW_CUDA(launch_overlapping_previous(stats_reduce_kernel, (unsigned)((2 * (int)C + 3) / 4), 128u, (cudaStream_t)stream,
+                                         (const float*)workspace, rows, (int)C, inv, mean, sqmean));
     return 0;
 }
 

@@ -30,12 +30,15 @@ static constexpr int kMaxRowsFloor = 1184;  // workspace rows are max(8 * SMs, t
 // Pass 2: fixed-order sum over the CTA rows
 // ------------------------------------------------------------------------------------------------
 // One warp per output element k: lane l adds rows l, l+32, ... in order, then the 32 lane sums are combined
-// by a fixed shuffle tree - the same order on every run.
+// by a fixed shuffle tree - the same order on every run.  OVERLAP: launched with launch_overlapping_previous,
+// so pass 1 may still be running when the CTAs are placed.
+template <bool OVERLAP>
 __global__ void __launch_bounds__(128) wgrad_reduce_kernel(const float* __restrict__ ws, int rows, int KC,
                                                           float* __restrict__ dw32, __half* __restrict__ dw16) {
     const int k = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (k >= KC) return;
+    if (OVERLAP) grid_dependency_wait();
     float acc = 0.f;
     for (int r = lane; r < rows; r += 32) acc += ws[(size_t)r * KC + k];
 #pragma unroll
@@ -468,8 +471,8 @@ static int wgrad_dispatch(const void* x, const void* grad, void* workspace, int6
         }
         if (rc) return rc;
     }
-    wgrad_reduce_kernel<<<(KC + 3) / 4, 128, 0, st>>>(ws, rows, KC, dw_f32, (__half*)dw_f16);
-    KDW_CUDA(cudaGetLastError());
+    KDW_CUDA(launch_overlapping_previous(wgrad_reduce_kernel<true>, (unsigned)((KC + 3) / 4), 128u, st, (const float*)ws,
+                                         rows, KC, dw_f32, (__half*)dw_f16));
     return 0;
 }
 
@@ -544,7 +547,7 @@ static int wgrad_static_dispatch(const void* x, const void* grad, float* dw_f32,
         rc = v.f(a, &rows);  // the launcher never uses more CTAs (= rows) than a.ws_rows
         if (rc) return rc;
     }
-    wgrad_reduce_kernel<<<(KC + 3) / 4, 128, 0, st>>>(ws, rows, KC, dw_f32, (__half*)dw_f16);
+    wgrad_reduce_kernel<false><<<(KC + 3) / 4, 128, 0, st>>>(ws, rows, KC, dw_f32, (__half*)dw_f16);
     KDW_CUDA(cudaGetLastError());
     return 0;
 }

@@ -55,6 +55,7 @@ __global__ void __launch_bounds__(kPushThreads) grad_push_sum_kernel(const float
     const long long flag_off = push_payload_floats(capacity);
     const long long mine = ((long long)(seq & 1u) * world + rank) * slot;  // where this rank's data goes, in every buffer
     if (tid == 0) s_failed = 0;
+    grid_dependency_wait();  // launched with launch_overlapping_previous: `local` is complete after this
     // 1. push the payload to every rank (own buffer included)
     for (int p = 0; p < world; ++p) {
         float* dst = peers.buf[p] + mine;
@@ -128,10 +129,9 @@ int kdw_allreduce_push_f32(const float* local, float* out_f32, void* out_f16, vo
     int* status = nullptr;
     int rc = status_ptr(&status);
     if (rc) return rc;
-    grad_push_sum_kernel<<<1, kPushThreads, 0, (cudaStream_t)stream>>>(local, out_f32, (__half*)out_f16, peers, (int)n,
-                                                                        (long long)capacity, rank, world, seq,
-                                                                        (unsigned long long)timeout_ns, status);
-    KDW_CUDA(cudaGetLastError());
+    KDW_CUDA(launch_overlapping_previous(grad_push_sum_kernel, 1u, (unsigned)kPushThreads, (cudaStream_t)stream, local,
+                                         out_f32, (__half*)out_f16, peers, (int)n, (long long)capacity, rank, world,
+                                         (unsigned)seq, (unsigned long long)timeout_ns, status));
     return 0;
 }
 

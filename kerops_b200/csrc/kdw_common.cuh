@@ -56,6 +56,29 @@ int encode_paired_map(CUtensorMap* map, const void* base, int64_t N, int64_t C, 
 
 int device_sm_count(int* sms);
 
+#ifdef __CUDACC__
+// Launches a small follow-up kernel (the fixed-order sums over per-CTA rows, the gradient exchange) with
+// programmatic stream serialisation: its CTAs may be placed while the kernel before it in the stream is still
+// draining, so the launch latency between two dependent kernels is hidden.  Such a kernel must execute
+// grid_dependency_wait() before it touches anything the previous kernel wrote - the wait returns when that kernel
+// has completed and its writes are visible; under an ordinary launch the wait returns at once.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapping_previous(void (*kernel)(KArgs...), unsigned grid, unsigned block, cudaStream_t st,
+                                               Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
+
 // Per kernel and device: the opt-in to `smem` bytes of dynamic shared memory, the CTAs per SM the kernel reaches
 // with `threads` threads and the SM count - looked up on the first launch on a device and remembered (one
 // static instance per kernel instantiation).
@@ -186,6 +209,9 @@ struct StepIter {
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// See launch_overlapping_previous: blocks until the previous kernel of the stream has completed.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
